@@ -1,0 +1,32 @@
+import os
+import sys
+
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
+sys.path.insert(0, os.path.dirname(HERE))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200)")
+
+
+@pytest.fixture
+def emulated(monkeypatch):
+    """The package with its kernels replaced by the CPU stand-ins of tests/emulated_ops.py."""
+    import emulated_ops
+    emulated_ops.install(monkeypatch)
+    return emulated_ops
+
+
+@pytest.fixture(scope="session")
+def model_folders(tmp_path_factory):
+    """Tiny random models A and B, written once per test session into a temporary folder."""
+    from tiny_configs import TINY_A, TINY_A_INIT, TINY_B, TINY_B_INIT
+    from velomind_b200 import write_random_model
+    root = tmp_path_factory.mktemp("models")
+    return {
+        "tiny_a": write_random_model(str(root / "tiny_a"), TINY_A, **TINY_A_INIT),
+        "tiny_b": write_random_model(str(root / "tiny_b"), TINY_B, **TINY_B_INIT),
+    }

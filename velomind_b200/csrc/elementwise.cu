@@ -1,0 +1,144 @@
+// Embedding gather, fused residual-add + RMSNorm, residual add, SwiGLU.
+//
+// The residual stream is float32 in both compute modes; norms and the residual sum are computed in
+// float32.  T is the activation type (float or bf16).
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding: out[t,:] = table[tokens[t],:]
+// Reference: src/cpu/ops/embedding.cpp:27-32.  Ids are validated on the host before the launch; the
+// kernel still refuses an id outside the table (writes zeros and raises the error word).
+template <typename W>
+__global__ void embed_gather_kernel(const W* __restrict__ table, const int* __restrict__ tokens,
+                                    float* __restrict__ out, int T, int hid, int vocab, int* __restrict__ err) {
+    const int t = blockIdx.x;
+    const int id = tokens[t];
+    const bool ok = (id >= 0 && id < vocab);
+    if (!ok && threadIdx.x == 0 && err) atomicExch(err, 1);
+    const W* row = table + (size_t)(ok ? id : 0) * hid;
+    for (int i = threadIdx.x; i < hid; i += blockDim.x)
+        out[(size_t)t * hid + i] = ok ? vm_to_float(row[i]) : 0.f;
+}
+
+VM_API int vm_embed_gather(const void* table, int table_dtype, const int* tokens, float* out, int T, int hid,
+                           int vocab, int* err, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    const int threads = hid >= 512 ? 256 : 128;
+    if (table_dtype == VM_F32)
+        embed_gather_kernel<float><<<T, threads, 0, stream>>>((const float*)table, tokens, out, T, hid, vocab, err);
+    else if (table_dtype == VM_BF16)
+        embed_gather_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>((const __nv_bfloat16*)table, tokens, out, T, hid, vocab, err);
+    else
+        return VM_ERR_UNSUPPORTED;
+    return vm_launch_status();
+}
+
+// ---------------------------------------------------------------- h (+= delta); out = rmsnorm(h) * w
+// Reference: src/cpu/ops/rmsnorm.cpp:42-59: inv = 1/sqrt(mean(x^2) + eps); y = x * inv * w.
+// One block per output row.  rows == nullptr: output row r reads residual row r and the sum is written
+// back to h.  rows != nullptr: output row r reads residual row rows[r]; h is left untouched (the caller
+// has no further use for it).
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ delta, const float* __restrict__ w,
+                                   T* __restrict__ out, const int* __restrict__ rows, int hid, float eps) {
+    extern __shared__ float row[];          // hid floats
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    float* hrow = h + (size_t)src * hid;
+    const T* drow = delta ? delta + (size_t)src * hid : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hid; i += blockDim.x) {
+        float v = hrow[i];
+        if (drow) v += vm_to_float(drow[i]);
+        row[i] = v;
+        ss += v * v;
+    }
+    ss = vm_block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)hid + eps);
+    for (int i = threadIdx.x; i < hid; i += blockDim.x) {
+        const float v = row[i];
+        if (drow && !rows) hrow[i] = v;
+        out[(size_t)r * hid + i] = vm_from_float<T>(v * inv * w[i]);
+    }
+}
+
+VM_API int vm_add_rmsnorm(float* h, const void* delta, const float* w, void* out, const int* rows, int n_out,
+                          int hid, float eps, int act_dtype, cudaStream_t stream) {
+    if (n_out <= 0) return 0;
+    const int threads = hid >= 1024 ? 256 : 128;
+    const size_t smem = (size_t)hid * sizeof(float);
+    if (smem > 200 * 1024) return VM_ERR_UNSUPPORTED;
+    if (act_dtype == VM_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        add_rmsnorm_kernel<float><<<n_out, threads, smem, stream>>>(h, (const float*)delta, w, (float*)out, rows, hid, eps);
+    } else if (act_dtype == VM_BF16) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        add_rmsnorm_kernel<__nv_bfloat16><<<n_out, threads, smem, stream>>>(h, (const __nv_bfloat16*)delta, w, (__nv_bfloat16*)out, rows, hid, eps);
+    } else {
+        return VM_ERR_UNSUPPORTED;
+    }
+    return vm_launch_status();
+}
+
+// ---------------------------------------------------------------- h += delta
+template <typename T>
+__global__ void residual_add_kernel(float* __restrict__ h, const T* __restrict__ delta, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        h[i] += vm_to_float(delta[i]);
+}
+
+VM_API int vm_residual_add(float* h, const void* delta, long long n, int act_dtype, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const int threads = 256;
+    const int blocks = (int)((n + threads - 1) / threads < 148 * 8 ? (n + threads - 1) / threads : 148 * 8);
+    if (act_dtype == VM_F32) residual_add_kernel<float><<<blocks, threads, 0, stream>>>(h, (const float*)delta, (size_t)n);
+    else if (act_dtype == VM_BF16) residual_add_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(h, (const __nv_bfloat16*)delta, (size_t)n);
+    else return VM_ERR_UNSUPPORTED;
+    return vm_launch_status();
+}
+
+// ---------------------------------------------------------------- out[t,i] = silu(gu[t,i]) * gu[t,I+i]
+// Reference: examples/common/llama/llama_graph.cpp:22-28, src/cpu/ops/sigmoid.cpp:23-26:
+// (1/(1+exp(-g)) * g) * u, in float32.
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int T_, int I) {
+    const size_t n = (size_t)T_ * I;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / I;
+        const int i = (int)(idx - t * I);
+        const float g = vm_to_float(gu[t * 2 * I + i]);
+        const float u = vm_to_float(gu[t * 2 * I + I + i]);
+        const float sig = 1.0f / (1.0f + expf(-g));
+        out[idx] = vm_from_float<T>((sig * g) * u);
+    }
+}
+
+VM_API int vm_swiglu(const void* gate_up, void* out, int T, int I, int act_dtype, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    const size_t n = (size_t)T * I;
+    const int threads = 256;
+    const size_t want = (n + threads - 1) / threads;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    if (act_dtype == VM_F32) swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, T, I);
+    else if (act_dtype == VM_BF16) swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, T, I);
+    else return VM_ERR_UNSUPPORTED;
+    return vm_launch_status();
+}
+
+// ---------------------------------------------------------------- dtype conversion (mixed-precision edges)
+template <typename A, typename B>
+__global__ void convert_kernel(const A* __restrict__ in, B* __restrict__ out, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = vm_from_float<B>(vm_to_float(in[i]));
+}
+
+VM_API int vm_convert(const void* in, int in_dtype, void* out, int out_dtype, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const int threads = 256;
+    const size_t want = ((size_t)n + threads - 1) / threads;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    if (in_dtype == VM_F32 && out_dtype == VM_BF16) convert_kernel<float, __nv_bfloat16><<<blocks, threads, 0, stream>>>((const float*)in, (__nv_bfloat16*)out, (size_t)n);
+    else if (in_dtype == VM_BF16 && out_dtype == VM_F32) convert_kernel<__nv_bfloat16, float><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)in, (float*)out, (size_t)n);
+    else return VM_ERR_UNSUPPORTED;
+    return vm_launch_status();
+}

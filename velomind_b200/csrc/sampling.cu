@@ -1,0 +1,187 @@
+// Sampling on the device: greedy, temperature and nucleus (top-p), one block per row of logits.
+//
+// Rules of the reference's sampler (examples/common/llama/llama_engine.cpp:668-726):
+//   * temperature <= 0 or top_p <= 0: greedy; NaN is skipped, the first maximum wins, all-NaN gives -1;
+//   * otherwise p_i = exp((x_i - max) / T) in float, normalised by a sum kept in double; the nucleus is
+//     the smallest set of most probable tokens whose mass reaches top_p; draw r uniform in [0, mass) and
+//     walk the nucleus until the running sum reaches r.
+// Differences, on purpose: the uniform number comes from Philox-4x32-10 keyed by (seed; stream, step)
+// instead of one std::mt19937 shared by all draws, so a request's tokens do not depend on what else is
+// in the batch; the walk goes in index order, not in sorted order, and every token that ties with the
+// least probable nucleus member belongs to the nucleus (same distribution; no sort of the vocabulary).
+#include "common.cuh"
+
+constexpr int SAMPLE_THREADS = 1024;
+
+__device__ __forceinline__ double warp_sum_d(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ double block_sum_d(double v, double* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_sum_d(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    double t = (lane < (int)((blockDim.x + 31) >> 5)) ? red[lane] : 0.0;
+    return warp_sum_d(t);
+}
+
+__device__ __forceinline__ void philox4x32_10(uint32_t c[4], uint32_t k0, uint32_t k1) {
+    const uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        const uint32_t hi0 = __umulhi(M0, c[0]), lo0 = M0 * c[0];
+        const uint32_t hi1 = __umulhi(M1, c[2]), lo1 = M1 * c[2];
+        const uint32_t n0 = hi1 ^ c[1] ^ k0, n2 = hi0 ^ c[3] ^ k1;
+        c[0] = n0; c[1] = lo1; c[2] = n2; c[3] = lo0;
+        k0 += W0; k1 += W1;
+    }
+}
+
+struct ArgBest { float v; int i; };
+
+__device__ __forceinline__ ArgBest better(ArgBest a, ArgBest b) {   // larger value; on a tie the lower index
+    if (b.i < 0) return a;
+    if (a.i < 0) return b;
+    if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
+    return a;
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_kernel(const float* __restrict__ logits, long long row_stride, int V, const float* __restrict__ temperature,
+              const float* __restrict__ top_p, const long long* __restrict__ seed, const long long* __restrict__ stream_id,
+              const long long* __restrict__ step, int* __restrict__ out) {
+    __shared__ double redd[32];
+    __shared__ float redv[32];
+    __shared__ int redi[32];
+    __shared__ double sums[SAMPLE_THREADS];
+    __shared__ int s_choice;
+    const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* x = logits + (size_t)row * row_stride;
+    const float temp = temperature ? temperature[row] : 0.f;
+    const float tp = top_p ? top_p[row] : 1.f;
+
+    // ---- maximum (NaN skipped) with its first index
+    ArgBest best{-INFINITY, -1};
+    for (int i = tid; i < V; i += blockDim.x) {
+        const float v = x[i];
+        if (v != v) continue;
+        best = better(best, ArgBest{v, i});
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        ArgBest other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+        best = better(best, other);
+    }
+    if (lane == 0) { redv[warp] = best.v; redi[warp] = best.i; }
+    __syncthreads();
+    best = ArgBest{-INFINITY, -1};
+    for (int k = 0; k < (int)(blockDim.x >> 5); ++k) best = better(best, ArgBest{redv[k], redi[k]});
+    if (!(temp > 0.f) || !(tp > 0.f) || best.i < 0) {
+        if (tid == 0) out[row] = best.i;
+        return;
+    }
+    // the reference takes the max over FINITE values only (an all -inf/+inf row gives -1)
+    float max_v = best.v;
+    if (isinf(max_v)) {
+        float fm = -INFINITY; int any = 0;
+        for (int i = tid; i < V; i += blockDim.x) { const float v = x[i]; if (isfinite(v)) { fm = fmaxf(fm, v); any = 1; } }
+        fm = vm_warp_max(fm); any = __any_sync(0xffffffffu, any);
+        __syncthreads();
+        if (lane == 0) { redv[warp] = fm; redi[warp] = any; }
+        __syncthreads();
+        fm = -INFINITY; any = 0;
+        for (int k = 0; k < (int)(blockDim.x >> 5); ++k) { fm = fmaxf(fm, redv[k]); any |= redi[k]; }
+        if (!any) { if (tid == 0) out[row] = -1; return; }
+        max_v = fm;
+    }
+    const float inv_t = 1.0f / temp;
+    auto prob_raw = [&](int i) -> float {
+        const float v = x[i];
+        return (v != v) ? 0.f : expf((v - max_v) * inv_t);
+    };
+    double part = 0.0;
+    for (int i = tid; i < V; i += blockDim.x) part += (double)prob_raw(i);
+    const double total = block_sum_d(part, redd);
+    const float inv_sum = (float)(1.0 / total);
+    auto prob = [&](int i) -> float { return prob_raw(i) * inv_sum; };
+
+    // ---- nucleus threshold: the largest tau with sum{p_i >= tau} >= top_p (bisection on the float bits)
+    float tau = 0.f;
+    if (tp < 1.0f) {
+        float pmax = 0.f;
+        for (int i = tid; i < V; i += blockDim.x) pmax = fmaxf(pmax, prob(i));
+        pmax = vm_warp_max(pmax);
+        __syncthreads();
+        if (lane == 0) redv[warp] = pmax;
+        __syncthreads();
+        pmax = 0.f;
+        for (int k = 0; k < (int)(blockDim.x >> 5); ++k) pmax = fmaxf(pmax, redv[k]);
+        uint32_t lo = 0u, hi = __float_as_uint(pmax) + 1u;   // cond(lo) holds or tau stays 0; cond(hi) fails
+        while (hi - lo > 1u) {
+            const uint32_t mid = lo + (hi - lo) / 2u;
+            const float th = __uint_as_float(mid);
+            double s = 0.0;
+            for (int i = tid; i < V; i += blockDim.x) { const float p = prob(i); if (p >= th) s += (double)p; }
+            s = block_sum_d(s, redd);
+            if (s >= (double)tp) lo = mid; else hi = mid;
+        }
+        tau = __uint_as_float(lo);
+    }
+
+    // ---- mass of the nucleus and the walk in index order
+    const int chunk = (V + blockDim.x - 1) / blockDim.x;
+    const int i0 = min(V, tid * chunk), i1 = min(V, i0 + chunk);
+    double mine = 0.0;
+    for (int i = i0; i < i1; ++i) { const float v = x[i]; const float p = prob(i); if (v == v && p >= tau) mine += (double)p; }
+    sums[tid] = mine;
+    __syncthreads();
+    if (tid == 0) {
+        double acc = 0.0;
+        for (int k = 0; k < (int)blockDim.x; ++k) { const double s = sums[k]; sums[k] = acc; acc += s; }
+        redd[0] = acc;          // mass
+        s_choice = 0x7fffffff;
+    }
+    __syncthreads();
+    const double mass = redd[0];
+    uint32_t c[4];
+    const unsigned long long st = (unsigned long long)(step ? step[row] : 0), sid = (unsigned long long)(stream_id ? stream_id[row] : 0);
+    const unsigned long long sd = (unsigned long long)(seed ? seed[row] : 0);
+    c[0] = (uint32_t)st; c[1] = (uint32_t)(st >> 32); c[2] = (uint32_t)sid; c[3] = (uint32_t)(sid >> 32);
+    philox4x32_10(c, (uint32_t)sd, (uint32_t)(sd >> 32));
+    const float u = (float)(c[0] >> 8) * (1.0f / 16777216.0f);
+    const double r = (double)u * mass;
+    // the chunk in which the running sum first reaches r walks its members
+    const double before = sums[tid];
+    if (before <= r) {
+        double acc = before;
+        for (int i = i0; i < i1; ++i) {
+            const float v = x[i]; const float p = prob(i);
+            if (v == v && p >= tau) {
+                acc += (double)p;
+                if (acc >= r) { atomicMin(&s_choice, i); break; }
+            }
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int choice = s_choice;
+        if (choice == 0x7fffffff) {       // rounding left the running sum short of r: the last member
+            choice = -1;
+            for (int i = V - 1; i >= 0; --i) { const float v = x[i]; if (v == v && prob(i) >= tau) { choice = i; break; } }
+        }
+        out[row] = choice;
+    }
+}
+
+VM_API int vm_sample(const float* logits, long long row_stride, int R, int V, const float* temperature,
+                     const float* top_p, const long long* seed, const long long* stream_id, const long long* step,
+                     int* out, cudaStream_t stream) {
+    if (R <= 0) return 0;
+    if (V <= 0) return VM_ERR_BAD_ARG;
+    sample_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(logits, row_stride, V, temperature, top_p, seed, stream_id, step, out);
+    return vm_launch_status();
+}

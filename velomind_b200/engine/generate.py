@@ -1,0 +1,159 @@
+"""The generation loop: batches of unequal prompts, stop tokens, sequences that end early, batch after batch.
+
+The reference generates one sequence: prefill, sample, then feed each token
+back until `max_new_tokens` or the end-of-sequence token, which is kept in the
+output and not fed (examples/common/llama/llama_engine.cpp:633-653;
+`max_new_tokens == 0` returns after the prompt, :635-637).  The same rules
+hold here for every sequence of a batch; a sequence that ends leaves the batch
+at once and its slot and pages go back to the cache; requests that did not fit
+into one batch run in the next.
+
+The loop only needs `open() / close(slot) / step(entries) -> logits` and a
+sampler, so its decisions can be tested without a GPU.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Callable, List, Optional, Sequence
+
+from ..cache.pages import PAGE_TOKENS
+from ..sampling.sampler import SamplingParams
+from .step import Entry
+
+
+@dataclass
+class Request:
+    prompt: Sequence[int]
+    params: SamplingParams = SamplingParams()
+    stream: int = 0                      # Philox stream of this request (its index, by default)
+
+
+@dataclass
+class Result:
+    """What the reference returns per call (llama_engine.h:32-38), per sequence."""
+    tokens: List[int] = field(default_factory=list)
+    finish_reason: str = ""              # "stop" (a stop token, kept in `tokens`), "length", "empty"
+    prompt_tokens: int = 0
+
+
+@dataclass
+class Timing:
+    prefill_seconds: float = 0.0
+    decode_seconds: float = 0.0
+    decode_steps: int = 0
+    generated_tokens: int = 0
+
+    @property
+    def tokens_per_second(self) -> float:
+        total = self.prefill_seconds + self.decode_seconds
+        return self.generated_tokens / total if total > 0 else 0.0
+
+
+def pages_for(request: Request) -> int:
+    """Pages a request may come to hold: prompt plus every token it may feed back."""
+    most = len(request.prompt) + max(request.params.max_tokens - 1, 0)
+    return -(-max(most, 1) // PAGE_TOKENS)
+
+
+def plan_batches(requests: Sequence[Request], total_pages: int, max_batch: int) -> List[List[int]]:
+    """Cut the request list, in order, into batches that fit the cache (by pages) and `max_batch` slots.
+    Raises ValueError for a request that cannot fit even alone."""
+    batches: List[List[int]] = []
+    cur: List[int] = []
+    used = 0
+    for i, r in enumerate(requests):
+        need = pages_for(r)
+        if need > total_pages:
+            raise ValueError(f"request {i} may reach {need * PAGE_TOKENS} cached tokens; the cache holds {total_pages * PAGE_TOKENS}")
+        if cur and (used + need > total_pages or len(cur) >= max_batch):
+            batches.append(cur)
+            cur, used = [], 0
+        cur.append(i)
+        used += need
+    if cur:
+        batches.append(cur)
+    return batches
+
+
+class GenerationLoop:
+    """Runs requests through a stepper (`open`, `close`, `step`) with a sampler
+    (`sample(logits, params, streams, steps) -> token per row`)."""
+
+    def __init__(self, stepper, sampler, total_pages: int, max_batch: int, default_stop: Sequence[int] = ()):
+        self.stepper = stepper
+        self.sampler = sampler
+        self.total_pages = int(total_pages)
+        self.max_batch = int(max_batch)
+        self.default_stop = tuple(default_stop)
+        self.timing = Timing()
+
+    def run(self, requests: Sequence[Request],
+            on_token: Optional[Callable[[int, int], None]] = None) -> List[Result]:
+        """Generate for every request; `on_token(request_index, token)` is called as tokens appear."""
+        requests = list(requests)
+        results = [Result(prompt_tokens=len(r.prompt)) for r in requests]
+        self.timing = Timing()
+        for batch in plan_batches(requests, self.total_pages, self.max_batch):
+            self._run_batch(requests, batch, results, on_token)
+        return results
+
+    def _run_batch(self, requests, batch, results, on_token) -> None:
+        stepper = self.stepper
+        live = []                        # (request index, slot)
+        for i in batch:
+            r = requests[i]
+            if r.params.max_tokens <= 0:
+                results[i].finish_reason = "length"      # llama_engine.cpp:635-637: nothing to generate
+                continue
+            if len(r.prompt) == 0:
+                results[i].finish_reason = "empty"
+                continue
+            live.append((i, stepper.open()))
+        try:
+            t0 = time.perf_counter()
+            feed = {i: list(requests[i].prompt) for i, _ in live}
+            step_no = 0
+            while live:
+                entries = [Entry(slot, feed[i], [len(feed[i]) - 1]) for i, slot in live]
+                logits = stepper.step(entries)
+                tokens = self.sampler.sample(
+                    logits, [requests[i].params for i, _ in live],
+                    [requests[i].stream for i, _ in live],
+                    [len(results[i].tokens) for i, _ in live])
+                now = time.perf_counter()
+                if step_no == 0:
+                    self.timing.prefill_seconds += now - t0
+                else:
+                    self.timing.decode_seconds += now - t0
+                    self.timing.decode_steps += 1
+                t0 = now
+                still = []
+                for (i, slot), tok in zip(live, tokens):
+                    tok = int(tok)
+                    res, par = results[i], requests[i].params
+                    res.tokens.append(tok)
+                    self.timing.generated_tokens += 1
+                    if on_token is not None:
+                        on_token(i, tok)
+                    stops = par.stop_tokens if par.stop_tokens else self.default_stop
+                    if tok in stops:
+                        res.finish_reason = "stop"
+                    elif len(res.tokens) >= par.max_tokens:
+                        res.finish_reason = "length"
+                    elif tok < 0:
+                        res.finish_reason = "error"
+                    if res.finish_reason:
+                        stepper.close(slot)          # the slot and its pages are free for the next batch at once
+                    else:
+                        feed[i] = [tok]
+                        still.append((i, slot))
+                live = still
+                step_no += 1
+        except Exception:
+            for _, slot in live:
+                try:
+                    stepper.close(slot)
+                except Exception:
+                    pass
+            raise

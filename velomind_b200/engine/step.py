@@ -1,0 +1,352 @@
+"""The step function: a batch of sequences, each bringing its next tokens; one pass from the cache.
+
+The reference has two entry points for one sequence, `prefill(tokens)` and
+`forward_step(token, pos)`, each of which builds, compiles and allocates a new
+graph (examples/common/llama/llama_engine.cpp:333-393, :395-455).  Here one
+function serves any batch: whole prompts of unequal lengths in one step, then
+one token per sequence, or any other cut.  It runs only the tokens it is
+given, packed without padding, reads and extends the cache in place, and
+returns float32 logits at the wanted places.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..cache.pages import PAGE_TOKENS, CacheError
+from ..cache.store import SequenceCache
+from ..kernels import ops
+from .arena import Workspace
+from .model import DecoderModel
+
+
+@dataclass
+class Entry:
+    """One sequence's share of a step: its slot, its next tokens, and the places among these tokens
+    (0-based) whose logits are wanted."""
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+def _bucket(n: int, fine_from: int = 512, fine_step: int = 512, floor: int = 8) -> int:
+    """Capacity a count is rounded up to, so that few distinct buffer plans exist."""
+    n = max(int(n), 1)
+    if n <= fine_from:
+        b = floor
+        while b < n:
+            b *= 2
+        return b
+    return -(-n // fine_step) * fine_step
+
+
+def _host_buffer(n: int, dtype: torch.dtype) -> torch.Tensor:
+    """Page-locked host memory, so that the copy to the device is asynchronous."""
+    return torch.empty(n, dtype=dtype, pin_memory=True)
+
+
+def _new_event():
+    return torch.cuda.Event()
+
+
+class Descriptors:
+    """The integers that describe one step, laid out in one pinned host buffer and one device buffer of
+    the same layout, so that a step costs one host-to-device copy."""
+
+    def __init__(self, T: int, B: int, R: int, table_widths: Sequence[int], device):
+        self.caps = (T, B, R, tuple(table_widths))
+        fields = [("tokens", T), ("positions", T), ("seq_of_token", T), ("cu_tokens", B + 1), ("slots", B),
+                  ("ctx_len", B), ("logit_rows", max(R, 1))]
+        for g, w in enumerate(table_widths):
+            fields.append((f"table{g}", B * w))
+        self.offsets: Dict[str, Tuple[int, int]] = {}
+        off = 0
+        for name, n in fields:
+            self.offsets[name] = (off, n)
+            off += -(-n // 4) * 4          # 16-byte aligned fields
+        self.total = off
+        self.host = _host_buffer(off, torch.int32)
+        self.host_np = self.host.numpy()
+        self.dev = torch.zeros(off, dtype=torch.int32, device=device)
+        self.copied = _new_event()
+        self.used = False
+
+    def h(self, name: str) -> np.ndarray:
+        off, n = self.offsets[name]
+        return self.host_np[off: off + n]
+
+    def d(self, name: str) -> torch.Tensor:
+        off, n = self.offsets[name]
+        return self.dev[off: off + n]
+
+    def upload(self) -> None:
+        self.dev.copy_(self.host, non_blocking=True)
+        self.copied.record()
+        self.used = True
+
+    def wait_reusable(self) -> None:
+        if self.used:
+            self.copied.synchronize()
+
+
+class StepContext:
+    """What the parts see of a step: packed tokens and their places, the cache, scratch buffers.
+
+    Device tensors (int32): tokens [T], positions [T] (place of each token in its sequence),
+    seq_of_token [T] (index into the batch), cu_tokens [B+1] (token offsets of the sequences),
+    slots [B] (cache slot of each sequence), ctx_len [B] (length after this step), logit_rows [R].
+    Host copies of the same live in `host_*` numpy arrays.
+    """
+
+    def __init__(self, engine: "Engine", desc: Descriptors, T: int, B: int, R: int, table_widths: Sequence[int]):
+        self.engine = engine
+        self.cache: SequenceCache = engine.cache
+        self.ws: Workspace = engine.ws
+        self.act_dtype: torch.dtype = engine.dtype
+        self.err: torch.Tensor = engine.err
+        self.T, self.B, self.R = T, B, R
+        self.T_cap, self.B_cap, self.R_cap, _ = desc.caps
+        self.desc = desc
+        self.tokens = desc.d("tokens")[:T]
+        self.positions = desc.d("positions")[:T]
+        self.seq_of_token = desc.d("seq_of_token")[:T]
+        self.cu_tokens = desc.d("cu_tokens")[:B + 1]
+        self.slots = desc.d("slots")[:B]
+        self.ctx_len = desc.d("ctx_len")[:B]
+        self.logit_rows = desc.d("logit_rows")[:R]
+        self.tables = [desc.d(f"table{g}").view(self.B_cap, w)[:B] for g, w in enumerate(table_widths)]
+        self.host_positions = desc.h("positions")[:T]
+        self.host_cu_tokens = desc.h("cu_tokens")[:B + 1]
+        self.host_ctx_len = desc.h("ctx_len")[:B]
+        self.host_slots = desc.h("slots")[:B]
+        self.max_ctx_len = int(self.host_ctx_len.max()) if B else 0
+        self.max_new = int(np.diff(self.host_cu_tokens).max()) if B else 0
+        self.one_token_each = (self.max_new == 1 and T == B)
+        self.run: Optional[int] = None
+        self.logits: Optional[torch.Tensor] = None
+
+    # ---- scratch
+    def take_tokens(self, cols: int, dtype: torch.dtype) -> torch.Tensor:
+        """A [T, cols] buffer (backed by capacity rows, so that the plan of the bucket fits every step in it)."""
+        return self.ws.take((self.T_cap, cols), dtype)[: self.T]
+
+    def take_rows(self, cols: int, dtype: torch.dtype) -> torch.Tensor:
+        return self.ws.take((self.R_cap, cols), dtype)[: self.R]
+
+    def take(self, shape, dtype: torch.dtype) -> torch.Tensor:
+        return self.ws.take(shape, dtype)
+
+    # ---- the cache of the layer that is running
+    def kv(self):
+        """(k_pages, v_pages, block_table, owns) of the running schedule position: pages
+        [n_pages, kv_heads, 64, head_dim], block_table int32 [B, width] (page of each 64-token block of each
+        sequence of the batch; -1 where none), owns False when the run reads another run's cache."""
+        g, layer = self.cache.where(self.run)
+        group = self.cache.groups[g]
+        k, v = group.layer(layer)
+        owns = self.engine.model.plan.schedule[self.run].cache_of is None
+        return k, v, self.tables[g], owns
+
+    def state(self) -> Optional[torch.Tensor]:
+        """The fixed-size float32 state [max_slots, n] of the running schedule position (index it with
+        `ctx.slots`); None if the mixer asked for none.  Zeroed when a slot is opened."""
+        return self.cache.state[self.run]
+
+
+class Engine:
+    """A model on one GPU with its cache: open/close sequence slots and step batches through the model."""
+
+    def __init__(self, model: DecoderModel, max_tokens: int, max_slots: Optional[int] = None,
+                 max_step_tokens: int = 8192):
+        if model.device is None:
+            raise RuntimeError("the model has no weights bound; use load_model()")
+        self.model = model
+        self.device = ops.require_cuda(model.device)
+        self.dtype = model.dtype
+        self.vocab = model.plan.vocab_size
+        self.max_step_tokens = int(max_step_tokens)
+        # pages are whole: round the budget up
+        max_tokens = -(-int(max_tokens) // PAGE_TOKENS) * PAGE_TOKENS
+        self.cache = SequenceCache(model.cache_needs(), model.cache_shares(), max_tokens, model.plan.max_positions,
+                                   self.dtype, self.device, max_slots)
+        self.ws = Workspace(self.device)
+        self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._desc: Dict[Tuple, Descriptors] = {}
+        self._logits: Optional[torch.Tensor] = None
+        self.steps_run = 0
+
+    # ---- slots
+    def open(self) -> int:
+        return self.cache.open()
+
+    def close(self, slot: int) -> None:
+        self.cache.close(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length[slot]
+
+    # ---- one step
+    def step(self, entries: Sequence[Entry]) -> torch.Tensor:
+        """Run the entries' tokens as one batch from the cache; return float32 logits [wanted, vocab] on the
+        device, in the order of the entries and of each entry's `want`.  The tensor is valid until the next step."""
+        entries = list(entries)
+        self._validate(entries)
+        n_rows = sum(len(e.want) for e in entries)
+        logits = self._logits_buffer(n_rows)
+        total = sum(len(e.tokens) for e in entries)
+        if total <= self.max_step_tokens:
+            chunks = [[(i, 0, len(e.tokens)) for i, e in enumerate(entries) if len(e.tokens)]]
+        else:
+            chunks = self._cut(entries)
+        # rows come out in processing order (entry, then place); `order` maps them to the asked-for order
+        produced: List[Tuple[int, int]] = []
+        row0 = 0
+        for chunk in chunks:
+            if not chunk:
+                continue
+            rows_here = self._run_chunk(entries, chunk, logits, row0, produced)
+            row0 += rows_here
+        asked = [(i, int(w)) for i, e in enumerate(entries) for w in e.want]
+        if produced != asked:
+            index = {key: r for r, key in enumerate(produced)}
+            perm = torch.tensor([index[k] for k in asked], dtype=torch.long, device=self.device)
+            logits = logits[:n_rows].index_select(0, perm)
+        self.steps_run += 1
+        return logits[:n_rows]
+
+    def raise_if_error(self) -> None:
+        """Synchronise and raise if a kernel reported a fault of the step's descriptors (no page, bad id)."""
+        code = int(self.err.item())
+        if code:
+            self.err.zero_()
+            what = {1: "a token id outside the vocabulary", 2: "a cache write without a page",
+                    3: "a cache read without a page"}.get(code, f"code {code}")
+            raise CacheError(f"a kernel reported {what}")
+
+    # ---- internals
+    def _validate(self, entries: Sequence[Entry]) -> None:
+        seen = set()
+        need: Dict[int, int] = {}
+        for e in entries:
+            if e.slot in seen:
+                raise ValueError(f"slot {e.slot} appears twice in one step")
+            seen.add(e.slot)
+            if not self.cache.slots.is_held(e.slot):
+                raise CacheError(f"slot {e.slot} is not open")
+            n = len(e.tokens)
+            if n == 0 and len(e.want):
+                raise ValueError(f"slot {e.slot}: logits wanted but no tokens given")
+            for t in e.tokens:
+                if not 0 <= int(t) < self.vocab:
+                    # the reference checks ids on the host before its embedding kernel too (src/executable.cpp:54-72)
+                    raise ValueError(f"slot {e.slot}: token id {int(t)} outside the vocabulary of {self.vocab}")
+            for w in e.want:
+                if not 0 <= int(w) < n:
+                    raise ValueError(f"slot {e.slot}: wanted place {int(w)} outside the {n} tokens of this step")
+            new_len = self.cache.length[e.slot] + n
+            if new_len > self.cache.max_positions:
+                raise CacheError(f"slot {e.slot} would reach {new_len} tokens; the model's limit is {self.cache.max_positions}")
+            need[e.slot] = new_len
+        if not self.cache.can_hold(need):
+            raise CacheError("out of cache pages for this step: the live sequences and the new tokens exceed max_tokens")
+
+    def _cut(self, entries: Sequence[Entry]) -> List[List[Tuple[int, int, int]]]:
+        """Cut a step that brings more than max_step_tokens into pieces (entry, first, last+1), in order."""
+        chunks, cur, room = [], [], self.max_step_tokens
+        for i, e in enumerate(entries):
+            a, n = 0, len(e.tokens)
+            while a < n:
+                take = min(n - a, room)
+                cur.append((i, a, a + take))
+                a += take
+                room -= take
+                if room == 0:
+                    chunks.append(cur)
+                    cur, room = [], self.max_step_tokens
+        if cur:
+            chunks.append(cur)
+        return chunks
+
+    def _logits_buffer(self, rows: int) -> torch.Tensor:
+        cap = _bucket(rows)
+        if self._logits is None or self._logits.shape[0] < cap:
+            self._logits = None
+            self._logits = torch.empty((cap, self.vocab), dtype=torch.float32, device=self.device)
+        return self._logits
+
+    def _descriptors(self, T: int, B: int, R: int, widths: Sequence[int]) -> Descriptors:
+        key = (_bucket(T), _bucket(B, floor=1), _bucket(R), tuple(widths))
+        d = self._desc.get(key)
+        if d is None:
+            d = Descriptors(key[0], key[1], key[2], key[3], self.device)
+            self._desc[key] = d
+        return d
+
+    def _run_chunk(self, entries, chunk, logits, row0, produced) -> int:
+        cache = self.cache
+        B = len(chunk)
+        T = sum(b - a for _, a, b in chunk)
+        rows: List[int] = []
+        new_len: List[int] = []
+        for (i, a, b) in chunk:
+            e = entries[i]
+            cache.reserve(e.slot, cache.length[e.slot] + (b - a))
+        # widths of the block tables of this batch, per group (power of two, at most the table's width)
+        widths = []
+        for g in cache.groups:
+            need = max(1, max(g.blocks_end[entries[i].slot] for i, _, _ in chunk))
+            w = 1
+            while w < need:
+                w *= 2
+            widths.append(min(w, g.max_blocks))
+        wanted_here = []
+        for (i, a, b) in chunk:
+            for w in sorted(int(x) for x in entries[i].want):
+                if a <= w < b:
+                    wanted_here.append((i, w))
+        R = len(wanted_here)
+        desc = self._descriptors(T, B, R, widths)
+        desc.wait_reusable()
+        tok, pos, sot = desc.h("tokens"), desc.h("positions"), desc.h("seq_of_token")
+        cu, slots, ctx_len, lrows = desc.h("cu_tokens"), desc.h("slots"), desc.h("ctx_len"), desc.h("logit_rows")
+        t0 = 0
+        cu[0] = 0
+        start_of = {}
+        for s, (i, a, b) in enumerate(chunk):
+            e = entries[i]
+            n = b - a
+            base = cache.length[e.slot]
+            tok[t0: t0 + n] = np.asarray(e.tokens[a:b], dtype=np.int32)
+            pos[t0: t0 + n] = np.arange(base, base + n, dtype=np.int32)
+            sot[t0: t0 + n] = s
+            slots[s] = e.slot
+            ctx_len[s] = base + n
+            new_len.append(base + n)
+            start_of[i] = t0 - a
+            t0 += n
+            cu[s + 1] = t0
+        for r, (i, w) in enumerate(wanted_here):
+            lrows[r] = start_of[i] + w
+        for g, group in enumerate(cache.groups):
+            w = widths[g]
+            tab = desc.h(f"table{g}").reshape(desc.caps[1], w)
+            for s, (i, _, _) in enumerate(chunk):
+                tab[s, :] = group.block_table[entries[i].slot, :w]
+        desc.upload()
+
+        ctx = StepContext(self, desc, T, B, R, widths)
+        ctx.logits = logits[row0: row0 + R]
+        self.ws.begin((desc.caps[0], desc.caps[1], desc.caps[2]))
+        try:
+            self.model.forward(ctx)
+        except Exception:
+            self.ws.abort()
+            raise
+        self.ws.end()
+        for s, (i, a, b) in enumerate(chunk):
+            cache.commit(entries[i].slot, new_len[s])
+        produced.extend(wanted_here)
+        return R

@@ -1,0 +1,175 @@
+"""The device operations the parts are made of: thin checked wrappers over the CUDA launchers.
+
+Every function takes CUDA tensors and launches on torch's current stream.
+There is no other implementation: a tensor that is not on a CUDA device, or a
+missing kernel library, raises.  Activations are float32 or bfloat16 (one dtype
+per engine); the residual stream is always float32.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .library import KernelLibraryError, library
+
+F32, BF16 = 0, 1
+_CODES = {torch.float32: F32, torch.bfloat16: BF16}
+
+_c_int, _c_ll, _c_f, _c_p = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p
+
+launch_count = 0          # kernels launched through this module (the bench reports it)
+
+
+class KernelError(RuntimeError):
+    """A launcher refused its arguments or CUDA reported an error."""
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _CODES[t.dtype]
+    except KeyError:
+        raise KernelError(f"dtype {t.dtype} has no kernel (float32 and bfloat16 do)") from None
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    if t is None:
+        return _c_p(0)
+    if not t.is_cuda:
+        raise KernelError("this library runs on CUDA devices only; got a tensor on " + str(t.device))
+    return _c_p(t.data_ptr())
+
+
+def _stream():
+    return _c_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(status: int, name: str) -> None:
+    global launch_count
+    launch_count += 1
+    if status == 0:
+        return
+    if status == -1:
+        raise KernelError(f"{name}: this size or dtype is not supported by the kernel")
+    if status == -2:
+        raise KernelError(f"{name}: bad argument")
+    raise KernelError(f"{name}: CUDA error {status}")
+
+
+def _contig(t: torch.Tensor, name: str) -> torch.Tensor:
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    return t
+
+
+# ------------------------------------------------------------------------------------------------
+def embed_gather(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, err: Optional[torch.Tensor] = None) -> None:
+    """out[t, :] = table[tokens[t], :] as float32.  table [V, hid] float32|bfloat16, tokens int32 [T]."""
+    T, hid = out.shape
+    _check(library().vm_embed_gather(_ptr(_contig(table, "table")), _c_int(dtype_code(table)), _ptr(tokens), _ptr(out),
+                                     _c_int(T), _c_int(hid), _c_int(table.shape[0]), _ptr(err), _stream()), "embed_gather")
+
+
+def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float, out: torch.Tensor,
+                rows: Optional[torch.Tensor] = None) -> None:
+    """h += delta (if given), out = rmsnorm(h) * weight.  h float32 [T, hid]; delta/out of the activation dtype;
+    weight float32 [hid].  With `rows` (int32 [R]) only those rows are normed into out [R, hid] and h is not written."""
+    n_out, hid = out.shape
+    if weight.dtype != torch.float32 or h.dtype != torch.float32:
+        raise KernelError("add_rmsnorm: residual and norm weight are float32")
+    if delta is not None and delta.dtype != out.dtype:
+        raise KernelError("add_rmsnorm: delta and out must share the activation dtype")
+    _check(library().vm_add_rmsnorm(_ptr(h), _ptr(delta), _ptr(weight), _ptr(out), _ptr(rows), _c_int(n_out), _c_int(hid),
+                                    _c_f(eps), _c_int(dtype_code(out)), _stream()), "add_rmsnorm")
+
+
+def residual_add(h: torch.Tensor, delta: torch.Tensor) -> None:
+    """h += delta; h float32, delta of the activation dtype, same shape."""
+    _check(library().vm_residual_add(_ptr(h), _ptr(_contig(delta, "delta")), _c_ll(h.numel()), _c_int(dtype_code(delta)),
+                                     _stream()), "residual_add")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]; gate_up [T, 2I], out [T, I]."""
+    T, I = out.shape
+    _check(library().vm_swiglu(_ptr(_contig(gate_up, "gate_up")), _ptr(out), _c_int(T), _c_int(I), _c_int(dtype_code(out)),
+                               _stream()), "swiglu")
+
+
+def convert(src: torch.Tensor, out: torch.Tensor) -> None:
+    """out = src in out's dtype (float32 <-> bfloat16)."""
+    _check(library().vm_convert(_ptr(_contig(src, "src")), _c_int(dtype_code(src)), _ptr(out), _c_int(dtype_code(out)),
+                                _c_ll(src.numel()), _stream()), "convert")
+
+
+def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
+                  inv_freq: Optional[torch.Tensor], rot_dim: int, k_pages: Optional[torch.Tensor],
+                  v_pages: Optional[torch.Tensor], H: int, Hkv: int, D: int, err: Optional[torch.Tensor] = None) -> None:
+    """Rotate queries (in place) and keys of qkv [T, (H+2Hkv)*D]; write keys and values into the pages
+    k_pages/v_pages [n_pages, Hkv, 64, D] at block_table[seq, pos // 64] (int32 [B, max_blocks]).
+    With k_pages None only the queries are rotated (a run that reads another run's cache)."""
+    T = qkv.shape[0]
+    n_pages = k_pages.shape[0] if k_pages is not None else 0
+    _check(library().vm_rope_kv_write(_ptr(_contig(qkv, "qkv")), _ptr(positions), _ptr(seq_of_token), _ptr(block_table),
+                                      _c_int(block_table.shape[1]), _ptr(inv_freq), _c_int(rot_dim), _ptr(k_pages),
+                                      _ptr(v_pages), _c_int(T), _c_int(H), _c_int(Hkv), _c_int(D),
+                                      _c_int(n_pages), _c_int(dtype_code(qkv)), _ptr(err), _stream()), "rope_kv_write")
+
+
+def attention_generic(q: torch.Tensor, q_row_stride: int, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                      block_table: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, out: torch.Tensor,
+                      H: int, Hkv: int, D: int, scale: float, window: int = 0, err: Optional[torch.Tensor] = None) -> None:
+    """out[t, h*D:(h+1)*D] = attention of query (t, h) over its sequence's cached keys at positions
+    max(0, pos-window+1)..pos (window 0: all).  q may be a view into qkv with row stride q_row_stride."""
+    T = out.shape[0]
+    _check(library().vm_attention_generic(_ptr(q), _c_int(q_row_stride), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+                                          _c_int(block_table.shape[1]), _ptr(positions), _ptr(seq_of_token), _ptr(out),
+                                          _c_int(T), _c_int(H), _c_int(Hkv), _c_int(D), _c_f(scale), _c_int(window),
+                                          _c_int(k_pages.shape[0]), _c_int(dtype_code(out)), _ptr(err), _stream()),
+           "attention_generic")
+
+
+def attention(ctx, q: torch.Tensor, q_row_stride: int, k_pages: torch.Tensor, v_pages: torch.Tensor,
+              block_table: torch.Tensor, out: torch.Tensor, H: int, Hkv: int, D: int, scale: float, window: int = 0) -> None:
+    """Attention of the step's tokens over the cache; picks the kernel for the step's shape and dtype."""
+    attention_generic(q, q_row_stride, k_pages, v_pages, block_table, ctx.positions, ctx.seq_of_token, out,
+                      H, Hkv, D, scale, window, ctx.err)
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x @ weight^T.  x [T, K], weight [N, K] (the checkpoint's [out, in] layout), out [T, N].
+    A library matrix product, as in the reference (src/cuda/ops/matmul.cu:87-96); float32 runs without
+    any reduced-precision mode."""
+    if not x.is_cuda:
+        raise KernelError("this library runs on CUDA devices only; got a tensor on " + str(x.device))
+    global launch_count
+    launch_count += 1
+    if x.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
+        raise KernelError("float32 matrix products must not use TF32; torch.backends.cuda.matmul.allow_tf32 is set")
+    if out.dtype == x.dtype:
+        torch.mm(x, weight.t(), out=out)
+    else:
+        torch.mm(x, weight.t(), out_dtype=out.dtype, out=out)
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor, seed: torch.Tensor,
+           stream_id: torch.Tensor, step: torch.Tensor, out: torch.Tensor) -> None:
+    """One token per row of logits float32 [R, V]: greedy where temperature <= 0 or top_p <= 0, else
+    temperature / nucleus sampling with a Philox draw keyed by (seed; stream_id, step) (all int64 [R])."""
+    R, V = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("sample: logits are float32 rows")
+    _check(library().vm_sample(_ptr(logits), _c_ll(logits.stride(0)), _c_int(R), _c_int(V), _ptr(temperature), _ptr(top_p),
+                               _ptr(seed), _ptr(stream_id), _ptr(step), _ptr(out), _stream()), "sample")
+
+
+def require_cuda(device) -> torch.device:
+    """The device an engine may run on, or a loud refusal."""
+    dev = torch.device(device)
+    if dev.type != "cuda":
+        raise KernelLibraryError(f"device {dev} refused: this library has CUDA kernels only and no CPU fallback")
+    if not torch.cuda.is_available():
+        raise KernelLibraryError("no CUDA device is available; this library has no CPU fallback")
+    library()
+    return dev

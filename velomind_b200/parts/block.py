@@ -1,0 +1,37 @@
+"""Arrangements: how a layer wires its norms, mixer, feed-forward and the residual stream."""
+from __future__ import annotations
+
+from .registry import register_part
+
+
+class PreNormBlock:
+    """h += mixer(norm(h)); h += feed_forward(norm(h))  (examples/common/llama/llama_graph.cpp:203-229).
+
+    The residual stream h is float32.  Each sum is carried out by the norm kernel that follows it, so
+    `forward` takes the delta the previous layer left pending and returns its own last delta pending.
+    """
+
+    def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm):
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+
+    def parts(self):
+        return {"mixer": self.mixer, "feed_forward": self.feed_forward, "mixer_norm": self.mixer_norm,
+                "feed_forward_norm": self.feed_forward_norm}
+
+    def forward(self, ctx, h, pending):
+        hid = h.shape[1]
+        x = ctx.take_tokens(hid, ctx.act_dtype)
+        self.mixer_norm.forward(ctx, h, pending, x)
+        ctx.ws.give(pending)
+        mixed = ctx.take_tokens(hid, ctx.act_dtype)
+        self.mixer.forward(ctx, x, mixed)
+        self.feed_forward_norm.forward(ctx, h, mixed, x)
+        ctx.ws.give(mixed)
+        out = ctx.take_tokens(hid, ctx.act_dtype)
+        self.feed_forward.forward(ctx, x, out)
+        ctx.ws.give(x)
+        return out
+
+
+register_part("arrangement", "prenorm", PreNormBlock)

@@ -1,0 +1,77 @@
+"""Sampling parameters and the device sampler.
+
+Option names and defaults follow the reference's command line
+(examples/smollm2/interactive_main.cpp:23-25,39-41): `--temp` 0.7 (0 or less:
+greedy), `--top-p` 0.9 (0 or less: greedy), `--max-tokens` 32; its fixed seed is
+42 (:113).  The rule itself is in csrc/sampling.cu.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..kernels import ops
+
+
+def _host_buffer(shape, dtype: torch.dtype) -> torch.Tensor:
+    return torch.empty(shape, dtype=dtype, pin_memory=True)
+
+
+def _sync() -> None:
+    torch.cuda.current_stream().synchronize()
+
+
+@dataclass(frozen=True)
+class SamplingParams:
+    temperature: float = 0.7
+    top_p: float = 0.9
+    max_tokens: int = 32
+    seed: int = 42
+    stop_tokens: Tuple[int, ...] = ()
+
+    @property
+    def greedy(self) -> bool:
+        return self.temperature <= 0 or self.top_p <= 0
+
+
+class DeviceSampler:
+    """Draws one token per row of logits on the device.  A row's draw depends on (seed, stream, step) of
+    its request only, never on the rest of the batch."""
+
+    FIELDS = 5   # temperature, top_p (float32 bit patterns in an int64 lane), seed, stream, step
+
+    def __init__(self, device, max_rows: int = 64):
+        self.device = torch.device(device)
+        self._alloc(max_rows)
+
+    def _alloc(self, rows: int) -> None:
+        self.rows = rows
+        self.host_f = _host_buffer((2, rows), torch.float32)
+        self.host_i = _host_buffer((3, rows), torch.int64)
+        self.dev_f = torch.empty((2, rows), dtype=torch.float32, device=self.device)
+        self.dev_i = torch.empty((3, rows), dtype=torch.int64, device=self.device)
+        self.out = torch.empty(rows, dtype=torch.int32, device=self.device)
+        self.out_host = _host_buffer((rows,), torch.int32)
+
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], streams: Sequence[int],
+               steps: Sequence[int]) -> np.ndarray:
+        """Tokens (host int32 array) for logits [R, V]; row r uses params[r] and the Philox counter
+        (steps[r], streams[r])."""
+        R = logits.shape[0]
+        if R == 0:
+            return np.zeros(0, dtype=np.int32)
+        if R > self.rows:
+            self._alloc(max(R, 2 * self.rows))
+        hf, hi = self.host_f.numpy(), self.host_i.numpy()
+        for r, p in enumerate(params):
+            hf[0, r], hf[1, r] = p.temperature, p.top_p
+            hi[0, r], hi[1, r], hi[2, r] = p.seed, streams[r], steps[r]
+        self.dev_f.copy_(self.host_f, non_blocking=True)
+        self.dev_i.copy_(self.host_i, non_blocking=True)
+        ops.sample(logits, self.dev_f[0], self.dev_f[1], self.dev_i[0], self.dev_i[1], self.dev_i[2], self.out)
+        self.out_host.copy_(self.out, non_blocking=True)
+        _sync()
+        return self.out_host.numpy()[:R].copy()
