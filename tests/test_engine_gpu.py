@@ -1,0 +1,139 @@
+"""The engine against the plain implementation on a GPU: every way of cutting requests into steps, in
+float32 and in bfloat16, on the two tiny configurations."""
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as P
+import schedules as S
+from tiny_configs import TINY_A, TINY_B
+
+pytestmark = pytest.mark.gpu
+
+# float32: the reference's own bound between its cached and stateless paths is 1e-4 on the CPU and 1e-3 on
+# CUDA (tests/test_smollm2_e2e.cpp:306,338; tests/test_interactive.cpp:337,354); logits here are ~1.
+TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+LENGTHS = (5, 9, 2, 70, 130, 64, 65, 200, 33, 1)
+CONFIGS = {"tiny_a": TINY_A, "tiny_b": TINY_B}
+
+
+def _engine(folder, dtype, max_tokens=2048, **kw):
+    import velomind_b200 as vm
+    model = vm.load_model(folder, {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype], "cuda:0")
+    return vm.Engine(model, max_tokens, **kw)
+
+
+def _compare(got, want, tol):
+    assert set(got) == set(want)
+    worst = 0.0
+    for step in want:
+        assert got[step].shape == want[step].shape, step
+        assert np.isfinite(got[step]).all(), step
+        worst = max(worst, float(np.abs(got[step] - want[step]).max()))
+    assert worst <= tol, f"max |logit - plain| = {worst:.3e} > {tol}"
+    return worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+@pytest.mark.parametrize("cut", ["whole", "tail", "batches"])
+def test_cuts_match_plain(model_folders, name, dtype, cut):
+    folder = model_folders[name]
+    requests = S.make_requests(CONFIGS[name]["vocab_size"], LENGTHS, seed=3)
+    plain = S.plain_logits(folder, requests)
+    steps = {"whole": S.steps_whole, "tail": S.steps_tail_one_by_one, "batches": S.steps_unequal_batches}[cut](requests)
+    # a cache just large enough for one batch, so that pages and slots are used again and again
+    engine = _engine(folder, dtype, max_tokens=64 * 8, max_slots=3)
+    got = S.run_steps_in_process(engine, steps)
+    _compare(got, S.expected_rows(steps, requests, plain), TOL[dtype])
+    assert engine.cache.slots.held_count == 0 and engine.cache.tokens_held() == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(model_folders, dtype):
+    """300 tokens one by one from a 3-token prompt: crosses several pages; compared at every position."""
+    folder = model_folders["tiny_b"]
+    requests = S.make_requests(TINY_B["vocab_size"], (303,), seed=5)
+    plain = S.plain_logits(folder, requests)
+    steps = S.steps_tail_one_by_one(requests, tail=300)
+    got = S.run_steps_in_process(_engine(folder, dtype), steps)
+    _compare(got, S.expected_rows(steps, requests, plain), TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens(model_folders, dtype):
+    """A sequence fed one token at a time from its very first token, next to one that starts whole."""
+    folder = model_folders["tiny_a"]
+    requests = S.make_requests(TINY_A["vocab_size"], (6, 6), seed=7)
+    plain = S.plain_logits(folder, requests)
+    a, b = requests["r0"], requests["r1"]
+    steps = [{"step": 0, "entries": [{"id": "r0", "tokens": a[:1], "want": [0]}, {"id": "r1", "tokens": b, "want": [5, 0]}], "end": ["r1"]}]
+    for j in range(1, 6):
+        steps.append({"step": j, "entries": [{"id": "r0", "tokens": [a[j]], "want": [0]}], "end": ["r0"] if j == 5 else []})
+    got = S.run_steps_in_process(_engine(folder, dtype), steps)
+    _compare(got, S.expected_rows(steps, requests, plain), TOL[dtype])
+
+
+def test_padding_and_company_change_nothing(model_folders):
+    """float32: a request's logits are the same alone, in a batch, and cut into pieces (beyond rounding)."""
+    folder = model_folders["tiny_b"]
+    requests = S.make_requests(TINY_B["vocab_size"], (90, 17, 150), seed=11)
+    engine = _engine(folder, "float32")
+    alone = S.run_steps_in_process(engine, S.steps_whole(requests))
+    toks = requests["r0"]
+    steps = [
+        {"step": 0, "entries": [{"id": "r0", "tokens": toks[:50], "want": list(range(50))},
+                                {"id": "r2", "tokens": requests["r2"], "want": []}], "end": []},
+        {"step": 1, "entries": [{"id": "r0", "tokens": toks[50:], "want": list(range(40))},
+                                {"id": "r1", "tokens": requests["r1"], "want": [16]}], "end": ["r0", "r1", "r2"]},
+    ]
+    got = S.run_steps_in_process(engine, steps)
+    cut = np.concatenate([got[0], got[1][:40]])
+    assert np.abs(cut - alone[0]).max() <= 2e-6
+
+
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_greedy_generation_entry_point(model_folders, name):
+    import velomind_b200 as vm
+    folder = model_folders[name]
+    cfg, w = P.read_model(folder)
+    prompts = [[5, 9, 2, 77, 1], [3, 4], list(range(10, 19)), [200] * 7]
+    want = [P.generate(cfg, w, p, 8) for p in prompts]
+    eng = vm.load(folder, dtype="float32", max_tokens=1024)
+    got = eng.generate(prompts, temperature=0.0, max_tokens=8, stop_tokens=())
+    assert [r.tokens for r in got] == want
+    assert all(r.finish_reason == "length" for r in got)
+    # bfloat16 runs the same path; tokens may differ where two logits are close, so only shapes are checked
+    eng16 = vm.load(folder, dtype="bfloat16", max_tokens=1024)
+    got16 = eng16.generate(prompts, temperature=0.0, max_tokens=8, stop_tokens=())
+    assert [len(r.tokens) for r in got16] == [8] * 4
+
+
+def test_sampled_generation_matches_plain(model_folders):
+    """Temperature 0.8 with a fixed seed: the device sampler and the plain sampler draw the same tokens."""
+    import velomind_b200 as vm
+    folder = model_folders["tiny_b"]
+    cfg, w = P.read_model(folder)
+    prompts = [[1, 2, 3, 4, 5, 6, 7], [9, 8, 7, 6]]
+    want = [P.generate(cfg, w, p, 6, temperature=0.8, top_p=1.0, seed=1234, stream=i) for i, p in enumerate(prompts)]
+    want_p = [P.generate(cfg, w, p, 6, temperature=0.8, top_p=0.9, seed=99, stream=i) for i, p in enumerate(prompts)]
+    eng = vm.load(folder, dtype="float32", max_tokens=1024)
+    got = eng.generate(prompts, temperature=0.8, top_p=1.0, max_tokens=6, seed=1234, stop_tokens=())
+    assert [r.tokens for r in got] == want
+    got_p = eng.generate(prompts, temperature=0.8, top_p=0.9, max_tokens=6, seed=99, stop_tokens=())
+    assert [r.tokens for r in got_p] == want_p
+
+
+def test_stop_token_ends_a_sequence_early(model_folders):
+    import velomind_b200 as vm
+    folder = model_folders["tiny_a"]
+    cfg, w = P.read_model(folder)
+    prompts = [[5, 9, 2, 77, 1], [3, 4]]
+    free = [P.generate(cfg, w, p, 8) for p in prompts]
+    stop = free[0][2]
+    want = [P.generate(cfg, w, p, 8, stop=(stop,)) for p in prompts]
+    eng = vm.load(folder, dtype="float32", max_tokens=1024)
+    got = eng.generate(prompts, temperature=0.0, max_tokens=8, stop_tokens=(stop,))
+    assert [r.tokens for r in got] == want
+    assert got[0].finish_reason == "stop" and got[0].tokens[-1] == stop
+    assert eng.engine.cache.slots.held_count == 0
