@@ -1,0 +1,261 @@
+"""Decode and prefill throughput of the library on one B200, at the sizes of SmolLM2-135M with random weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  `value` is decoded tokens per second at batch 8 (prompts of 512 tokens, cache sized
+for context 4096), timed on the device with CUDA events over exactly K decode steps, each of which runs
+the step function and the device sampler and hands the tokens to the host.  `e2e` is the same through
+`TextEngine.generate` (host token ids in, host token ids out, wall clock of its decode steps).  `prefill`
+is one prompt of 2,048 tokens; `points` holds decode at batch 1 and 64; `roofline` compares the decode
+step with the bytes it has to read.  The reference publishes no number (`vs_baseline` is null) and cannot
+be installed as a Python package, so `--impl reference` reports itself unavailable.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    out = dict(FALLBACK_PEAKS)
+    src = "fallback"
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                data = json.load(f)
+            for k in out:
+                if isinstance(data.get(k), (int, float)) and data[k] > 0:
+                    out[k] = float(data[k])
+                    src = "measured"
+        except (OSError, ValueError):
+            pass
+    out["source"] = src
+    return out
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def model_bytes_and_flops(cfg, layers):
+    hid, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    H, Hkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    D = hid // H
+    per_layer = hid * (H + 2 * Hkv) * D + H * D * hid + 3 * hid * I       # matrix elements of one layer
+    norms = (2 * layers + 1) * hid
+    weight_bytes = 2 * (per_layer * layers + V * hid) + 4 * norms          # bf16 matrices (tied head read once), f32 norms
+    kv_bytes_per_token = 2 * Hkv * D * 2 * layers
+    return per_layer, weight_bytes, kv_bytes_per_token, D
+
+
+def decode_run(text_engine, B, prompt_len, steps, warmup, vocab, clock=None):
+    """K timed decode steps at batch B; returns (ms per step, mean context, own-kernel launches, library calls)."""
+    import numpy as np
+    import torch
+    from velomind_b200 import Entry, SamplingParams
+    from velomind_b200.kernels import ops
+    eng, sampler = text_engine.engine, text_engine.sampler
+    rng = np.random.default_rng(B)
+    slots = [eng.open() for _ in range(B)]
+    params = [SamplingParams(temperature=0.0)] * B
+    streams = list(range(B))
+    logits = eng.step([Entry(s, rng.integers(0, vocab, prompt_len).tolist(), [prompt_len - 1]) for s in slots])
+    toks = sampler.sample(logits, params, streams, [0] * B)
+
+    def one(i):
+        nonlocal toks
+        logits = eng.step([Entry(s, [int(t)], [0]) for s, t in zip(slots, toks)])
+        toks = sampler.sample(logits, params, streams, [i] * B)
+
+    for i in range(warmup):
+        one(i)
+    torch.cuda.synchronize()
+    ctx0 = eng.length(slots[0])
+    l0, c0 = ops.launch_count, ops.library_calls
+    if clock:
+        clock.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for i in range(steps):
+        one(warmup + i)
+    ev1.record()
+    torch.cuda.synchronize()
+    clocks = clock.stop() if clock else None
+    ms = ev0.elapsed_time(ev1) / steps
+    launches, calls = ops.launch_count - l0, ops.library_calls - c0
+    mean_ctx = ctx0 + (steps + 1) / 2.0
+    for s in slots:
+        eng.close(s)
+    eng.raise_if_error()
+    return ms, mean_ctx, launches, calls, clocks
+
+
+def prefill_run(text_engine, T, vocab, repeats=5):
+    import numpy as np
+    import torch
+    from velomind_b200 import Entry
+    eng = text_engine.engine
+    rng = np.random.default_rng(7)
+    times = []
+    for r in range(repeats + 2):
+        toks = rng.integers(0, vocab, T).tolist()
+        slot = eng.open()
+        entries = [Entry(slot, toks, [T - 1])]
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        eng.step(entries)
+        ev1.record()
+        torch.cuda.synchronize()
+        eng.close(slot)
+        if r >= 2:
+            times.append(ev0.elapsed_time(ev1))
+    eng.raise_if_error()
+    return statistics.median(times)
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0: all); reported in config")
+    ap.add_argument("--quick", action="store_true", help="skip the batch 1 / 64 points and the end-to-end run")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a C++/CMake project without setup.py or pyproject.toml: pip cannot install it offline"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures a single-GPU library: --gpus {args.gpus} is not supported, run with --gpus 1")
+        return 2
+    warmup = max(args.warmup, 3)
+
+    import torch
+    import velomind_b200 as vm
+    from velomind_b200.kernels import ops
+
+    cfg = dict(vm.SMOLLM2_135M)
+    full_layers = cfg["num_hidden_layers"]
+    layers = args.layers or full_layers
+    cfg["num_hidden_layers"] = layers
+    vocab = cfg["vocab_size"]
+    B, prompt_len, context = 8, 512, 4096
+    pk = peaks()
+
+    with tempfile.TemporaryDirectory(prefix="velomind_bench_") as folder:
+        vm.write_random_model(folder, cfg, seed=0, std=0.02)
+        te = vm.TextEngine(vm.EngineConfig(model_path=folder, dtype="bfloat16", max_tokens=64 * context, max_batch=64)).load()
+
+    per_layer, weight_bytes, kv_per_token, D = model_bytes_and_flops(cfg, layers)
+
+    clock = ClockSampler()
+    ms, mean_ctx, launches, calls, clocks = decode_run(te, B, prompt_len, args.steps, warmup, vocab, clock)
+    value = B * 1000.0 / ms
+    step_bytes = weight_bytes + kv_per_token * mean_ctx * B
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+
+    # prefill of 2,048 tokens: linears + causal attention + the head on one row
+    T = 2048
+    pms = prefill_run(te, T, vocab)
+    H = cfg["num_attention_heads"]
+    flops = 2.0 * T * per_layer * layers + 4.0 * D * H * (T * (T + 1) / 2.0) * layers + 2.0 * vocab * cfg["hidden_size"]
+    prefill = {"value": T * 1000.0 / pms, "tokens": T, "ms": pms, "frac": flops / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12)}
+
+    points, e2e = {}, None
+    if not args.quick:
+        for b in (1, 64):
+            m, _, _, _, _ = decode_run(te, b, prompt_len, args.steps, warmup, vocab)
+            points[f"decode_b{b}"] = b * 1000.0 / m
+        # end to end through the public entry point: host token ids in, host token ids out
+        import numpy as np
+        rng = np.random.default_rng(1)
+        prompts = [rng.integers(0, vocab, prompt_len).tolist() for _ in range(B)]
+        te.generate(prompts, temperature=0.0, max_tokens=warmup + 1, stop_tokens=())
+        te.generate(prompts, temperature=0.0, max_tokens=args.steps + 1, stop_tokens=())
+        tm = te.last_timing
+        e2e = {"value": B * tm.decode_steps / tm.decode_seconds, "unit": "tokens/s",
+               "h2d_bytes_per_step": 4 * min(d.total for k, d in te.engine._desc.items() if k[0] == 8 and k[1] == 8)
+               + te.sampler.rows * (2 * 4 + 3 * 8),
+               "d2h_bytes_per_step": 4 * B}
+
+    line = {
+        "metric": "decode tok/s at batch 8 (SmolLM2-135M shape, prompts of 512 tokens)",
+        "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"model": "SmolLM2-135M shape, random weights", "global_batch": B, "seq_len": prompt_len,
+                   "context": context, "parallelism": "single GPU", "layers": layers, "layers_of_config": full_layers,
+                   "hidden": cfg["hidden_size"], "heads": H, "kv_heads": cfg["num_key_value_heads"], "head_dim": D,
+                   "intermediate": cfg["intermediate_size"], "vocab": vocab, "rope_theta": cfg["rope_theta"],
+                   "rms_eps": cfg["rms_norm_eps"], "tied": True, "sampling": "greedy on device",
+                   "l2": "inputs larger than L2 (weights + cache > 126 MB)", "peaks": pk["source"]},
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"]},
+        "points": points,
+        "clocks": clocks,
+        "gpu_launches": launches,
+        "library_gemm_calls": calls,
+    }
+    if e2e is not None:
+        line["e2e"] = e2e
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

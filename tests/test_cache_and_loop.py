@@ -1,0 +1,287 @@
+"""The cache's bookkeeping, the activation arena, the step function's host side (with the kernels replaced by
+CPU stand-ins) and the generation loop's decisions."""
+import random
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as P
+import schedules as S
+from tiny_configs import TINY_A, TINY_B
+from velomind_b200.cache import PAGE_TOKENS, CacheError, CacheNeed, FreeList, SequenceCache
+from velomind_b200.engine.arena import Workspace, plan_arena
+from velomind_b200.engine.generate import GenerationLoop, Request, pages_for, plan_batches
+from velomind_b200.sampling import SamplingParams
+
+
+# ------------------------------------------------------------------------------------------ free list
+def test_free_list_never_loses_or_doubles():
+    fl = FreeList(5, "thing")
+    got = [fl.take() for _ in range(5)]
+    assert got == [0, 1, 2, 3, 4] and fl.free_count == 0
+    with pytest.raises(CacheError, match="out of things"):
+        fl.take()
+    fl.give(3); fl.give(1)
+    with pytest.raises(CacheError, match="freed twice"):
+        fl.give(3)
+    with pytest.raises(CacheError, match="does not exist"):
+        fl.give(9)
+    assert fl.take() == 1 and fl.take() == 3          # lowest first: what a batch gave back is used again
+    fl.check()
+    rnd = random.Random(0)
+    held = set(range(5))
+    for _ in range(2000):
+        if held and rnd.random() < 0.5:
+            i = rnd.choice(sorted(held)); held.remove(i); fl.give(i)
+        elif len(held) < 5:
+            i = fl.take(); assert i not in held; held.add(i)
+        fl.check()
+        assert fl.held_count == len(held)
+
+
+def _cache(needs, max_tokens=64 * 8, shares=None, **kw):
+    shares = shares or [None] * len(needs)
+    return SequenceCache(needs, shares, max_tokens, 1024, torch.float32, "cpu", **kw)
+
+
+def test_slots_and_pages_come_back():
+    need = CacheNeed("all", 2, 16)
+    c = _cache([need, need], max_slots=3)
+    assert len(c.groups) == 1 and c.groups[0].k.shape == (2, 8, 2, PAGE_TOKENS, 16)
+    a, b = c.open(), c.open()
+    c.reserve(a, 65); c.commit(a, 65)
+    c.reserve(b, 64); c.commit(b, 64)
+    assert c.groups[0].pages.held_count == 3 and c.tokens_held() == 192
+    c.reserve(a, 66); c.commit(a, 66)                          # same page
+    assert c.groups[0].pages.held_count == 3
+    c.check()
+    with pytest.raises(CacheError, match="out of cache pages"):
+        c.reserve(b, 64 * 7)
+    assert c.groups[0].pages.held_count == 3                   # a refused reservation changes nothing
+    c.close(a)
+    with pytest.raises(CacheError, match="not open"):
+        c.close(a)
+    with pytest.raises(CacheError, match="not open"):
+        c.reserve(a, 1)
+    assert c.groups[0].pages.held_count == 1
+    a2 = c.open()
+    assert a2 == a and c.length[a2] == 0                        # the slot is used again, empty
+    c.reserve(a2, 1)
+    assert int(c.groups[0].block_table[a2, 0]) in (0, 1)       # and so are its pages
+    c.close(a2); c.close(b)
+    c.check()
+    assert c.slots.held_count == 0 and c.tokens_held() == 0
+    with pytest.raises(CacheError, match="model's limit"):
+        s = c.open(); c.reserve(s, 2000)
+
+
+def test_groups_with_different_needs_have_their_own_storage():
+    full, win = CacheNeed("all", 2, 16), CacheNeed("window", 1, 32, window=70)
+    c = _cache([full, win, full, None, CacheNeed("none", state_floats=5)], shares=[None, None, None, 1, None], max_tokens=64 * 16)
+    assert len(c.groups) == 2
+    assert c.where(0) == (0, 0) and c.where(2) == (0, 1) and c.where(1) == (1, 0) and c.where(3) == (1, 0) and c.where(4) is None
+    assert c.groups[0].k.shape[2:] == (2, 64, 16) and c.groups[1].k.shape[2:] == (1, 64, 32)
+    assert c.state[4].shape == (c.max_slots, 5) and c.state[0] is None
+    s = c.open()
+    c.state[4][s] = 7.0
+    c.reserve(s, 300); c.commit(s, 300)
+    assert c.groups[0].pages.held_count == 5
+    # window 70: the next query (position 300) sees keys 231..300, so blocks 0..2 (keys < 192) are gone
+    assert c.groups[1].pages.held_count == 2 and c.groups[1].blocks_begin[s] == 3
+    assert list(c.groups[1].block_table[s, :3]) == [-1, -1, -1]
+    c.check()
+    c.close(s)
+    s2 = c.open()
+    assert s2 == s and float(c.state[4][s2].abs().sum()) == 0.0    # state is cleared for the next sequence
+    c.close(s2)
+    c.check()
+
+
+# ------------------------------------------------------------------------------------------ arena
+def test_arena_plan_packs_by_liveness():
+    # a and b overlap in time, c lives after a died: c reuses a's bytes
+    plan = plan_arena([(1000, 1, 4), (500, 2, 6), (900, 5, 8)])
+    assert plan.peak_bytes == 1024 + 512 and plan.buffer_count == 3 and plan.reused_count >= 1
+    for i, (oi, si) in enumerate(zip(plan.offsets, plan.sizes)):
+        assert oi % 256 == 0
+    ivs = [(int(random.Random(i).randrange(1, 5000)), i, i + random.Random(i + 7).randrange(0, 6)) for i in range(40)]
+    plan = plan_arena(ivs)
+    for i in range(40):
+        for j in range(i):
+            overlap_t = not (ivs[i][2] < ivs[j][1] or ivs[j][2] < ivs[i][1])
+            overlap_m = plan.offsets[i] < plan.offsets[j] + plan.sizes[j] and plan.offsets[j] < plan.offsets[i] + plan.sizes[i]
+            assert not (overlap_t and overlap_m)
+    assert plan.bytes_saved == sum(plan.sizes) - plan.peak_bytes > 0
+
+
+def test_workspace_records_then_replays():
+    ws = Workspace("cpu")
+    for round_ in range(3):
+        ws.begin("k")
+        a = ws.take((10, 8), torch.float32); b = ws.take((4,), torch.bfloat16)
+        ws.give(a)
+        c = ws.take((10, 8), torch.float32)
+        if round_:
+            assert c.data_ptr() == a.data_ptr()              # planned: c lies where a lay
+            assert a.data_ptr() >= ws.arena.data_ptr()
+        ws.give(b); ws.give(c)
+        with pytest.raises(RuntimeError, match="given twice"):
+            ws.give(c)
+        ws.end()
+    assert ws.plans["k"].buffer_count == 3 and ws.generation == 1
+    ws.begin("k")
+    with pytest.raises(RuntimeError, match="other buffers"):
+        ws.take((100, 8), torch.float32)
+    ws.abort()
+
+
+# ------------------------------------------------------------------------------------------ step function, host side
+@pytest.mark.parametrize("name,cfg", [("tiny_a", TINY_A), ("tiny_b", TINY_B)])
+def test_step_function_with_stand_in_kernels(emulated, model_folders, name, cfg):
+    import velomind_b200 as vm
+    folder = model_folders[name]
+    requests = S.make_requests(cfg["vocab_size"], (5, 70, 2, 130, 65, 1), seed=2)
+    plain = S.plain_logits(folder, requests)
+    model = vm.load_model(folder, torch.float32, "cpu")
+    for cut in (S.steps_whole, S.steps_tail_one_by_one, S.steps_unequal_batches):
+        engine = vm.Engine(model, 64 * 6, max_slots=3, max_step_tokens=100)    # 130-token prompts are cut in two
+        steps = cut(requests) if cut is not S.steps_tail_one_by_one else cut(requests, tail=4)
+        got = S.run_steps_in_process(engine, steps)
+        want = S.expected_rows(steps, requests, plain)
+        assert set(got) == set(want)
+        assert max(float(np.abs(got[k] - want[k]).max()) for k in want) < 5e-6
+        assert engine.cache.slots.held_count == 0 and engine.cache.tokens_held() == 0
+
+
+def test_step_refusals(emulated, model_folders):
+    import velomind_b200 as vm
+    model = vm.load_model(model_folders["tiny_a"], torch.float32, "cpu")
+    engine = vm.Engine(model, 128, max_slots=2)
+    s = engine.open()
+    with pytest.raises(ValueError, match="outside the vocabulary"):
+        engine.step([vm.Entry(s, [1, 256], [0])])
+    with pytest.raises(ValueError, match="wanted place 2"):
+        engine.step([vm.Entry(s, [1, 2], [2])])
+    with pytest.raises(ValueError, match="twice"):
+        engine.step([vm.Entry(s, [1], []), vm.Entry(s, [2], [])])
+    with pytest.raises(CacheError, match="not open"):
+        engine.step([vm.Entry(1, [1], [])])
+    with pytest.raises(CacheError, match="max_tokens"):
+        engine.step([vm.Entry(s, [1] * 129, [])])
+    assert engine.length(s) == 0
+    out = engine.step([vm.Entry(s, [1, 2, 3], [2, 0])])            # wanted places keep their order
+    ref = P.forward_logits(*P.read_model(model_folders["tiny_a"]), [1, 2, 3])
+    assert np.abs(out.numpy() - ref[[2, 0]]).max() < 5e-6
+    with pytest.raises(CacheError, match="model's limit"):
+        engine.step([vm.Entry(s, [1] * 600, [])])
+    engine.close(s)
+
+
+# ------------------------------------------------------------------------------------------ generation loop
+class FakeStepper:
+    """Logits that make the next token = (last token + 1) % vocab; records what it is asked to do."""
+
+    def __init__(self, vocab=50, slots=4):
+        self.vocab, self.free, self.open_slots, self.log, self.closed = vocab, list(range(slots)), set(), [], []
+
+    def open(self):
+        s = min(self.free); self.free.remove(s); self.open_slots.add(s); return s
+
+    def close(self, slot):
+        assert slot in self.open_slots, "closed twice"
+        self.open_slots.remove(slot); self.free.append(slot); self.closed.append(slot)
+
+    def step(self, entries):
+        self.log.append([(e.slot, list(e.tokens)) for e in entries])
+        out = torch.full((len(entries), self.vocab), -1.0)
+        for r, e in enumerate(entries):
+            assert e.slot in self.open_slots and list(e.want) == [len(e.tokens) - 1]
+            out[r, (e.tokens[-1] + 1) % self.vocab] = 1.0
+        return out
+
+
+class GreedyHostSampler:
+    def sample(self, logits, params, streams, steps):
+        self.last = (list(streams), list(steps))
+        return logits.argmax(-1).numpy()
+
+
+def test_loop_unequal_prompts_stop_tokens_and_early_ends():
+    st, sm = FakeStepper(), GreedyHostSampler()
+    loop = GenerationLoop(st, sm, total_pages=100, max_batch=4, default_stop=(13,))
+    reqs = [Request([1, 2, 3], SamplingParams(0.0, 0.9, 5)), Request([10], SamplingParams(0.0, 0.9, 9)),
+            Request([40, 41], SamplingParams(0.0, 0.9, 2)), Request([7], SamplingParams(0.0, 0.9, 0)),
+            Request([], SamplingParams(0.0, 0.9, 4))]
+    seen = []
+    res = loop.run(reqs, on_token=lambda i, t: seen.append((i, t)))
+    assert res[0].tokens == [4, 5, 6, 7, 8] and res[0].finish_reason == "length"
+    assert res[1].tokens == [11, 12, 13] and res[1].finish_reason == "stop"        # the stop token is kept, not fed
+    assert res[2].tokens == [42, 43] and res[2].finish_reason == "length"
+    assert res[3].tokens == [] and res[3].finish_reason == "length"               # max_tokens 0: nothing to do
+    assert res[4].finish_reason == "empty"
+    assert st.log[0] == [(0, [1, 2, 3]), (1, [10]), (2, [40, 41])]                # prompts whole, in one step
+    assert st.log[1] == [(0, [4]), (1, [11]), (2, [42])]                          # then one token each
+    assert st.log[2] == [(0, [5]), (1, [12])]                                     # request 2 ended earlier
+    assert st.log[3] == [(0, [6])] and len(st.log) == 5                           # 13 was never fed
+    assert not st.open_slots and sorted(st.closed) == [0, 1, 2]
+    assert [t for i, t in seen if i == 1] == [11, 12, 13]
+    assert loop.timing.generated_tokens == 10 and loop.timing.decode_steps == 4
+    assert res[0].prompt_tokens == 3
+
+
+def test_loop_runs_batch_after_batch_and_reuses_slots():
+    st, sm = FakeStepper(slots=2), GreedyHostSampler()
+    loop = GenerationLoop(st, sm, total_pages=100, max_batch=2)
+    reqs = [Request([i], SamplingParams(0.0, 0.9, 2 + i), stream=i) for i in range(5)]
+    res = loop.run(reqs)
+    assert [r.tokens for r in res] == [[i + 1 + k for k in range(2 + i)] for i in range(5)]
+    assert st.closed == [0, 1, 0, 1, 0] or sorted(st.closed) == [0, 0, 0, 1, 1]
+    assert [e[0] for e in st.log[0]] == [0, 1] and not st.open_slots
+    assert sm.last == ([4], [5])                        # request 4's stream and its own step count
+
+
+def test_batches_are_cut_by_pages_and_slots():
+    reqs = [Request([0] * 100, SamplingParams(max_tokens=29)), Request([0] * 10, SamplingParams(max_tokens=1)),
+            Request([0] * 64, SamplingParams(max_tokens=2)), Request([0] * 300, SamplingParams(max_tokens=1))]
+    assert [pages_for(r) for r in reqs] == [2, 1, 2, 5]
+    assert plan_batches(reqs, total_pages=5, max_batch=8) == [[0, 1, 2], [3]]
+    assert plan_batches(reqs, total_pages=100, max_batch=2) == [[0, 1], [2, 3]]
+    with pytest.raises(ValueError, match="request 3"):
+        plan_batches(reqs, total_pages=4, max_batch=8)
+
+
+def test_loop_closes_slots_when_a_step_fails():
+    class Failing(FakeStepper):
+        def step(self, entries):
+            if len(self.log) == 1:
+                raise RuntimeError("boom")
+            return super().step(entries)
+    st = Failing()
+    loop = GenerationLoop(st, GreedyHostSampler(), 100, 4)
+    with pytest.raises(RuntimeError, match="boom"):
+        loop.run([Request([1], SamplingParams(0.0, 0.9, 5)), Request([2], SamplingParams(0.0, 0.9, 5))])
+    assert not st.open_slots
+
+
+def test_generation_with_stand_in_kernels_matches_plain(emulated, model_folders):
+    import velomind_b200 as vm
+    folder = model_folders["tiny_b"]
+    cfg, w = P.read_model(folder)
+    prompts = [[1, 2, 3, 4, 5, 6, 7], [9, 8, 7, 6]]
+    te = vm.TextEngine(vm.EngineConfig(model_path=folder, dtype="float32", device="cpu", max_tokens=512)).load()
+    got = te.generate(prompts, temperature=0.8, top_p=0.95, max_tokens=4, seed=5, stop_tokens=())
+    want = [P.generate(cfg, w, p, 4, temperature=0.8, top_p=0.95, seed=5, stream=i) for i, p in enumerate(prompts)]
+    assert [r.tokens for r in got] == want
+    pieces = []
+    te.generate(prompts[:1], temperature=0.0, max_tokens=2, on_token=lambda i, t, piece: pieces.append(piece))
+    assert all(p.startswith("[") for p in pieces)         # no tokenizer: ids in brackets
+    logits = te.prefill(prompts[0][:-1])
+    step = te.forward_step(prompts[0][-1])
+    ref = P.forward_logits(cfg, w, prompts[0])
+    assert te.session_length == 7
+    assert np.abs(logits.numpy() - ref[-2]).max() < 5e-6 and np.abs(step.numpy() - ref[-1]).max() < 5e-6
+    assert np.abs(te.forward_logits(prompts[0]).numpy() - ref[-1]).max() < 5e-6
+    assert np.abs(te.forward_full_logits(prompts[0]).numpy() - ref).max() < 5e-6
+    te.reset_session()
+    assert te.session_length == 0 and te.engine.cache.slots.held_count == 0

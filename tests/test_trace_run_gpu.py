@@ -1,0 +1,48 @@
+"""bin/trace_run as a user runs it: a subprocess fed JSON lines, writing <step>.f32 files."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import schedules as S
+from tiny_configs import TINY_A, TINY_B
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+
+
+def _replay(folder, dtype, steps, out, max_tokens):
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
+                           "--out", out, "--max-tokens", str(max_tokens)], input=S.to_jsonl(steps), text=True,
+                          capture_output=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [ln for ln in proc.stdout.splitlines() if ln.startswith("done ")] == [f"done {s['step']}" for s in steps]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,cfg", [("tiny_a", TINY_A), ("tiny_b", TINY_B)])
+def test_replay_three_cuts(model_folders, tmp_path, name, cfg, dtype):
+    folder = model_folders[name]
+    requests = S.make_requests(cfg["vocab_size"], (40, 7, 100, 66, 35, 129), seed=13)
+    plain = S.plain_logits(folder, requests)
+    cuts = {"whole": S.steps_whole(requests), "tail": S.steps_tail_one_by_one(requests),
+            "batches": S.steps_unequal_batches(requests)}
+    # one process replays all three cuts, one after another, with a cache of 6 pages per... 3 live requests at most
+    steps, owner = [], {}
+    for cut, recs in cuts.items():
+        for r in recs:
+            r = dict(r, step=len(steps))
+            owner[r["step"]] = cut
+            steps.append(r)
+    out = str(tmp_path / "out")
+    _replay(folder, dtype, steps, out, max_tokens=64 * 8)
+    want = S.expected_rows(steps, requests, plain)
+    for step, rows in want.items():
+        got = np.fromfile(os.path.join(out, f"{step}.f32"), dtype="<f4").reshape(-1, cfg["vocab_size"])
+        assert got.shape == rows.shape, (step, owner[step])
+        err = float(np.abs(got - rows).max())
+        assert err <= TOL[dtype], f"step {step} of cut {owner[step]!r}: max |logit - plain| = {err:.3e}"
+    assert sorted(int(f[:-4]) for f in os.listdir(out)) == sorted(want)

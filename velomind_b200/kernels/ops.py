@@ -19,7 +19,8 @@ _CODES = {torch.float32: F32, torch.bfloat16: BF16}
 
 _c_int, _c_ll, _c_f, _c_p = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p
 
-launch_count = 0          # kernels launched through this module (the bench reports it)
+launch_count = 0          # this library's own kernels launched through this module (the bench reports it)
+library_calls = 0         # library matrix products (cuBLAS through torch.mm)
 
 
 class KernelError(RuntimeError):
@@ -143,8 +144,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
     any reduced-precision mode."""
     if not x.is_cuda:
         raise KernelError("this library runs on CUDA devices only; got a tensor on " + str(x.device))
-    global launch_count
-    launch_count += 1
+    global library_calls
+    library_calls += 1
     if x.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
         raise KernelError("float32 matrix products must not use TF32; torch.backends.cuda.matmul.allow_tf32 is set")
     if out.dtype == x.dtype:
