@@ -28,18 +28,20 @@ def test_replay_three_cuts(model_folders, tmp_path, name, cfg, dtype):
     folder = model_folders[name]
     requests = S.make_requests(cfg["vocab_size"], (40, 7, 100, 66, 35, 129), seed=13)
     plain = S.plain_logits(folder, requests)
-    cuts = {"whole": S.steps_whole(requests), "tail": S.steps_tail_one_by_one(requests),
-            "batches": S.steps_unequal_batches(requests)}
-    # one process replays all three cuts, one after another, with a cache of 6 pages per... 3 live requests at most
-    steps, owner = [], {}
-    for cut, recs in cuts.items():
-        for r in recs:
+    cuts = {"whole": S.steps_whole, "tail": S.steps_tail_one_by_one, "batches": S.steps_unequal_batches}
+    # one process replays all three cuts, one after another, with a cache of 8 pages: pages and slots are used again
+    steps, owner, all_requests, all_plain = [], {}, {}, {}
+    for cut, make in cuts.items():
+        renamed = {f"{cut}:{rid}": toks for rid, toks in requests.items()}
+        all_requests.update(renamed)
+        all_plain.update({f"{cut}:{rid}": plain[rid] for rid in requests})
+        for r in make(renamed):
             r = dict(r, step=len(steps))
             owner[r["step"]] = cut
             steps.append(r)
     out = str(tmp_path / "out")
     _replay(folder, dtype, steps, out, max_tokens=64 * 8)
-    want = S.expected_rows(steps, requests, plain)
+    want = S.expected_rows(steps, all_requests, all_plain)
     for step, rows in want.items():
         got = np.fromfile(os.path.join(out, f"{step}.f32"), dtype="<f4").reshape(-1, cfg["vocab_size"])
         assert got.shape == rows.shape, (step, owner[step])
