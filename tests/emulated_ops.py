@@ -134,6 +134,7 @@ def install(monkeypatch):
         def synchronize(self):
             pass
 
+    monkeypatch.setattr(step, "GRAPHS_DEFAULT", False)
     monkeypatch.setattr(step, "_host_buffer", lambda n, dtype: torch.empty(n, dtype=dtype))
     monkeypatch.setattr(step, "_new_event", lambda: _Event())
     monkeypatch.setattr(sampler, "_host_buffer", lambda shape, dtype: torch.empty(shape, dtype=dtype))

@@ -1,0 +1,299 @@
+"""Each CUDA kernel alone against a plain float32 reference, at sizes other than the engine tests use:
+head sizes in steps of 16, odd head counts and groups, widths and vocabularies that are no power of two."""
+import math
+import types
+
+import numpy as np
+import pytest
+import torch
+
+import emulated_ops as E
+import plain_llama as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def ops():
+    from velomind_b200.kernels import ops as o
+    return o
+
+
+def _gen(seed):
+    g = torch.Generator(device="cpu")
+    g.manual_seed(seed)
+    return g
+
+
+@pytest.mark.parametrize("table_dtype", [torch.float32, torch.bfloat16])
+def test_embed_gather(table_dtype):
+    V, hid, T = 1000, 136, 37
+    table = torch.randn(V, hid, generator=_gen(0)).to(table_dtype)
+    tokens = torch.randint(0, V, (T,), generator=_gen(1), dtype=torch.int32)
+    out = torch.empty(T, hid, device=DEV)
+    ops().embed_gather(table.to(DEV), tokens.to(DEV), out)
+    assert torch.equal(out.cpu(), table[tokens.long()].float())
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-6), (torch.bfloat16, 2e-2)])
+@pytest.mark.parametrize("hid", [200, 576, 4100])
+def test_add_rmsnorm(dtype, tol, hid):
+    T, eps = 19, 3e-6
+    h = torch.randn(T, hid, generator=_gen(2)) * 3
+    delta = torch.randn(T, hid, generator=_gen(3)).to(dtype)
+    w = 1 + 0.2 * torch.randn(hid, generator=_gen(4))
+    want_h = h + delta.float()
+    want = torch.from_numpy(P.rmsnorm(want_h.numpy(), w.numpy(), eps))
+    hd, out = h.to(DEV), torch.empty(T, hid, dtype=dtype, device=DEV)
+    ops().add_rmsnorm(hd, delta.to(DEV), w.to(DEV), eps, out)
+    assert torch.allclose(hd.cpu(), want_h, atol=1e-6)
+    assert (out.float().cpu() - want).abs().max() <= tol * max(1.0, float(want.abs().max()))
+    # no delta, selected rows: h untouched
+    rows = torch.tensor([18, 0, 7], dtype=torch.int32)
+    hd2, out2 = h.to(DEV), torch.empty(3, hid, dtype=dtype, device=DEV)
+    ops().add_rmsnorm(hd2, None, w.to(DEV), eps, out2, rows.to(DEV))
+    want2 = torch.from_numpy(P.rmsnorm(h[rows.long()].numpy(), w.numpy(), eps))
+    assert torch.equal(hd2.cpu(), h)
+    assert (out2.float().cpu() - want2).abs().max() <= tol * max(1.0, float(want2.abs().max()))
+    # delta and selected rows together
+    out3 = torch.empty(3, hid, dtype=dtype, device=DEV)
+    ops().add_rmsnorm(hd2, delta.to(DEV), w.to(DEV), eps, out3, rows.to(DEV))
+    assert (out3.float().cpu() - want[rows.long()]).abs().max() <= tol * max(1.0, float(want.abs().max()))
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-6), (torch.bfloat16, 1e-2)])
+def test_swiglu_residual_convert(dtype, tol):
+    T, I = 23, 100
+    gu = (torch.randn(T, 2 * I, generator=_gen(5)) * 2).to(dtype)
+    out = torch.empty(T, I, dtype=dtype, device=DEV)
+    ops().swiglu(gu.to(DEV), out)
+    want = torch.from_numpy(P.swiglu(gu[:, :I].float().numpy(), gu[:, I:].float().numpy()))
+    assert (out.float().cpu() - want).abs().max() <= tol * float(want.abs().max())
+    h = torch.randn(T, I, generator=_gen(6))
+    hd = h.to(DEV)
+    ops().residual_add(hd, out)
+    assert torch.allclose(hd.cpu(), h + out.float().cpu(), atol=1e-6)
+    if dtype == torch.bfloat16:
+        x = torch.randn(1000, generator=_gen(7))
+        y = torch.empty(1000, dtype=torch.bfloat16, device=DEV)
+        ops().convert(x.to(DEV), y)
+        assert torch.equal(y.cpu(), x.to(torch.bfloat16))
+        z = torch.empty(1000, dtype=torch.float32, device=DEV)
+        ops().convert(y, z)
+        assert torch.equal(z.cpu(), x.to(torch.bfloat16).float())
+
+
+def _paged(K, V, lens, n_pages, seed):
+    """Scatter dense per-sequence keys/values [len, Hkv, D] into shuffled pages; returns pages and block table."""
+    Hkv, D = K[0].shape[1:]
+    order = torch.randperm(n_pages, generator=_gen(seed)).tolist()
+    width = max(-(-n // 64) for n in lens)
+    table = torch.full((len(lens), width), -1, dtype=torch.int32)
+    kp = torch.randn(n_pages, Hkv, 64, D, generator=_gen(seed + 1)) * 5      # stale content in unused rows
+    vp = torch.randn(n_pages, Hkv, 64, D, generator=_gen(seed + 2)) * 5
+    for s, n in enumerate(lens):
+        for b in range(-(-n // 64)):
+            pg = order.pop()
+            table[s, b] = pg
+            m = min(64, n - 64 * b)
+            kp[pg, :, :m] = K[s][64 * b: 64 * b + m].transpose(0, 1)
+            vp[pg, :, :m] = V[s][64 * b: 64 * b + m].transpose(0, 1)
+    return kp, vp, table
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-6), (torch.bfloat16, 1.5e-2)])
+@pytest.mark.parametrize("H,Hkv,D,rot", [(5, 5, 48, 48), (6, 2, 16, 16), (7, 1, 80, 32), (4, 4, 128, 0)])
+def test_rope_kv_write(dtype, tol, H, Hkv, D, rot):
+    lens_before, new = [3, 70, 0], [5, 1, 66]
+    B = 3
+    T = sum(new)
+    qkv = torch.randn(T, (H + 2 * Hkv) * D, generator=_gen(8)).to(dtype)
+    positions = torch.cat([torch.arange(a, a + n) for a, n in zip(lens_before, new)]).int()
+    seq = torch.cat([torch.full((n,), s) for s, n in enumerate(new)]).int()
+    n_pages = 8
+    table = torch.tensor([[5, -1], [2, 7], [0, 3]], dtype=torch.int32)
+    inv_freq = torch.from_numpy((1.0 / np.power(np.float32(5000.0), np.arange(rot // 2, dtype=np.float32) * 2 / max(rot, 1))).astype(np.float32)) if rot else None
+    kp = torch.zeros(n_pages, Hkv, 64, D, dtype=dtype)
+    vp = torch.zeros_like(kp)
+    want_qkv, want_k, want_v = qkv.clone(), kp.clone(), vp.clone()
+    E.rope_kv_write(want_qkv, positions, seq, table, inv_freq, rot, want_k, want_v, H, Hkv, D)
+    d_qkv, d_k, d_v = qkv.to(DEV), kp.to(DEV), vp.to(DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops().rope_kv_write(d_qkv, positions.to(DEV), seq.to(DEV), table.to(DEV), None if inv_freq is None else inv_freq.to(DEV),
+                        rot, d_k, d_v, H, Hkv, D, err)
+    assert int(err.item()) == 0
+    q_cols = H * D
+    assert (d_qkv.float().cpu()[:, :q_cols] - want_qkv.float()[:, :q_cols]).abs().max() <= tol * 4
+    assert torch.equal(d_qkv.cpu()[:, q_cols:], qkv[:, q_cols:])                 # k and v columns of the input stay
+    assert (d_k.float().cpu() - want_k.float()).abs().max() <= tol * 4
+    assert torch.equal(d_v.cpu(), want_v)
+    # queries only (a run that reads another run's cache): no page is written
+    d_k2 = torch.zeros_like(d_k)
+    d_qkv2 = qkv.to(DEV)
+    ops().rope_kv_write(d_qkv2, positions.to(DEV), seq.to(DEV), table.to(DEV), None if inv_freq is None else inv_freq.to(DEV),
+                        rot, None, None, H, Hkv, D, err)
+    assert torch.equal(d_qkv2.cpu()[:, :q_cols], d_qkv.cpu()[:, :q_cols]) and float(d_k2.abs().sum()) == 0
+    # a missing page is reported, not written through
+    bad = table.clone(); bad[2, 1] = -1
+    ops().rope_kv_write(qkv.to(DEV), positions.to(DEV), seq.to(DEV), bad.to(DEV), None if inv_freq is None else inv_freq.to(DEV),
+                        rot, d_k, d_v, H, Hkv, D, err)
+    assert int(err.item()) == 2
+
+
+def _attention_case(H, Hkv, D, lens_before, new, window, seed, spike=True):
+    """Dense q/k/v per sequence, the plain result for the NEW tokens, and everything paged for the kernels.
+    With `spike`, one far key per sequence is made to dominate the last query of head 0, so that a kernel
+    which loses that key (a wrong page, a window off by one, a split that is skipped) is far off."""
+    rng = np.random.default_rng(seed)
+    K, V, Q, want = [], [], [], []
+    for a, n in zip(lens_before, new):
+        L = a + n
+        k = rng.standard_normal((L, Hkv, D)).astype(np.float32)
+        v = rng.standard_normal((L, Hkv, D)).astype(np.float32)
+        q = rng.standard_normal((L, H, D)).astype(np.float32)
+        if spike and L > 3:
+            far = (L - window if window and L > window else 1)          # the oldest key the last query may see
+            far = max(far, 0)
+            k[far, 0, :] = 0; k[far, 0, 0] = 8.0 * math.sqrt(D)
+            q[L - 1, 0, :] = 0; q[L - 1, 0, 0] = 8.0 * math.sqrt(D)
+        K.append(k); V.append(v); Q.append(q)
+    return Q, K, V
+
+
+def _run_attention(kind, dtype, H, Hkv, D, lens_before, new, window, seed=0):
+    o = ops()
+    Q, K, V = _attention_case(H, Hkv, D, lens_before, new, window, seed)
+    scale = 1.0 / math.sqrt(D)
+    tdt = dtype
+    Kt = [torch.from_numpy(k).to(tdt) for k in K]
+    Vt = [torch.from_numpy(v).to(tdt) for v in V]
+    Qt = [torch.from_numpy(q).to(tdt) for q in Q]
+    want = []
+    for q, k, v, a, n in zip(Qt, Kt, Vt, lens_before, new):
+        full = P.attention(q.float().numpy(), k.float().numpy(), v.float().numpy(), scale, window=window)
+        want.append(full[a: a + n].reshape(n, H * D))
+    want = np.concatenate(want)
+    lens = [a + n for a, n in zip(lens_before, new)]
+    n_pages = sum(-(-n // 64) for n in lens) + 3
+    kp, vp, table = _paged(Kt, Vt, lens, n_pages, seed + 10)
+    kp, vp = kp.to(tdt), vp.to(tdt)
+    T = sum(new)
+    # q as a view into a wider qkv-like buffer (row stride > H*D), as the engine passes it
+    stride = (H + 2 * Hkv) * D
+    qkv = torch.zeros(T, stride, dtype=tdt)
+    qkv[:, : H * D] = torch.cat([q[a: a + n].reshape(n, H * D) for q, a, n in zip(Qt, lens_before, new)])
+    positions = torch.cat([torch.arange(a, a + n) for a, n in zip(lens_before, new)]).int()
+    seq = torch.cat([torch.full((n,), s) for s, n in enumerate(new)]).int()
+    cu = torch.tensor([0] + list(np.cumsum(new)), dtype=torch.int32)
+    out = torch.full((T, H * D), float("nan"), dtype=tdt, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    d = lambda t: t.to(DEV)
+    if kind == "generic":
+        o.attention_generic(d(qkv), stride, d(kp), d(vp), d(table), d(positions), d(seq), out, H, Hkv, D, scale, window, err)
+    elif kind == "prefill":
+        n_tiles = sum(-(-n // 64) for n in new)
+        o.attention_prefill_bf16(d(qkv), stride, d(kp), d(vp), d(table), d(positions), d(cu), n_tiles, out, H, Hkv, D, scale,
+                                 window, err)
+    else:
+        B = len(new)
+        n_splits = o.decode_splits(B, Hkv, H // Hkv, table.shape[1])
+        for splits in sorted({1, n_splits, min(3, table.shape[1])}):
+            partial = torch.full((B * H * splits * (D + 2),), float("nan"), device=DEV)
+            counters = torch.zeros(B * H, dtype=torch.int32, device=DEV)
+            out.fill_(float("nan"))
+            o.attention_decode_bf16(d(qkv), stride, d(kp), d(vp), d(table), d(positions), out, partial, counters, H, Hkv, D,
+                                    splits, scale, window, err)
+            assert int(counters.abs().sum().item()) == 0            # the counters are left ready for the next launch
+            got = out.float().cpu().numpy()
+            assert np.abs(got - want).max() <= 2e-2, (splits, float(np.abs(got - want).max()))
+    assert int(err.item()) == 0
+    return out.float().cpu().numpy(), want
+
+
+SHAPES = [(4, 2, 16), (3, 1, 32), (5, 5, 48), (9, 3, 64), (6, 2, 80), (7, 7, 96), (10, 1, 112), (8, 2, 128)]
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 3e-5), (torch.bfloat16, 2e-2)])
+@pytest.mark.parametrize("H,Hkv,D", SHAPES + [(2, 1, 144), (2, 2, 256)])
+@pytest.mark.parametrize("window", [0, 70])
+def test_attention_generic(dtype, tol, H, Hkv, D, window):
+    got, want = _run_attention("generic", dtype, H, Hkv, D, [0, 130, 63, 0, 200], [100, 3, 2, 1, 1], window)
+    assert np.isfinite(got).all() and np.abs(got - want).max() <= tol
+
+
+@pytest.mark.parametrize("H,Hkv,D", SHAPES)
+@pytest.mark.parametrize("window", [0, 70, 64])
+def test_attention_prefill_bf16(H, Hkv, D, window):
+    # whole prompts of awkward lengths, a continued sequence (chunked prefill), single tokens
+    got, want = _run_attention("prefill", torch.bfloat16, H, Hkv, D, [0, 130, 63, 0, 200, 0], [200, 67, 2, 1, 1, 64], window)
+    assert np.isfinite(got).all() and np.abs(got - want).max() <= 2e-2
+
+
+@pytest.mark.parametrize("H,Hkv,D", SHAPES + [(12, 1, 64), (16, 16, 64)])
+@pytest.mark.parametrize("window", [0, 70])
+def test_attention_decode_bf16(H, Hkv, D, window):
+    _run_attention("decode", torch.bfloat16, H, Hkv, D, [0, 63, 64, 130, 700, 1], [1, 1, 1, 1, 1, 1], window)
+
+
+def test_attention_reports_a_missing_page():
+    o = ops()
+    H, Hkv, D = 2, 1, 16
+    kp = torch.zeros(4, Hkv, 64, D, device=DEV)
+    table = torch.tensor([[1, -1]], dtype=torch.int32, device=DEV)
+    q = torch.zeros(1, H * D, device=DEV)
+    out = torch.empty(1, H * D, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    o.attention_generic(q, H * D, kp, kp, table, torch.tensor([70], dtype=torch.int32, device=DEV),
+                        torch.tensor([0], dtype=torch.int32, device=DEV), out, H, Hkv, D, 1.0, 0, err)
+    assert int(err.item()) == 3
+
+
+@pytest.mark.parametrize("V", [1000, 49152 + 7])
+def test_sampling(V):
+    o = ops()
+    R = 6
+    rng = np.random.default_rng(V)
+    logits = (rng.standard_normal((R, V)) * 2).astype(np.float32)
+    logits[0, 17] = logits[0, 400] = logits[0].max() + 1          # a tie: the lower index wins
+    logits[1, :5] = np.nan
+    logits[2, :] = np.nan                                         # nothing to choose from
+    logits[3, 10] = np.inf
+    temperature = np.array([0.0, 0.0, 0.0, 0.0, 0.8, 1.3], dtype=np.float32)
+    top_p = np.array([0.9, 0.9, 0.9, 0.9, 1.0, 0.6], dtype=np.float32)
+    seed = np.array([1, 2, 3, 4, 1234, 99], dtype=np.int64)
+    stream = np.array([0, 1, 2, 3, 4, 5], dtype=np.int64)
+    dl = torch.from_numpy(logits).to(DEV)
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    mism = 0
+    for step in range(40):
+        steps = np.full(R, step, dtype=np.int64)
+        o.sample(dl, torch.from_numpy(temperature).to(DEV), torch.from_numpy(top_p).to(DEV), torch.from_numpy(seed).to(DEV),
+                 torch.from_numpy(stream).to(DEV), torch.from_numpy(steps).to(DEV), out)
+        got = out.cpu().numpy()
+        assert got[0] == 17 and got[1] == int(np.nanargmax(logits[1])) and got[2] == -1 and got[3] == 10
+        for r in (4, 5):
+            want = P.sample_top_p(logits[r], float(temperature[r]), float(top_p[r]), P.uniform01(int(seed[r]), int(stream[r]), step))
+            mism += int(got[r] != want)
+    assert mism == 0
+    # a strided view of a wider buffer works too
+    wide = torch.zeros(R, V + 9, device=DEV)
+    wide[:, :V] = dl
+    o.sample(wide[:, :V], None, None, None, None, None, out)
+    assert out.cpu().numpy()[0] == 17
+
+
+def test_sampled_distribution():
+    o = ops()
+    probs = np.array([0.5, 0.25, 0.125, 0.0625, 0.0625], dtype=np.float32)
+    R = 4096
+    logits = torch.from_numpy(np.log(probs)).repeat(R, 1).to(DEV)
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    ones = torch.ones(R, device=DEV)
+    o.sample(logits, ones, ones, torch.full((R,), 7, dtype=torch.int64, device=DEV), torch.arange(R, dtype=torch.int64, device=DEV),
+             torch.zeros(R, dtype=torch.int64, device=DEV), out)
+    freq = np.bincount(out.cpu().numpy(), minlength=5) / R
+    assert np.abs(freq - probs).max() < 0.03
+    o.sample(logits, ones, ones * 0.7, torch.full((R,), 7, dtype=torch.int64, device=DEV), torch.arange(R, dtype=torch.int64, device=DEV),
+             torch.zeros(R, dtype=torch.int64, device=DEV), out)
+    freq = np.bincount(out.cpu().numpy(), minlength=5) / R
+    assert freq[2:].sum() == 0 and abs(freq[0] - 2 / 3) < 0.03       # nucleus of 0.7 = the two most probable tokens

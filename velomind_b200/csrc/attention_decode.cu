@@ -1,0 +1,219 @@
+// Decode attention for bfloat16: every sequence of the batch brings ONE new token; its query heads read
+// the whole cache of the sequence.  The work is bandwidth- and latency-bound, so the keys of a sequence
+// are split over several CTAs (split-KV) and the partial results are merged by the last CTA to finish.
+//
+// Arithmetic as in attention_generic.cu (reference: examples/common/llama/llama_graph.cpp:97-103 and the
+// online form of src/cpu/ops/fused_attention.cpp:84-135); the G = H / Hkv query heads that share a kv
+// head (src/cpu/ops/repeat_kv.cpp:51-61) are served by one CTA, so each key and value is read once.
+//
+// grid = (n_splits, Hkv * ceil(G / GM), B), 128 threads.  A CTA's key range is a whole number of cache
+// pages, computed on the device from the sequence's length: the launch shape does not depend on the
+// lengths, so the launch can sit in a CUDA graph.  Scratch (global memory beyond inputs and outputs):
+// float partials [B, H, n_splits, D + 2] and one int counter per (B, kv-head group), which must be zero
+// before the first launch and is left zero by every launch.
+#include "common.cuh"
+
+namespace {
+
+constexpr int DEC_WARPS = 4;
+
+template <int GM, int EPL>
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, const __nv_bfloat16* __restrict__ kpages,
+                   const __nv_bfloat16* __restrict__ vpages, const int* __restrict__ block_table, int max_blocks,
+                   const int* __restrict__ positions, __nv_bfloat16* __restrict__ out, float* __restrict__ partial,
+                   int* __restrict__ counters, int H, int Hkv, int D, float scale, int window, int n_pages,
+                   int* __restrict__ err) {
+    extern __shared__ float sm[];                          // q [GM][D]; then per-warp results [DEC_WARPS][GM][D+2]
+    const int split = blockIdx.x, n_splits = gridDim.x;
+    const int G = H / Hkv;
+    const int groups_per_kv = (G + GM - 1) / GM;
+    const int hk = blockIdx.y / groups_per_kv, gg = blockIdx.y - hk * groups_per_kv;
+    const int b = blockIdx.z;
+    const int h0 = hk * G + gg * GM;                       // first query head of this CTA
+    const int ng = min(GM, G - gg * GM);                   // query heads of this CTA
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pos = positions[b];                          // one token per sequence: token index == sequence index
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int first_page = lo / VM_PAGE_TOKENS, last_page = pos / VM_PAGE_TOKENS;
+    const int pages = last_page - first_page + 1;
+    const int per_split = (pages + n_splits - 1) / n_splits;
+    const int page_a = first_page + split * per_split, page_b = min(last_page + 1, page_a + per_split);
+    float* qs = sm;
+    float* res = sm + GM * D;
+    for (int i = threadIdx.x; i < ng * D; i += blockDim.x) {
+        const int g = i / D, d = i - g * D;
+        qs[g * D + d] = __bfloat162float(q[(size_t)b * q_row_stride + (size_t)(h0 + g) * D + d]) * scale;
+    }
+    __syncthreads();
+
+    float m[GM], l[GM], acc[GM][EPL];
+#pragma unroll
+    for (int g = 0; g < GM; ++g) {
+        m[g] = -INFINITY; l[g] = 0.f;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) acc[g][i] = 0.f;
+    }
+    const size_t page_stride = (size_t)Hkv * VM_PAGE_TOKENS * D;
+    const int* table = block_table + (size_t)b * max_blocks;
+    // each warp takes 32-key half pages: chunk c of the CTA's range covers keys page_a*64 + 32c ..
+    const int n_chunks = (page_b > page_a) ? (page_b - page_a) * 2 : 0;
+    for (int c = warp; c < n_chunks; c += DEC_WARPS) {
+        const int blk = page_a + (c >> 1);
+        const int base = blk * VM_PAGE_TOKENS + (c & 1) * 32;
+        if (base > pos || base + 31 < lo) continue;
+        const int page = (blk < max_blocks) ? table[blk] : -1;
+        if (page < 0 || page >= n_pages) { if (lane == 0 && err) atomicExch(err, 3); continue; }
+        const size_t tile = (size_t)page * page_stride + ((size_t)hk * VM_PAGE_TOKENS + (c & 1) * 32) * D;
+        const int j = base + lane;
+        const bool valid = (j >= lo && j <= pos);
+        float s[GM];
+#pragma unroll
+        for (int g = 0; g < GM; ++g) s[g] = 0.f;
+        if (valid) {
+            const uint4* krow = reinterpret_cast<const uint4*>(kpages + tile + (size_t)lane * D);
+            for (int ch = 0; ch < D / 8; ++ch) {
+                const uint4 kv = krow[ch];
+                const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&kv);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 kf = __bfloat1622float2(k2[e]);
+#pragma unroll
+                    for (int g = 0; g < GM; ++g) {
+                        if (g < ng) {
+                            s[g] = fmaf(qs[g * D + ch * 8 + 2 * e], kf.x, s[g]);
+                            s[g] = fmaf(qs[g * D + ch * 8 + 2 * e + 1], kf.y, s[g]);
+                        }
+                    }
+                }
+            }
+        }
+        float p[GM];
+#pragma unroll
+        for (int g = 0; g < GM; ++g) {
+            const float sv = valid ? s[g] : -INFINITY;
+            const float mn = fmaxf(m[g], vm_warp_max(sv));           // the chunk holds at least one valid key
+            p[g] = valid ? expf(sv - mn) : 0.f;
+            const float alpha = expf(m[g] - mn);
+            l[g] = l[g] * alpha + vm_warp_sum(p[g]);
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) acc[g][i] *= alpha;
+            m[g] = mn;
+        }
+        const int cnt = min(32, pos - base + 1);
+        const int first = max(0, lo - base);
+        for (int jj = first; jj < cnt; ++jj) {
+            const __nv_bfloat16* vrow = vpages + tile + (size_t)jj * D;
+            float vv[EPL];
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) { const int d = lane + 32 * i; vv[i] = (d < D) ? __bfloat162float(vrow[d]) : 0.f; }
+#pragma unroll
+            for (int g = 0; g < GM; ++g) {
+                const float pj = __shfl_sync(0xffffffffu, p[g], jj);
+#pragma unroll
+                for (int i = 0; i < EPL; ++i) acc[g][i] = fmaf(pj, vv[i], acc[g][i]);
+            }
+        }
+    }
+    // ---- join the CTA's warps
+    const int RW = D + 2;
+#pragma unroll
+    for (int g = 0; g < GM; ++g) {
+        if (g < ng) {
+            float* r = res + ((size_t)warp * GM + g) * RW;
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) { const int d = lane + 32 * i; if (d < D) r[d] = acc[g][i]; }
+            if (lane == 0) { r[D] = m[g]; r[D + 1] = l[g]; }
+        }
+    }
+    __syncthreads();
+    // partial[b, h, split, :] = (o[D], m, l), merged over the warps
+    for (int i = threadIdx.x; i < ng * D; i += blockDim.x) {
+        const int g = i / D, d = i - g * D;
+        float M = -INFINITY;
+        for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, res[((size_t)w * GM + g) * RW + D]);
+        float o = 0.f, L = 0.f;
+        for (int w = 0; w < DEC_WARPS; ++w) {
+            const float* r = res + ((size_t)w * GM + g) * RW;
+            const float f = (r[D] == -INFINITY) ? 0.f : expf(r[D] - M);
+            o += f * r[d]; L += f * r[D + 1];
+        }
+        float* dst = partial + (((size_t)b * H + (h0 + g)) * n_splits + split) * RW;
+        dst[d] = o;
+        if (d == 0) { dst[D] = M; dst[D + 1] = L; }
+    }
+    // ---- the last CTA of this (sequence, head group) merges the splits
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int old = atomicAdd(&counters[(size_t)b * gridDim.y + blockIdx.y], 1);
+        is_last = (old == n_splits - 1);
+        if (is_last) counters[(size_t)b * gridDim.y + blockIdx.y] = 0;     // ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int i = threadIdx.x; i < ng * D; i += blockDim.x) {
+        const int g = i / D, d = i - g * D;
+        const float* src = partial + ((size_t)b * H + (h0 + g)) * n_splits * RW;
+        float M = -INFINITY;
+        for (int s2 = 0; s2 < n_splits; ++s2) M = fmaxf(M, __ldcg(src + (size_t)s2 * RW + D));
+        float o = 0.f, L = 0.f;
+        for (int s2 = 0; s2 < n_splits; ++s2) {
+            const float ms = __ldcg(src + (size_t)s2 * RW + D);
+            const float f = (ms == -INFINITY) ? 0.f : expf(ms - M);
+            o += f * __ldcg(src + (size_t)s2 * RW + d);
+            L += f * __ldcg(src + (size_t)s2 * RW + D + 1);
+        }
+        out[((size_t)b * H + (h0 + g)) * D + d] = __float2bfloat16_rn(o / L);
+    }
+}
+
+template <int GM>
+int launch_decode(int epl, dim3 grid, size_t smem, cudaStream_t stream, const __nv_bfloat16* q, int q_row_stride,
+                  const __nv_bfloat16* kpages, const __nv_bfloat16* vpages, const int* block_table, int max_blocks,
+                  const int* positions, __nv_bfloat16* out, float* partial, int* counters, int H, int Hkv, int D,
+                  float scale, int window, int n_pages, int* err) {
+#define VM_DEC_CASE(E)                                                                                               \
+    case E:                                                                                                          \
+        attn_decode_kernel<GM, E><<<grid, DEC_WARPS * 32, smem, stream>>>(q, q_row_stride, kpages, vpages, block_table, \
+            max_blocks, positions, out, partial, counters, H, Hkv, D, scale, window, n_pages, err);                   \
+        break;
+    switch (epl) {
+        VM_DEC_CASE(1) VM_DEC_CASE(2) VM_DEC_CASE(3) VM_DEC_CASE(4)
+        default: return VM_ERR_UNSUPPORTED;
+    }
+#undef VM_DEC_CASE
+    return vm_launch_status();
+}
+
+}  // namespace
+
+// Bytes of float scratch the kernel needs for a batch of B sequences.
+VM_API long long vm_attention_decode_scratch_floats(int B, int H, int D, int n_splits) {
+    return (long long)B * H * n_splits * (D + 2);
+}
+
+// q: [B, H, D] rows with stride q_row_stride; out: [B, H*D].  counters: at least B * Hkv * ceil(G/GM) ints, zero.
+VM_API int vm_attention_decode_bf16(const void* q, int q_row_stride, const void* kpages, const void* vpages,
+                                    const int* block_table, int max_blocks, const int* positions, void* out,
+                                    float* partial, int* counters, int B, int H, int Hkv, int D, int n_splits,
+                                    float scale, int window, int n_pages, int* err, cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || D % 8 != 0 || D > 128 || n_splits < 1 || (q_row_stride % 8) != 0)
+        return VM_ERR_UNSUPPORTED;
+    const int G = H / Hkv;
+    const int GM = G <= 1 ? 1 : (G <= 2 ? 2 : (G <= 4 ? 4 : 8));
+    const int groups = (G + GM - 1) / GM;
+    dim3 grid(n_splits, Hkv * groups, B);
+    const size_t smem = ((size_t)GM * D + (size_t)DEC_WARPS * GM * (D + 2)) * sizeof(float);
+    const int epl = (D + 31) / 32;
+    const __nv_bfloat16 *qq = (const __nv_bfloat16*)q, *kk = (const __nv_bfloat16*)kpages, *vv = (const __nv_bfloat16*)vpages;
+    switch (GM) {
+        case 1: return launch_decode<1>(epl, grid, smem, stream, qq, q_row_stride, kk, vv, block_table, max_blocks, positions, (__nv_bfloat16*)out, partial, counters, H, Hkv, D, scale, window, n_pages, err);
+        case 2: return launch_decode<2>(epl, grid, smem, stream, qq, q_row_stride, kk, vv, block_table, max_blocks, positions, (__nv_bfloat16*)out, partial, counters, H, Hkv, D, scale, window, n_pages, err);
+        case 4: return launch_decode<4>(epl, grid, smem, stream, qq, q_row_stride, kk, vv, block_table, max_blocks, positions, (__nv_bfloat16*)out, partial, counters, H, Hkv, D, scale, window, n_pages, err);
+        default: return launch_decode<8>(epl, grid, smem, stream, qq, q_row_stride, kk, vv, block_table, max_blocks, positions, (__nv_bfloat16*)out, partial, counters, H, Hkv, D, scale, window, n_pages, err);
+    }
+}

@@ -84,6 +84,11 @@ class Workspace:
         self._recording = plan is None or self.arena is None or self.arena.numel() < plan.peak_bytes
         self._log, self._live, self._clock, self._next = [], {}, 0, 0
 
+    def planned(self, key) -> bool:
+        """True if a step of bucket `key` would be served from the arena (its plan exists and fits)."""
+        plan = self.plans.get(key)
+        return plan is not None and self.arena is not None and self.arena.numel() >= plan.peak_bytes
+
     def take(self, shape, dtype: torch.dtype) -> torch.Tensor:
         numel = 1
         for d in shape:

@@ -43,6 +43,9 @@ def _bucket(n: int, fine_from: int = 512, fine_step: int = 512, floor: int = 8) 
     return -(-n // fine_step) * fine_step
 
 
+GRAPHS_DEFAULT = True     # decode steps are replayed from CUDA graphs unless an Engine is told otherwise
+
+
 def _host_buffer(n: int, dtype: torch.dtype) -> torch.Tensor:
     """Page-locked host memory, so that the copy to the device is asynchronous."""
     return torch.empty(n, dtype=dtype, pin_memory=True)
@@ -127,6 +130,8 @@ class StepContext:
         self.one_token_each = (self.max_new == 1 and T == B)
         self.run: Optional[int] = None
         self.logits: Optional[torch.Tensor] = None
+        self.capturing = False          # True while the step is recorded into a CUDA graph: no choice may depend
+        #                                 on this step's lengths, only on its shape (T, B, R, table widths)
 
     # ---- scratch
     def take_tokens(self, cols: int, dtype: torch.dtype) -> torch.Tensor:
@@ -160,7 +165,7 @@ class Engine:
     """A model on one GPU with its cache: open/close sequence slots and step batches through the model."""
 
     def __init__(self, model: DecoderModel, max_tokens: int, max_slots: Optional[int] = None,
-                 max_step_tokens: int = 8192):
+                 max_step_tokens: int = 8192, use_graphs: Optional[bool] = None):
         if model.device is None:
             raise RuntimeError("the model has no weights bound; use load_model()")
         self.model = model
@@ -176,6 +181,9 @@ class Engine:
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._desc: Dict[Tuple, Descriptors] = {}
         self._logits: Optional[torch.Tensor] = None
+        self._graphs: Dict[Tuple, "torch.cuda.CUDAGraph"] = {}
+        self.use_graphs = GRAPHS_DEFAULT if use_graphs is None else bool(use_graphs)
+        self.graphs_captured = 0
         self.steps_run = 0
 
     # ---- slots
@@ -285,6 +293,39 @@ class Engine:
             self._desc[key] = d
         return d
 
+    def _run_eager(self, ctx: StepContext, bucket) -> None:
+        self.ws.begin(bucket)
+        try:
+            self.model.forward(ctx)
+        except Exception:
+            self.ws.abort()
+            raise
+        self.ws.end()
+
+    def _replay_graph(self, ctx: StepContext, bucket, shape_key) -> None:
+        """Decode steps (one token per sequence) are launch-bound: the kernels of a step are captured once
+        per batch shape into a CUDA graph and replayed.  Everything that changes from step to step (tokens,
+        positions, lengths, block tables) lies in the descriptor buffer, which the graph reads."""
+        key = (bucket, shape_key, self.ws.generation)
+        graph = self._graphs.get(key)
+        if graph is None:
+            if len(self._graphs) >= 256:
+                self._graphs.clear()
+            ctx.capturing = True
+            graph = torch.cuda.CUDAGraph()
+            torch.cuda.current_stream().synchronize()
+            self.ws.begin(bucket)
+            try:
+                with torch.cuda.graph(graph):
+                    self.model.forward(ctx)
+            except Exception:
+                self.ws.abort()
+                raise
+            self.ws.end()
+            self._graphs[key] = graph
+            self.graphs_captured += 1
+        graph.replay()
+
     def _run_chunk(self, entries, chunk, logits, row0, produced) -> int:
         cache = self.cache
         B = len(chunk)
@@ -339,13 +380,11 @@ class Engine:
 
         ctx = StepContext(self, desc, T, B, R, widths)
         ctx.logits = logits[row0: row0 + R]
-        self.ws.begin((desc.caps[0], desc.caps[1], desc.caps[2]))
-        try:
-            self.model.forward(ctx)
-        except Exception:
-            self.ws.abort()
-            raise
-        self.ws.end()
+        bucket = (desc.caps[0], desc.caps[1], desc.caps[2], ctx.one_token_each)   # decode steps take other scratch
+        if self.use_graphs and ctx.one_token_each and self.ws.planned(bucket):
+            self._replay_graph(ctx, bucket, (T, B, R, tuple(widths), ctx.logits.data_ptr()))
+        else:
+            self._run_eager(ctx, bucket)
         for s, (i, a, b) in enumerate(chunk):
             cache.commit(entries[i].slot, new_len[s])
         produced.extend(wanted_here)

@@ -131,11 +131,78 @@ def attention_generic(q: torch.Tensor, q_row_stride: int, k_pages: torch.Tensor,
            "attention_generic")
 
 
+def attention_prefill_bf16(q: torch.Tensor, q_row_stride: int, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                           block_table: torch.Tensor, positions: torch.Tensor, cu_tokens: torch.Tensor, n_tiles: int,
+                           out: torch.Tensor, H: int, Hkv: int, D: int, scale: float, window: int = 0,
+                           err: Optional[torch.Tensor] = None) -> None:
+    """Tensor-core attention of the step's new tokens over the cache (bfloat16, D in 16..128 step 16).
+    cu_tokens int32 [B+1]: token offsets of the sequences; n_tiles = sum of ceil(new tokens / 64)."""
+    B = cu_tokens.shape[0] - 1
+    _check(library().vm_attention_prefill_bf16(_ptr(q), _c_int(q_row_stride), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+                                               _c_int(block_table.shape[1]), _ptr(positions), _ptr(cu_tokens), _c_int(B),
+                                               _c_int(n_tiles), _ptr(out), _c_int(H), _c_int(Hkv), _c_int(D), _c_f(scale),
+                                               _c_int(window), _c_int(k_pages.shape[0]), _ptr(err), _stream()),
+           "attention_prefill_bf16")
+
+
+_decode_counters = {}
+DECODE_COUNTERS = 1 << 16
+MAX_DECODE_SPLITS = 16
+
+
+def decode_counters(device) -> torch.Tensor:
+    """Zeroed int32 counters the split-KV decode kernel leaves zero after every launch (one per device)."""
+    key = str(device)
+    if key not in _decode_counters:
+        _decode_counters[key] = torch.zeros(DECODE_COUNTERS, dtype=torch.int32, device=device)
+    return _decode_counters[key]
+
+
+def decode_splits(B: int, Hkv: int, G: int, table_width: int) -> int:
+    """How many CTAs share the keys of one (sequence, kv head): enough to fill the GPU, a function of the
+    step's SHAPE only (so that a captured launch stays valid as sequences grow)."""
+    gm = 1 if G <= 1 else 2 if G <= 2 else 4 if G <= 4 else 8
+    groups = B * Hkv * (-(-G // gm))
+    want = -(-2 * 148 // groups)
+    return max(1, min(want, MAX_DECODE_SPLITS, table_width))
+
+
+def attention_decode_bf16(q: torch.Tensor, q_row_stride: int, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                          block_table: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, partial: torch.Tensor,
+                          counters: torch.Tensor, H: int, Hkv: int, D: int, n_splits: int, scale: float, window: int = 0,
+                          err: Optional[torch.Tensor] = None) -> None:
+    """One new token per sequence: split-KV attention over the cache (bfloat16, D <= 128, D % 8 == 0).
+    partial: float32 scratch of B*H*n_splits*(D+2); counters: zeroed int32, left zero."""
+    B = out.shape[0]
+    if partial.numel() < B * H * n_splits * (D + 2) or counters.numel() < B * H:
+        raise KernelError("attention_decode_bf16: scratch too small")
+    _check(library().vm_attention_decode_bf16(_ptr(q), _c_int(q_row_stride), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+                                              _c_int(block_table.shape[1]), _ptr(positions), _ptr(out), _ptr(partial),
+                                              _ptr(counters), _c_int(B), _c_int(H), _c_int(Hkv), _c_int(D), _c_int(n_splits),
+                                              _c_f(scale), _c_int(window), _c_int(k_pages.shape[0]), _ptr(err), _stream()),
+           "attention_decode_bf16")
+
+
 def attention(ctx, q: torch.Tensor, q_row_stride: int, k_pages: torch.Tensor, v_pages: torch.Tensor,
               block_table: torch.Tensor, out: torch.Tensor, H: int, Hkv: int, D: int, scale: float, window: int = 0) -> None:
-    """Attention of the step's tokens over the cache; picks the kernel for the step's shape and dtype."""
-    attention_generic(q, q_row_stride, k_pages, v_pages, block_table, ctx.positions, ctx.seq_of_token, out,
-                      H, Hkv, D, scale, window, ctx.err)
+    """Attention of the step's tokens over the cache; picks the kernel for the step's shape and dtype:
+    bfloat16 with one new token per sequence -> split-KV decode kernel; bfloat16 otherwise -> tensor-core
+    prefill kernel; float32, or a head size those refuse -> the generic kernel."""
+    fast = out.dtype == torch.bfloat16 and D % 16 == 0 and D <= 128 and q_row_stride % 8 == 0
+    if fast and ctx.one_token_each and ctx.B * H <= DECODE_COUNTERS:
+        n_splits = decode_splits(ctx.B, Hkv, H // Hkv, block_table.shape[1])
+        partial = ctx.take((ctx.B_cap * H * MAX_DECODE_SPLITS * (D + 2),), torch.float32)   # sized by shape, not by lengths
+        attention_decode_bf16(q, q_row_stride, k_pages, v_pages, block_table, ctx.positions, out, partial,
+                              decode_counters(out.device), H, Hkv, D, n_splits, scale, window, ctx.err)
+        ctx.ws.give(partial)
+    elif fast and not ctx.capturing:
+        lens = ctx.host_cu_tokens[1:] - ctx.host_cu_tokens[:-1]
+        n_tiles = int(((lens + 63) // 64).sum())
+        attention_prefill_bf16(q, q_row_stride, k_pages, v_pages, block_table, ctx.positions, ctx.cu_tokens, n_tiles, out,
+                               H, Hkv, D, scale, window, ctx.err)
+    else:
+        attention_generic(q, q_row_stride, k_pages, v_pages, block_table, ctx.positions, ctx.seq_of_token, out,
+                          H, Hkv, D, scale, window, ctx.err)
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
