@@ -17,6 +17,18 @@ namespace {
 
 constexpr int DEC_WARPS = 4;
 
+__device__ __forceinline__ void dec_cp_async16(void* smem, const void* gmem) {
+    const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sa), "l"(gmem));
+}
+
+// One CTA iteration covers UNIT_PAGES cache pages (128 keys): all of their keys and values are fetched
+// into shared memory at once (every thread has several 16-byte copies in flight), then each warp works
+// on its own 32 keys.
+constexpr int UNIT_PAGES = 2;
+constexpr int UNIT_KEYS = UNIT_PAGES * VM_PAGE_TOKENS;
+static_assert(UNIT_KEYS == DEC_WARPS * 32, "one 32-key chunk per warp");
+
 template <int GM, int EPL>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, const __nv_bfloat16* __restrict__ kpages,
@@ -24,7 +36,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, const 
                    const int* __restrict__ positions, __nv_bfloat16* __restrict__ out, float* __restrict__ partial,
                    int* __restrict__ counters, int H, int Hkv, int D, float scale, int window, int n_pages,
                    int* __restrict__ err) {
-    extern __shared__ float sm[];                          // q [GM][D]; then per-warp results [DEC_WARPS][GM][D+2]
+    // shared: q [GM][D] float | per-warp results [DEC_WARPS][GM][D+2] float | K [128][D+8] bf16 | V [128][D+8] bf16
+    extern __shared__ __align__(16) float sm[];
     const int split = blockIdx.x, n_splits = gridDim.x;
     const int G = H / Hkv;
     const int groups_per_kv = (G + GM - 1) / GM;
@@ -36,16 +49,18 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, const 
     const int pos = positions[b];                          // one token per sequence: token index == sequence index
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int first_page = lo / VM_PAGE_TOKENS, last_page = pos / VM_PAGE_TOKENS;
-    const int pages = last_page - first_page + 1;
-    const int per_split = (pages + n_splits - 1) / n_splits;
-    const int page_a = first_page + split * per_split, page_b = min(last_page + 1, page_a + per_split);
+    const int units = (last_page - first_page) / UNIT_PAGES + 1;
+    const int per_split = (units + n_splits - 1) / n_splits;
+    const int unit_a = split * per_split, unit_b = min(units, unit_a + per_split);
+    const int DP = D + 8;                                  // padded row: an odd number of 16-byte units
     float* qs = sm;
     float* res = sm + GM * D;
+    __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(res + DEC_WARPS * GM * (D + 2));
+    __nv_bfloat16* sV = sK + UNIT_KEYS * DP;
     for (int i = threadIdx.x; i < ng * D; i += blockDim.x) {
         const int g = i / D, d = i - g * D;
         qs[g * D + d] = __bfloat162float(q[(size_t)b * q_row_stride + (size_t)(h0 + g) * D + d]) * scale;
     }
-    __syncthreads();
 
     float m[GM], l[GM], acc[GM][EPL];
 #pragma unroll
@@ -56,23 +71,41 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, const 
     }
     const size_t page_stride = (size_t)Hkv * VM_PAGE_TOKENS * D;
     const int* table = block_table + (size_t)b * max_blocks;
-    // each warp takes 32-key half pages: chunk c of the CTA's range covers keys page_a*64 + 32c ..
-    const int n_chunks = (page_b > page_a) ? (page_b - page_a) * 2 : 0;
-    for (int c = warp; c < n_chunks; c += DEC_WARPS) {
-        const int blk = page_a + (c >> 1);
-        const int base = blk * VM_PAGE_TOKENS + (c & 1) * 32;
-        if (base > pos || base + 31 < lo) continue;
-        const int page = (blk < max_blocks) ? table[blk] : -1;
-        if (page < 0 || page >= n_pages) { if (lane == 0 && err) atomicExch(err, 3); continue; }
-        const size_t tile = (size_t)page * page_stride + ((size_t)hk * VM_PAGE_TOKENS + (c & 1) * 32) * D;
+    const int CH = D / 8;                                  // 16-byte chunks per row
+    for (int unit = unit_a; unit < unit_b; ++unit) {
+        const int blk0 = first_page + unit * UNIT_PAGES;
+        __syncthreads();                                   // the previous unit's tiles (and qs, the first time) are settled
+        for (int pg = 0; pg < UNIT_PAGES; ++pg) {
+            const int blk = blk0 + pg;
+            if (blk > last_page) break;
+            const int page = (blk < max_blocks) ? table[blk] : -1;
+            if (page < 0 || page >= n_pages) { if (threadIdx.x == 0 && err) atomicExch(err, 3); continue; }
+            const __nv_bfloat16* kg = kpages + (size_t)page * page_stride + (size_t)hk * VM_PAGE_TOKENS * D;
+            const __nv_bfloat16* vg = vpages + (size_t)page * page_stride + (size_t)hk * VM_PAGE_TOKENS * D;
+            for (int c = threadIdx.x; c < VM_PAGE_TOKENS * CH; c += blockDim.x) {
+                const int r = c / CH, ch = c - r * CH;
+                dec_cp_async16(sK + (size_t)(pg * VM_PAGE_TOKENS + r) * DP + ch * 8, kg + (size_t)r * D + ch * 8);
+                dec_cp_async16(sV + (size_t)(pg * VM_PAGE_TOKENS + r) * DP + ch * 8, vg + (size_t)r * D + ch * 8);
+            }
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+        asm volatile("cp.async.wait_group 0;\n" ::);
+        __syncthreads();
+        const int base = blk0 * VM_PAGE_TOKENS + warp * 32;
+        if (base > pos || base + 31 < lo) continue;         // warp-uniform: none of this warp's keys is visible
+        {
+            const int blk = base / VM_PAGE_TOKENS;
+            const int page = (blk < max_blocks) ? table[blk] : -1;
+            if (page < 0 || page >= n_pages) continue;      // reported above; its tile was not loaded
+        }
         const int j = base + lane;
         const bool valid = (j >= lo && j <= pos);
         float s[GM];
 #pragma unroll
         for (int g = 0; g < GM; ++g) s[g] = 0.f;
         if (valid) {
-            const uint4* krow = reinterpret_cast<const uint4*>(kpages + tile + (size_t)lane * D);
-            for (int ch = 0; ch < D / 8; ++ch) {
+            const uint4* krow = reinterpret_cast<const uint4*>(sK + (size_t)(warp * 32 + lane) * DP);
+            for (int ch = 0; ch < CH; ++ch) {
                 const uint4 kv = krow[ch];
                 const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&kv);
 #pragma unroll
@@ -92,7 +125,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, const 
 #pragma unroll
         for (int g = 0; g < GM; ++g) {
             const float sv = valid ? s[g] : -INFINITY;
-            const float mn = fmaxf(m[g], vm_warp_max(sv));           // the chunk holds at least one valid key
+            const float mn = fmaxf(m[g], vm_warp_max(sv));           // the chunk holds at least one visible key
             p[g] = valid ? expf(sv - mn) : 0.f;
             const float alpha = expf(m[g] - mn);
             l[g] = l[g] * alpha + vm_warp_sum(p[g]);
@@ -103,7 +136,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, const 
         const int cnt = min(32, pos - base + 1);
         const int first = max(0, lo - base);
         for (int jj = first; jj < cnt; ++jj) {
-            const __nv_bfloat16* vrow = vpages + tile + (size_t)jj * D;
+            const __nv_bfloat16* vrow = sV + (size_t)(warp * 32 + jj) * DP;
             float vv[EPL];
 #pragma unroll
             for (int i = 0; i < EPL; ++i) { const int d = lane + 32 * i; vv[i] = (d < D) ? __bfloat162float(vrow[d]) : 0.f; }
@@ -115,6 +148,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, const 
             }
         }
     }
+    __syncthreads();
     // ---- join the CTA's warps
     const int RW = D + 2;
 #pragma unroll
@@ -177,6 +211,14 @@ int launch_decode(int epl, dim3 grid, size_t smem, cudaStream_t stream, const __
                   float scale, int window, int n_pages, int* err) {
 #define VM_DEC_CASE(E)                                                                                               \
     case E:                                                                                                          \
+        if (smem > 48 * 1024) {                                                                                      \
+            static bool configured = false;                                                                          \
+            if (!configured) {                                                                                       \
+                cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<GM, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
+                if (e != cudaSuccess) return (int)e;                                                                 \
+                configured = true;                                                                                   \
+            }                                                                                                        \
+        }                                                                                                            \
         attn_decode_kernel<GM, E><<<grid, DEC_WARPS * 32, smem, stream>>>(q, q_row_stride, kpages, vpages, block_table, \
             max_blocks, positions, out, partial, counters, H, Hkv, D, scale, window, n_pages, err);                   \
         break;
@@ -207,7 +249,8 @@ VM_API int vm_attention_decode_bf16(const void* q, int q_row_stride, const void*
     const int GM = G <= 1 ? 1 : (G <= 2 ? 2 : (G <= 4 ? 4 : 8));
     const int groups = (G + GM - 1) / GM;
     dim3 grid(n_splits, Hkv * groups, B);
-    const size_t smem = ((size_t)GM * D + (size_t)DEC_WARPS * GM * (D + 2)) * sizeof(float);
+    const size_t smem = ((size_t)GM * D + (size_t)DEC_WARPS * GM * (D + 2)) * sizeof(float)
+                        + 2 * (size_t)UNIT_KEYS * (D + 8) * sizeof(__nv_bfloat16);
     const int epl = (D + 31) / 32;
     const __nv_bfloat16 *qq = (const __nv_bfloat16*)q, *kk = (const __nv_bfloat16*)kpages, *vv = (const __nv_bfloat16*)vpages;
     switch (GM) {
