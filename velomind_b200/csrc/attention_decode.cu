@@ -260,3 +260,52 @@ VM_API int vm_attention_decode_bf16(const void* q, int q_row_stride, const void*
         default: return launch_decode<8>(epl, grid, smem, stream, qq, q_row_stride, kk, vv, block_table, max_blocks, positions, (__nv_bfloat16*)out, partial, counters, H, Hkv, D, scale, window, n_pages, err);
     }
 }
+
+// ------------------------------------------------------------------------------------------------
+// The variant that allocates nothing (declared and explained in velomind_no_alloc.h).
+#include "velomind_no_alloc.h"
+
+namespace {
+
+// The scratch of the no-alloc entry point.  In HOST code this name is only a handle for the symbol: it is
+// not a device address and must never be passed to a kernel; the address comes from cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char vm_no_alloc_scratch[VM_NO_ALLOC_SCRATCH_BYTES];
+
+constexpr int NO_ALLOC_MAX_DEVICES = 64;
+unsigned char* no_alloc_base[NO_ALLOC_MAX_DEVICES] = {};     // per device, looked up on the first call there
+
+long long no_alloc_counter_bytes(int B, int H) { return (((long long)B * H * 4) + 255) / 256 * 256; }
+
+}  // namespace
+
+VM_API long long vm_attention_decode_no_alloc_bytes(int B, int H, int D, int n_splits) {
+    return no_alloc_counter_bytes(B, H) + 4ll * B * H * n_splits * (D + 2);
+}
+
+VM_API int vm_attention_decode_bf16_no_alloc(const void* q, int q_row_stride, const void* kpages, const void* vpages,
+                                             const int* block_table, int max_blocks, const int* positions, void* out,
+                                             int B, int H, int Hkv, int D, int n_splits, float scale, int window,
+                                             int n_pages, int* err, cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (H <= 0 || D <= 0 || n_splits < 1) return VM_ERR_BAD_ARG;
+    if (vm_attention_decode_no_alloc_bytes(B, H, D, n_splits) > VM_NO_ALLOC_SCRATCH_BYTES) return VM_NO_ALLOC_TOO_LARGE;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= NO_ALLOC_MAX_DEVICES) return VM_ERR_UNSUPPORTED;
+    if (no_alloc_base[dev] == nullptr) {
+        // once per device, with that device current: the symbol's address ON THIS DEVICE
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, vm_no_alloc_scratch);
+        if (e != cudaSuccess) return (int)e;
+        no_alloc_base[dev] = static_cast<unsigned char*>(p);
+    }
+    unsigned char* base = no_alloc_base[dev];
+    int* counters = reinterpret_cast<int*>(base);
+    float* partial = reinterpret_cast<float*>(base + no_alloc_counter_bytes(B, H));
+    // the array keeps the last call's contents: the counters must start at zero
+    e = cudaMemsetAsync(counters, 0, (size_t)no_alloc_counter_bytes(B, H), stream);
+    if (e != cudaSuccess) return (int)e;
+    return vm_attention_decode_bf16(q, q_row_stride, kpages, vpages, block_table, max_blocks, positions, out, partial,
+                                    counters, B, H, Hkv, D, n_splits, scale, window, n_pages, err, stream);
+}
