@@ -68,6 +68,13 @@ class DecoderModel:
             part.bind({name: tensors[prefix + name] for name in part.weight_specs()}, bc)
         self.dtype, self.device = dtype, torch.device(device)
 
+    @property
+    def graph_safe(self) -> bool:
+        """True if every part says its decode step may be recorded into a CUDA graph."""
+        parts = [p for _, p in self.named_parts()] + [l.block for l in self.layers]
+        parts += [l.mixer.position for l in self.layers if hasattr(l.mixer, "position")]
+        return all(getattr(p, "graph_safe", False) for p in parts)
+
     # ---- cache needs, one per schedule position
     def cache_needs(self) -> List[Optional[CacheNeed]]:
         out: List[Optional[CacheNeed]] = []

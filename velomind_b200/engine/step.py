@@ -182,7 +182,7 @@ class Engine:
         self._desc: Dict[Tuple, Descriptors] = {}
         self._logits: Optional[torch.Tensor] = None
         self._graphs: Dict[Tuple, "torch.cuda.CUDAGraph"] = {}
-        self.use_graphs = GRAPHS_DEFAULT if use_graphs is None else bool(use_graphs)
+        self.use_graphs = (GRAPHS_DEFAULT if use_graphs is None else bool(use_graphs)) and model.graph_safe
         self.graphs_captured = 0
         self.steps_run = 0
 

@@ -26,6 +26,8 @@ class GroupedQueryAttention(Part):
     `window` > 0 limits a query to the last `window` keys (itself included); 0 means all earlier keys.
     """
 
+    graph_safe = True
+
     def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, position: PartSpec,
                  window: int = 0, scale: float | None = None):
         if heads % kv_heads:

@@ -50,6 +50,11 @@ class BindContext:
 
 
 class Part:
+    # True only for parts whose `forward` launches the same work for every step of the same SHAPE (token,
+    # sequence and row counts, table widths) and reads everything else from device memory: such a step can
+    # be recorded into a CUDA graph.  A part that looks at host copies of the step (slots, lengths) says False.
+    graph_safe = False
+
     def weight_specs(self) -> Dict[str, WeightSpec]:
         return {}
 

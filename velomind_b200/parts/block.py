@@ -11,6 +11,8 @@ class PreNormBlock:
     `forward` takes the delta the previous layer left pending and returns its own last delta pending.
     """
 
+    graph_safe = True
+
     def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm):
         self.mixer, self.feed_forward = mixer, feed_forward
         self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm

@@ -13,6 +13,8 @@ from .registry import register_part
 class TokenEmbedding(Part):
     """h[t, :] = table[token[t], :] into the float32 residual stream (src/cpu/ops/embedding.cpp:27-32)."""
 
+    graph_safe = True
+
     def __init__(self, vocab: int, hidden: int):
         self.vocab, self.hidden = int(vocab), int(hidden)
         self.table = None
@@ -31,6 +33,8 @@ class LinearHead(Part):
     """logits = x W^T in float32.  `tied_to` names the tensor that stands in when the checkpoint has no
     head of its own (examples/smollm2/model_loader.cpp:124-158: lm_head.weight if present, else the
     embedding when tied); the device tensor is then shared with the embedding, not copied."""
+
+    graph_safe = True
 
     def __init__(self, vocab: int, hidden: int, tied_to: str | None = None):
         self.vocab, self.hidden, self.tied_to = int(vocab), int(hidden), tied_to

@@ -14,6 +14,8 @@ class SwiGLU(Part):
     """down(silu(gate(x)) * up(x)), no biases (examples/common/llama/llama_graph.cpp:22-28,122-138).
     gate and up are one stacked product; the activation kernel reads both halves."""
 
+    graph_safe = True
+
     def __init__(self, hidden: int, intermediate: int):
         self.hidden, self.intermediate = int(hidden), int(intermediate)
         self.gate_up = self.down = None

@@ -13,6 +13,8 @@ class RMSNorm(Part):
     """y = x / sqrt(mean(x^2) + eps) * weight, statistics in float32 (src/cpu/ops/rmsnorm.cpp:42-59).
     The residual add that precedes a norm in a pre-norm block is fused into the same kernel."""
 
+    graph_safe = True
+
     def __init__(self, size: int, eps: float):
         self.size = int(size)
         self.eps = float(eps)

@@ -14,6 +14,8 @@ class RotaryHalfSplit(Part):
     (examples/common/llama/llama_rope_mask.cpp:17-19); the angle pos * inv_freq[j] and its sine and cosine
     are computed in float32 on the device."""
 
+    graph_safe = True
+
     def __init__(self, head_dim: int, theta: float, rotary_dim: int | None = None):
         self.head_dim = int(head_dim)
         self.rotary_dim = int(rotary_dim) if rotary_dim is not None else self.head_dim
@@ -35,6 +37,8 @@ class RotaryHalfSplit(Part):
 
 class NoPosition(Part):
     """No position encoding: queries and keys pass unrotated."""
+
+    graph_safe = True
 
     def __init__(self, head_dim: int = 0):
         self.head_dim = head_dim
