@@ -297,3 +297,85 @@ def test_sampled_distribution():
              torch.zeros(R, dtype=torch.int64, device=DEV), out)
     freq = np.bincount(out.cpu().numpy(), minlength=5) / R
     assert freq[2:].sum() == 0 and abs(freq[0] - 2 / 3) < 0.03       # nucleus of 0.7 = the two most probable tokens
+
+
+# ------------------------------------------------------------------------------------------ weight-streaming products
+def _bf(t):
+    return t.to(torch.bfloat16)
+
+
+def _rms_ref(h, w, eps):
+    return _bf(torch.from_numpy(P.rmsnorm(h.numpy(), w.numpy(), eps)))
+
+
+@pytest.mark.parametrize("M", [1, 8, 17, 64])
+@pytest.mark.parametrize("N,K", [(72, 64), (576, 576), (200, 160), (576, 1536), (4752, 96)])
+def test_skinny_linear(M, N, K):
+    o = ops()
+    x = _bf(torch.randn(M, K, generator=_gen(M + N)))
+    w = _bf(torch.randn(N, K, generator=_gen(K)) * 0.1)
+    want = x.float() @ w.float().t()
+    tol = 2e-2 * float(want.abs().max())
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    o.skinny_linear(x.to(DEV), None, w.to(DEV), out)
+    assert (out.float().cpu() - want).abs().max() <= tol
+    out32 = torch.full((M, N + 3), float("nan"), device=DEV)                 # a strided float32 output (logits)
+    o.skinny_linear(x.to(DEV), None, w.to(DEV), out32[:, :N])
+    assert (out32[:, :N].cpu() - want).abs().max() <= 1e-3 * max(1.0, float(want.abs().max()))
+    assert torch.isnan(out32[:, N:]).all()
+    h = torch.randn(M, N, generator=_gen(5))
+    hd = h.to(DEV)
+    o.skinny_linear(x.to(DEV), None, w.to(DEV), None, residual=hd)
+    assert (hd.cpu() - (h + want)).abs().max() <= 1e-3 * max(1.0, float(want.abs().max()))
+    # the norm as prologue
+    hres = torch.randn(M, K, generator=_gen(6)) * 2
+    nw = 1 + 0.1 * torch.randn(K, generator=_gen(7))
+    xn = _rms_ref(hres, nw, 1e-5)
+    want_n = xn.float() @ w.float().t()
+    o.skinny_linear(hres.to(DEV), (nw.to(DEV), 1e-5), w.to(DEV), out)
+    assert (out.float().cpu() - want_n).abs().max() <= 2e-2 * float(want_n.abs().max())
+
+
+@pytest.mark.parametrize("M,I,K", [(3, 192, 64), (8, 1536, 576), (33, 160, 96), (64, 1000, 1536)])
+def test_skinny_swiglu(M, I, K):
+    o = ops()
+    hres = torch.randn(M, K, generator=_gen(M)) * 2
+    nw = 1 + 0.1 * torch.randn(K, generator=_gen(I))
+    w = _bf(torch.randn(2 * I, K, generator=_gen(K)) * 0.2)
+    xn = _rms_ref(hres, nw, 1e-6)
+    gu = xn.float() @ w.float().t()
+    want = torch.from_numpy(P.swiglu(gu[:, :I].numpy(), gu[:, I:].numpy()))
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    o.skinny_swiglu(hres.to(DEV), (nw.to(DEV), 1e-6), w.to(DEV), out)
+    assert (out.float().cpu() - want).abs().max() <= 2e-2 * float(want.abs().max())
+    o.skinny_swiglu(xn.to(DEV), None, w.to(DEV), out)
+    assert (out.float().cpu() - want).abs().max() <= 2e-2 * float(want.abs().max())
+
+
+@pytest.mark.parametrize("H,Hkv,D,K,rot", [(4, 2, 16, 64, 16), (3, 1, 32, 96, 32), (9, 3, 64, 576, 64), (5, 5, 48, 160, 0), (2, 1, 128, 256, 128)])
+def test_skinny_qkv_rope(H, Hkv, D, K, rot):
+    o = ops()
+    lens_before, new = [3, 70, 0], [5, 1, 20]
+    T = sum(new)
+    hres = torch.randn(T, K, generator=_gen(H)) * 2
+    nw = 1 + 0.1 * torch.randn(K, generator=_gen(D))
+    w = _bf(torch.randn((H + 2 * Hkv) * D, K, generator=_gen(K)) * 0.2)
+    positions = torch.cat([torch.arange(a, a + n) for a, n in zip(lens_before, new)]).int()
+    seq = torch.cat([torch.full((n,), s) for s, n in enumerate(new)]).int()
+    table = torch.tensor([[5, -1], [2, 7], [0, 3]], dtype=torch.int32)
+    inv_freq = torch.from_numpy((1.0 / np.power(np.float32(5000.0), np.arange(rot // 2, dtype=np.float32) * 2 / max(rot, 1))).astype(np.float32)) if rot else None
+    xn = _rms_ref(hres, nw, 1e-5)
+    qkv = (xn.float() @ w.float().t())                                     # float32 reference all the way
+    kp = torch.zeros(8, Hkv, 64, D); vp = torch.zeros_like(kp)
+    E.rope_kv_write(qkv, positions, seq, table, inv_freq, rot, kp, vp, H, Hkv, D)
+    dq = torch.full((T, H * D), float("nan"), dtype=torch.bfloat16, device=DEV)
+    dk = torch.zeros(8, Hkv, 64, D, dtype=torch.bfloat16, device=DEV); dv = torch.zeros_like(dk)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    o.skinny_qkv_rope(hres.to(DEV), (nw.to(DEV), 1e-5), w.to(DEV), dq, positions.to(DEV), seq.to(DEV), table.to(DEV),
+                      None if inv_freq is None else inv_freq.to(DEV), rot, dk, dv, H, Hkv, D, err)
+    assert int(err.item()) == 0
+    scale = float(qkv.abs().max())
+    assert (dq.float().cpu() - qkv[:, : H * D]).abs().max() <= 2e-2 * scale
+    assert (dk.float().cpu() - kp).abs().max() <= 2e-2 * scale
+    assert (dv.float().cpu() - vp).abs().max() <= 2e-2 * scale
+    assert float(dk.float().abs().sum()) > 0

@@ -1,0 +1,317 @@
+// Weight-streaming matrix products for few rows (M <= 64: decode steps and other small steps), bfloat16,
+// with the neighbouring elementwise work fused in so that a decode layer is five launches:
+//
+//   prologue   none      A is bf16 [M, K]
+//              rmsnorm   A = rmsnorm(h) * w from the float32 residual h [M, K] (src/cpu/ops/rmsnorm.cpp:42-59);
+//                        h * w is staged as bf16 and the row's 1/rms multiplies the float32 sums afterwards
+//   epilogue   store     out[M, N] = A W^T            (bf16, or float32 for logits)
+//              residual  h[M, N] += A W^T             (float32 residual stream; llama_graph.cpp:225-226,137)
+//              swiglu    out[M, I] = silu(A Wg^T) * (A Wu^T), W = [Wg; Wu] stacked (llama_graph.cpp:22-28)
+//              rope_kv   W = [Wq; Wk; Wv] stacked: rotate q and k (rotary_embedding.cpp:30-44), write q to
+//                        out [M, H*D], k and v into the paged cache (llama_graph.cpp:210-215)
+//
+// y = x W^T with W [N, K] row-major (K contiguous).  Every weight byte is read once per step, so the kernel
+// is organised around the weight stream: a CTA owns 8 or 16 output columns, its four warps split K, and
+// each thread fetches 16 contiguous bytes of a weight row per 32-wide k block straight from global memory
+// into the B fragments of two mma.sync m16n8k16 (bf16 in, float32 accumulate).  The k indices inside a
+// block are permuted the same way for A and B, which leaves the dot product unchanged and makes the
+// 16-byte loads possible.  A (at most 64 rows) sits in shared memory.
+//
+// Sizes: K % 32 == 0, N % 8 == 0 (16 for the two-tile forms), head size % 16 == 0, I % 8 == 0; M <= 64.
+// Anything else is refused with VM_ERR_UNSUPPORTED and the caller uses the library product.
+#include "mma.cuh"
+
+namespace {
+
+enum : int { PRO_NONE = 0, PRO_RMSNORM = 1 };
+enum : int { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3, EPI_ROPE_KV = 4 };
+
+constexpr int SK_WARPS = 4;
+constexpr int SK_THREADS = SK_WARPS * 32;
+
+struct SkinnyParams {
+    const void* A;               // bf16 [M, K] (PRO_NONE) or float32 residual [M, K] (PRO_RMSNORM)
+    const float* norm_w;         // [K]
+    float eps;
+    const __nv_bfloat16* W;      // [N, K]
+    int M, N, K;
+    int pro, epi, tiles;         // tiles: n8 tiles per CTA (1 or 2)
+    void* out;                   // bf16 or float32 [M, out_stride]
+    int out_stride;
+    float* h;                    // residual [M, N]
+    int I;                       // swiglu: rows of Wg (and of Wu)
+    // rope_kv
+    const int* positions; const int* seq_of_token; const int* block_table; int max_blocks;
+    const float* inv_freq; int rot_dim;
+    __nv_bfloat16* kpages; __nv_bfloat16* vpages; int H, Hkv, D, n_pages; int* err;
+    int kc;                      // k chunk staged in shared memory at a time (multiple of 32)
+    int row_bytes;               // shared-memory row pitch of the A tile, == 64 mod 128
+};
+
+template <int MT>
+__global__ void __launch_bounds__(SK_THREADS)
+skinny_gemm_kernel(const SkinnyParams p) {
+    constexpr int ROWS = 16 * MT;
+    extern __shared__ __align__(16) unsigned char smem[];
+    unsigned char* sA = smem;                                              // ROWS x row_bytes
+    float* red = reinterpret_cast<float*>(smem + (size_t)ROWS * p.row_bytes);   // [SK_WARPS][ROWS][16]
+    float* inv = red + SK_WARPS * ROWS * 16;                               // [ROWS]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+
+    // ---- which output columns
+    int nA, nB, head = 0;
+    if (p.epi == EPI_SWIGLU) { nA = 8 * blockIdx.x; nB = p.I + nA; }
+    else if (p.epi == EPI_ROPE_KV) {
+        const int per_head = p.D / 16;
+        head = blockIdx.x / per_head;
+        const int sub = blockIdx.x - head * per_head;
+        if (head < p.H + p.Hkv && p.rot_dim > 0) { nA = head * p.D + 8 * sub; nB = nA + p.D / 2; }   // rotary pair (j, j + D/2)
+        else { nA = head * p.D + 16 * sub; nB = nA + 8; }
+    }
+    else if (p.tiles == 2) { nA = 16 * blockIdx.x; nB = nA + 8; }
+    else { nA = 8 * blockIdx.x; nB = nA; }
+    const __nv_bfloat16* wA = p.W + (size_t)(nA + g) * p.K;
+    const __nv_bfloat16* wB = p.W + (size_t)(nB + g) * p.K;
+    const bool two = (p.tiles == 2);
+
+    // ---- weight fragments do not depend on A: the first group of this warp's k blocks is requested before
+    //      anything else, so that its DRAM latency overlaps the staging of A
+    constexpr int PF = 6;                                   // k blocks in flight per warp
+    uint4 wa[PF], wb[PF];
+    auto issue = [&](int kc0, int blocks, int group) {
+#pragma unroll
+        for (int u = 0; u < PF; ++u) {
+            const int b = warp + SK_WARPS * (group * PF + u);
+            if (b < blocks) {
+                const int k = kc0 + 32 * b + 8 * t4;
+                wa[u] = *reinterpret_cast<const uint4*>(wA + k);
+                if (two) wb[u] = *reinterpret_cast<const uint4*>(wB + k);
+            }
+        }
+    };
+    issue(0, min(p.kc, p.K) / 32, 0);
+
+    float acc[MT][2][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int t = 0; t < 2; ++t) acc[mt][t][0] = acc[mt][t][1] = acc[mt][t][2] = acc[mt][t][3] = 0.f;
+
+    for (int kc0 = 0; kc0 < p.K; kc0 += p.kc) {
+        const int kc = min(p.kc, p.K - kc0);
+        if (kc0 > 0) __syncthreads();                       // the previous chunk has been consumed
+        // ---- stage A[:, kc0 : kc0+kc] as bf16
+        if (p.pro == PRO_NONE) {
+            const __nv_bfloat16* A = static_cast<const __nv_bfloat16*>(p.A);
+            const int chunks = kc / 8;
+            for (int c = tid; c < ROWS * chunks; c += SK_THREADS) {
+                const int r = c / chunks, ch = c - r * chunks;
+                unsigned char* dst = sA + (size_t)r * p.row_bytes + ch * 16;
+                if (r < p.M) vm_cp_async16(dst, A + (size_t)r * p.K + kc0 + ch * 8);
+                else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+            }
+            vm_cp_async_commit();
+            vm_cp_async_wait_all();
+        } else {
+            // x * w as bf16 (the row's 1/rms is applied to the float32 sums in the epilogue: a row scale
+            // commutes with the product); a warp owns whole rows and sums their squares on the way
+            const float* h = static_cast<const float*>(p.A);
+            const int quads = kc / 4;
+            for (int r = warp; r < ROWS; r += SK_WARPS) {
+                unsigned char* dst = sA + (size_t)r * p.row_bytes;
+                if (r >= p.M) {
+                    for (int qd = lane; qd < quads; qd += 32) *reinterpret_cast<uint2*>(dst + qd * 8) = make_uint2(0u, 0u);
+                    continue;
+                }
+                const float4* hrow = reinterpret_cast<const float4*>(h + (size_t)r * p.K + kc0);
+                const float4* wrow = reinterpret_cast<const float4*>(p.norm_w + kc0);
+                float ss = 0.f;
+                for (int q0 = lane; q0 < quads; q0 += 32 * 4) {
+                    float4 x[4], w[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int qd = q0 + 32 * u;
+                        if (qd < quads) { x[u] = hrow[qd]; w[u] = wrow[qd]; }
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int qd = q0 + 32 * u;
+                        if (qd < quads) {
+                            ss += x[u].x * x[u].x + x[u].y * x[u].y + x[u].z * x[u].z + x[u].w * x[u].w;
+                            uint2 v;
+                            v.x = vm_pack_bf16(x[u].x * w[u].x, x[u].y * w[u].y);
+                            v.y = vm_pack_bf16(x[u].z * w[u].z, x[u].w * w[u].w);
+                            *reinterpret_cast<uint2*>(dst + qd * 8) = v;
+                        }
+                    }
+                }
+                ss = vm_warp_sum(ss);
+                if (lane == 0) inv[r] = (kc0 == 0 ? 0.f : inv[r]) + ss;        // sum of squares so far
+            }
+        }
+        __syncthreads();
+        // ---- this warp's k blocks of the chunk: block b covers k = kc0 + 32 b .. + 31
+        const int blocks = kc / 32;
+        for (int group = 0; warp + SK_WARPS * group * PF < blocks; ++group) {
+            if (group > 0 || kc0 > 0) issue(kc0, blocks, group);
+#pragma unroll
+            for (int u = 0; u < PF; ++u) {
+                const int b = warp + SK_WARPS * (group * PF + u);
+                if (b < blocks) {
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        const uint4 a_lo = *reinterpret_cast<const uint4*>(sA + (size_t)(mt * 16 + g) * p.row_bytes + (32 * b + 8 * t4) * 2);
+                        const uint4 a_hi = *reinterpret_cast<const uint4*>(sA + (size_t)(mt * 16 + g + 8) * p.row_bytes + (32 * b + 8 * t4) * 2);
+                        vm_mma_bf16_16816(acc[mt][0], a_lo.x, a_hi.x, a_lo.y, a_hi.y, wa[u].x, wa[u].y);
+                        vm_mma_bf16_16816(acc[mt][0], a_lo.z, a_hi.z, a_lo.w, a_hi.w, wa[u].z, wa[u].w);
+                        if (two) {
+                            vm_mma_bf16_16816(acc[mt][1], a_lo.x, a_hi.x, a_lo.y, a_hi.y, wb[u].x, wb[u].y);
+                            vm_mma_bf16_16816(acc[mt][1], a_lo.z, a_hi.z, a_lo.w, a_hi.w, wb[u].z, wb[u].w);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    // ---- join the warps' partial sums: red[warp][row][col], col 0..7 = tile A, 8..15 = tile B
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int t = 0; t < 2; ++t)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int row = mt * 16 + g + 8 * (e >> 1), col = t * 8 + 2 * t4 + (e & 1);
+                red[((size_t)warp * ROWS + row) * 16 + col] = acc[mt][t][e];
+            }
+    __syncthreads();
+    for (int item = tid; item < ROWS * 8; item += SK_THREADS) {
+        const int row = item >> 3, c = item & 7;
+        if (row >= p.M) continue;
+        float vA = 0.f, vB = 0.f;
+#pragma unroll
+        for (int w = 0; w < SK_WARPS; ++w) {
+            vA += red[((size_t)w * ROWS + row) * 16 + c];
+            vB += red[((size_t)w * ROWS + row) * 16 + 8 + c];
+        }
+        if (p.pro == PRO_RMSNORM) {
+            const float rs = 1.0f / sqrtf(inv[row] / (float)p.K + p.eps);       // inv[] holds the row's sum of squares
+            vA *= rs; vB *= rs;
+        }
+        switch (p.epi) {
+            case EPI_STORE_BF16: {
+                __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + (size_t)row * p.out_stride;
+                o[nA + c] = __float2bfloat16_rn(vA);
+                if (two) o[nB + c] = __float2bfloat16_rn(vB);
+            } break;
+            case EPI_STORE_F32: {
+                float* o = static_cast<float*>(p.out) + (size_t)row * p.out_stride;
+                o[nA + c] = vA;
+                if (two) o[nB + c] = vB;
+            } break;
+            case EPI_RESIDUAL: {
+                float* o = p.h + (size_t)row * p.N;
+                o[nA + c] += vA;
+                if (two) o[nB + c] += vB;
+            } break;
+            case EPI_SWIGLU: {
+                const float sig = 1.0f / (1.0f + expf(-vA));
+                static_cast<__nv_bfloat16*>(p.out)[(size_t)row * p.out_stride + nA + c] = __float2bfloat16_rn((sig * vA) * vB);
+            } break;
+            case EPI_ROPE_KV: {
+                const int pos = p.positions[row];
+                float ya = vA, yb = vB;
+                int da, db;                                 // the two columns' places inside the head
+                if (head < p.H + p.Hkv && p.rot_dim > 0) {
+                    da = (nA - head * p.D) + c; db = da + p.D / 2;
+                    float s, co;
+                    sincosf((float)pos * p.inv_freq[da], &s, &co);
+                    ya = vA * co - vB * s;
+                    yb = vB * co + vA * s;
+                } else { da = (nA - head * p.D) + c; db = da + 8; }
+                if (head < p.H) {
+                    __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + (size_t)row * p.out_stride + (size_t)head * p.D;
+                    o[da] = __float2bfloat16_rn(ya); o[db] = __float2bfloat16_rn(yb);
+                } else if (p.kpages != nullptr) {
+                    const int blk = pos / VM_PAGE_TOKENS;
+                    const int page = (blk < p.max_blocks) ? p.block_table[(size_t)p.seq_of_token[row] * p.max_blocks + blk] : -1;
+                    if (page < 0 || page >= p.n_pages) { if (p.err) atomicExch(p.err, 2); break; }
+                    const bool is_k = head < p.H + p.Hkv;
+                    const int hk = is_k ? head - p.H : head - p.H - p.Hkv;
+                    __nv_bfloat16* dst = (is_k ? p.kpages : p.vpages) + (size_t)page * ((size_t)p.Hkv * VM_PAGE_TOKENS * p.D)
+                                         + ((size_t)hk * VM_PAGE_TOKENS + pos % VM_PAGE_TOKENS) * p.D;
+                    dst[da] = __float2bfloat16_rn(ya); dst[db] = __float2bfloat16_rn(yb);
+                }
+            } break;
+        }
+    }
+}
+
+int skinny_launch(SkinnyParams p, int grid, cudaStream_t stream) {
+    if (p.M <= 0 || grid <= 0) return 0;
+    if (p.M > 64 || p.K % 32 != 0 || p.K <= 0) return VM_ERR_UNSUPPORTED;
+    const int mt = (p.M + 15) / 16;
+    const int MT = mt <= 1 ? 1 : (mt <= 2 ? 2 : 4);
+    const int rows = 16 * MT;
+    // A chunk in shared memory: at most ~96 KB, rows of kc bf16 plus padding to a pitch == 64 (mod 128) bytes
+    int kc = p.K;
+    const int cap = (96 * 1024) / (rows * 2) / 128 * 128;
+    if (kc > cap) kc = cap;
+    p.kc = kc;
+    int pitch = kc * 2;
+    pitch += ((64 - pitch % 128) + 128) % 128;
+    p.row_bytes = pitch;
+    const size_t smem = (size_t)rows * pitch + (size_t)SK_WARPS * rows * 16 * sizeof(float) + rows * sizeof(float);
+#define VM_SK_CASE(X)                                                                                                 \
+    case X: {                                                                                                         \
+        static size_t configured = 0;                                                                                 \
+        if (smem > 48 * 1024 && smem > configured) {                                                                  \
+            cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<X>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); \
+            if (e != cudaSuccess) return (int)e;                                                                      \
+            configured = 160 * 1024;                                                                                  \
+        }                                                                                                             \
+        skinny_gemm_kernel<X><<<grid, SK_THREADS, smem, stream>>>(p);                                                 \
+    } break;
+    switch (MT) { VM_SK_CASE(1) VM_SK_CASE(2) VM_SK_CASE(4) }
+#undef VM_SK_CASE
+    return vm_launch_status();
+}
+
+}  // namespace
+
+// out = A W^T (pro 0) or rmsnorm(h) W^T (pro 1); out bf16 (out_f32 0) or float32 (1); or h += ... (residual 1).
+VM_API int vm_skinny_linear(const void* A, int pro, const float* norm_w, float eps, const void* W, int M, int N, int K,
+                            void* out, int out_stride, int out_f32, float* residual_h, cudaStream_t stream) {
+    if (N % 8 != 0) return VM_ERR_UNSUPPORTED;
+    SkinnyParams p{};
+    p.A = A; p.pro = pro; p.norm_w = norm_w; p.eps = eps; p.W = (const __nv_bfloat16*)W; p.M = M; p.N = N; p.K = K;
+    p.out = out; p.out_stride = out_stride; p.h = residual_h;
+    p.epi = residual_h ? EPI_RESIDUAL : (out_f32 ? EPI_STORE_F32 : EPI_STORE_BF16);
+    p.tiles = (N % 16 == 0 && N / 16 >= 148) ? 2 : 1;
+    return skinny_launch(p, p.tiles == 2 ? N / 16 : N / 8, stream);
+}
+
+// out[M, I] = silu(x Wg^T) * (x Wu^T) with x = A (pro 0) or rmsnorm(h) (pro 1); W = [Wg; Wu] is [2I, K].
+VM_API int vm_skinny_swiglu(const void* A, int pro, const float* norm_w, float eps, const void* W, int M, int I, int K,
+                            void* out, cudaStream_t stream) {
+    if (I % 8 != 0) return VM_ERR_UNSUPPORTED;
+    SkinnyParams p{};
+    p.A = A; p.pro = pro; p.norm_w = norm_w; p.eps = eps; p.W = (const __nv_bfloat16*)W; p.M = M; p.N = 2 * I; p.K = K;
+    p.out = out; p.out_stride = I; p.I = I; p.epi = EPI_SWIGLU; p.tiles = 2;
+    return skinny_launch(p, I / 8, stream);
+}
+
+// q_out[M, H*D] = rope(x Wq^T); rope(x Wk^T) and x Wv^T go to the cache pages; W = [Wq; Wk; Wv] is [(H+2Hkv)*D, K].
+// rot_dim must be 0 (no rotation) or D.  kpages == nullptr: nothing is cached.
+VM_API int vm_skinny_qkv_rope(const void* A, int pro, const float* norm_w, float eps, const void* W, int M, int K,
+                              void* q_out, const int* positions, const int* seq_of_token, const int* block_table,
+                              int max_blocks, const float* inv_freq, int rot_dim, void* kpages, void* vpages, int H, int Hkv,
+                              int D, int n_pages, int* err, cudaStream_t stream) {
+    if (D % 16 != 0 || !(rot_dim == 0 || rot_dim == D) || (rot_dim > 0 && inv_freq == nullptr)) return VM_ERR_UNSUPPORTED;
+    SkinnyParams p{};
+    p.A = A; p.pro = pro; p.norm_w = norm_w; p.eps = eps; p.W = (const __nv_bfloat16*)W; p.M = M; p.N = (H + 2 * Hkv) * D; p.K = K;
+    p.out = q_out; p.out_stride = H * D; p.epi = EPI_ROPE_KV; p.tiles = 2;
+    p.positions = positions; p.seq_of_token = seq_of_token; p.block_table = block_table; p.max_blocks = max_blocks;
+    p.inv_freq = inv_freq; p.rot_dim = rot_dim; p.kpages = (__nv_bfloat16*)kpages; p.vpages = (__nv_bfloat16*)vpages;
+    p.H = H; p.Hkv = Hkv; p.D = D; p.n_pages = n_pages; p.err = err;
+    return skinny_launch(p, (H + 2 * Hkv) * (D / 16), stream);
+}

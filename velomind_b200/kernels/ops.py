@@ -221,6 +221,58 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
         torch.mm(x, weight.t(), out_dtype=out.dtype, out=out)
 
 
+SKINNY_MAX_ROWS = 64
+SKINNY_NORM_ROWS = 16      # up to this many rows the norm is fused into the product that follows it
+
+
+def skinny_ok(M: int, K: int, weight: torch.Tensor) -> bool:
+    """True if the weight-streaming kernels take this product (few rows, bfloat16, K a multiple of 32)."""
+    return 0 < M <= SKINNY_MAX_ROWS and K % 32 == 0 and weight.dtype == torch.bfloat16 and weight.is_contiguous()
+
+
+def _norm_args(norm):
+    if norm is None:
+        return 0, None, 0.0
+    weight, eps = norm
+    return 1, weight, float(eps)
+
+
+def skinny_linear(x: torch.Tensor, norm, weight: torch.Tensor, out: Optional[torch.Tensor],
+                  residual: Optional[torch.Tensor] = None) -> None:
+    """out = x' W^T (bf16 or float32 out), or residual += x' W^T (float32), for M <= 64 rows.
+    x' = x (bf16 [M, K]) when `norm` is None, else rmsnorm(x) * norm[0] with eps norm[1] from x float32 [M, K]."""
+    M, K = x.shape
+    N = weight.shape[0]
+    pro, nw, eps = _norm_args(norm)
+    _check(library().vm_skinny_linear(_ptr(_contig(x, "x")), _c_int(pro), _ptr(nw), _c_f(eps), _ptr(weight), _c_int(M), _c_int(N),
+                                      _c_int(K), _ptr(out), _c_int(out.stride(0) if out is not None else N),
+                                      _c_int(1 if (out is not None and out.dtype == torch.float32) else 0), _ptr(residual),
+                                      _stream()), "skinny_linear")
+
+
+def skinny_swiglu(x: torch.Tensor, norm, weight: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, I] = silu(x' Wg^T) * (x' Wu^T), weight = [Wg; Wu] stacked [2I, K]; x' as in skinny_linear."""
+    M, K = x.shape
+    pro, nw, eps = _norm_args(norm)
+    _check(library().vm_skinny_swiglu(_ptr(_contig(x, "x")), _c_int(pro), _ptr(nw), _c_f(eps), _ptr(weight), _c_int(M),
+                                      _c_int(out.shape[1]), _c_int(K), _ptr(_contig(out, "out")), _stream()), "skinny_swiglu")
+
+
+def skinny_qkv_rope(x: torch.Tensor, norm, weight: torch.Tensor, q_out: torch.Tensor, positions: torch.Tensor,
+                    seq_of_token: torch.Tensor, block_table: torch.Tensor, inv_freq: Optional[torch.Tensor], rot_dim: int,
+                    k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], H: int, Hkv: int, D: int,
+                    err: Optional[torch.Tensor] = None) -> None:
+    """q_out[M, H*D] = rotated queries; rotated keys and values go straight into the cache pages.
+    weight = [Wq; Wk; Wv] stacked; x' as in skinny_linear; rot_dim 0 or D."""
+    M, K = x.shape
+    pro, nw, eps = _norm_args(norm)
+    n_pages = k_pages.shape[0] if k_pages is not None else 0
+    _check(library().vm_skinny_qkv_rope(_ptr(_contig(x, "x")), _c_int(pro), _ptr(nw), _c_f(eps), _ptr(weight), _c_int(M), _c_int(K),
+                                        _ptr(_contig(q_out, "q_out")), _ptr(positions), _ptr(seq_of_token), _ptr(block_table),
+                                        _c_int(block_table.shape[1]), _ptr(inv_freq), _c_int(rot_dim), _ptr(k_pages), _ptr(v_pages),
+                                        _c_int(H), _c_int(Hkv), _c_int(D), _c_int(n_pages), _ptr(err), _stream()), "skinny_qkv_rope")
+
+
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor, seed: torch.Tensor,
            stream_id: torch.Tensor, step: torch.Tensor, out: torch.Tensor) -> None:
     """One token per row of logits float32 [R, V]: greedy where temperature <= 0 or top_p <= 0, else

@@ -1,6 +1,7 @@
 """Arrangements: how a layer wires its norms, mixer, feed-forward and the residual stream."""
 from __future__ import annotations
 
+from ..kernels import ops
 from .registry import register_part
 
 
@@ -23,6 +24,17 @@ class PreNormBlock:
 
     def forward(self, ctx, h, pending):
         hid = h.shape[1]
+        # Few tokens (decode): parts that can take the preceding norm into their first kernel and the residual
+        # sum into their last one do so; the step is then bound by the weights it streams, not by launches.
+        fuse_mixer = getattr(self.mixer, "can_fuse", None) is not None and self.mixer.can_fuse(ctx, self.mixer_norm)
+        fuse_ff = getattr(self.feed_forward, "can_fuse", None) is not None and self.feed_forward.can_fuse(ctx, self.feed_forward_norm)
+        if fuse_mixer and fuse_ff:
+            if pending is not None:
+                ops.residual_add(h, pending)
+                ctx.ws.give(pending)
+            self.mixer.forward_fused(ctx, h, self.mixer_norm)
+            self.feed_forward.forward_fused(ctx, h, self.feed_forward_norm)
+            return None
         x = ctx.take_tokens(hid, ctx.act_dtype)
         self.mixer_norm.forward(ctx, h, pending, x)
         ctx.ws.give(pending)

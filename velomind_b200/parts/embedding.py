@@ -47,7 +47,11 @@ class LinearHead(Part):
         self.proj = Linear([weights["weight"]], bc)
 
     def forward(self, ctx, x, logits) -> None:
-        self.proj(ctx, x, logits)
+        w = self.proj.weight
+        if x.dtype == torch.bfloat16 and ops.skinny_ok(x.shape[0], self.hidden, w) and self.vocab % 8 == 0:
+            ops.skinny_linear(x, None, w, logits)        # few rows: stream the table once, float32 logits
+        else:
+            self.proj(ctx, x, logits)
 
 
 register_part("embedding", "token_table", TokenEmbedding)

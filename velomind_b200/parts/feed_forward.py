@@ -31,6 +31,25 @@ class SwiGLU(Part):
         self.gate_up = Linear([weights["gate_proj.weight"], weights["up_proj.weight"]], bc)
         self.down = Linear([weights["down_proj.weight"]], bc)
 
+    def can_fuse(self, ctx, norm) -> bool:
+        rms = getattr(norm, "as_rms", None)
+        return (rms is not None and ctx.act_dtype == torch.bfloat16 and ops.skinny_ok(ctx.T, self.hidden, self.gate_up.weight)
+                and ops.skinny_ok(ctx.T, self.intermediate, self.down.weight) and self.intermediate % 8 == 0
+                and self.hidden % 8 == 0)
+
+    def forward_fused(self, ctx, h: torch.Tensor, norm) -> None:
+        """h += down(silu(gate(norm(h))) * up(norm(h))) in two launches (few tokens, bfloat16)."""
+        x, rms = h, norm.as_rms()
+        if ctx.T > ops.SKINNY_NORM_ROWS:          # many rows: norm once, not once per CTA
+            x, rms = ctx.take_tokens(self.hidden, torch.bfloat16), None
+            norm.forward(ctx, h, None, x)
+        act = ctx.take_tokens(self.intermediate, torch.bfloat16)
+        ops.skinny_swiglu(x, rms, self.gate_up.weight, act)
+        if x is not h:
+            ctx.ws.give(x)
+        ops.skinny_linear(act, None, self.down.weight, None, residual=h)
+        ctx.ws.give(act)
+
     def forward(self, ctx, x: torch.Tensor, out: torch.Tensor) -> None:
         gu = ctx.take_tokens(2 * self.intermediate, x.dtype)
         self.gate_up(ctx, x, gu)

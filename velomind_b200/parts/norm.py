@@ -26,6 +26,10 @@ class RMSNorm(Part):
     def bind(self, weights, bc: BindContext) -> None:
         self.weight = bc.upload(weights["weight"], torch.float32)   # exact for BF16 and F32 storage
 
+    def as_rms(self):
+        """(weight, eps) for kernels that fuse this norm into the product that follows it."""
+        return self.weight, self.eps
+
     def forward(self, ctx, h, delta, out, rows=None) -> None:
         ops.add_rmsnorm(h, delta, self.weight, self.eps, out, rows)
 
