@@ -6,181 +6,198 @@
 // online form of src/cpu/ops/fused_attention.cpp:84-135); the G = H / Hkv query heads that share a kv
 // head (src/cpu/ops/repeat_kv.cpp:51-61) are served by one CTA, so each key and value is read once.
 //
-// grid = (n_splits, Hkv * ceil(G / GM), B), 128 threads.  A CTA's key range is a whole number of cache
+// grid = (n_splits, Hkv * ceil(G / 16), B), 128 threads.  A CTA's key range is a whole number of cache
 // pages, computed on the device from the sequence's length: the launch shape does not depend on the
-// lengths, so the launch can sit in a CUDA graph.  Scratch (global memory beyond inputs and outputs):
+// lengths, so the launch can sit in a CUDA graph.  Head sizes 16, 32, ..., 128.  Scratch (global memory beyond inputs and outputs):
 // float partials [B, H, n_splits, D + 2] and one int counter per (B, kv-head group), which must be zero
 // before the first launch and is left zero by every launch.
-#include "common.cuh"
+#include "mma.cuh"
 
 namespace {
 
 constexpr int DEC_WARPS = 4;
+constexpr int DEC_ROWS = 16;           // query heads per CTA (the M of the tensor-core tile); more heads per kv head take more CTAs
+constexpr int MAX_SPLITS = 16;         // the merge keeps one value per split in registers
 
-__device__ __forceinline__ void dec_cp_async16(void* smem, const void* gmem) {
-    const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sa), "l"(gmem));
-}
-
-// One CTA iteration covers UNIT_PAGES cache pages (128 keys): all of their keys and values are fetched
-// into shared memory at once (every thread has several 16-byte copies in flight), then each warp works
-// on its own 32 keys.
-constexpr int UNIT_PAGES = 2;
-constexpr int UNIT_KEYS = UNIT_PAGES * VM_PAGE_TOKENS;
-static_assert(UNIT_KEYS == DEC_WARPS * 32, "one 32-key chunk per warp");
-
-template <int GM, int EPL>
+// One warp works on one cache page (64 keys) at a time: K and V of the page go to the warp's own shared
+// memory with cp.async, S = Q K^T and O += P V run on mma.sync m16n8k16 with the G query heads of the kv
+// head as the rows of the tile (padded to 16), the softmax state is float32 in base 2.
+template <int D>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, const __nv_bfloat16* __restrict__ kpages,
                    const __nv_bfloat16* __restrict__ vpages, const int* __restrict__ block_table, int max_blocks,
                    const int* __restrict__ positions, __nv_bfloat16* __restrict__ out, float* __restrict__ partial,
-                   int* __restrict__ counters, int H, int Hkv, int D, float scale, int window, int n_pages,
+                   int* __restrict__ counters, int H, int Hkv, float scale_log2, int window, int n_pages,
                    int* __restrict__ err) {
-    // shared: q [GM][D] float | per-warp results [DEC_WARPS][GM][D+2] float | K [128][D+8] bf16 | V [128][D+8] bf16
-    extern __shared__ __align__(16) float sm[];
+    constexpr int DP = D + 8;              // padded row: an odd number of 16-byte units -> conflict-free ldmatrix
+    constexpr int CH = D / 8;              // 16-byte chunks per row
+    constexpr int RW = D + 2;              // a result row: D sums, then the running max and the running sum
+    constexpr int BN = VM_PAGE_TOKENS;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);                    // [16][DP]
+    __nv_bfloat16* sKV = sQ + DEC_ROWS * DP;                                            // [warps][K,V][64][DP]
+    float* res = reinterpret_cast<float*>(sKV + DEC_WARPS * 2 * BN * DP);               // [warps][16][RW]
+    vm_pdl_launch_dependents();
+    vm_pdl_wait();
     const int split = blockIdx.x, n_splits = gridDim.x;
     const int G = H / Hkv;
-    const int groups_per_kv = (G + GM - 1) / GM;
+    const int groups_per_kv = (G + DEC_ROWS - 1) / DEC_ROWS;
     const int hk = blockIdx.y / groups_per_kv, gg = blockIdx.y - hk * groups_per_kv;
     const int b = blockIdx.z;
-    const int h0 = hk * G + gg * GM;                       // first query head of this CTA
-    const int ng = min(GM, G - gg * GM);                   // query heads of this CTA
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h0 = hk * G + gg * DEC_ROWS;                 // first query head of this CTA
+    const int ng = min(DEC_ROWS, G - gg * DEC_ROWS);       // query heads of this CTA
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int pos = positions[b];                          // one token per sequence: token index == sequence index
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    const int first_page = lo / VM_PAGE_TOKENS, last_page = pos / VM_PAGE_TOKENS;
-    const int units = (last_page - first_page) / UNIT_PAGES + 1;
-    const int per_split = (units + n_splits - 1) / n_splits;
-    const int unit_a = split * per_split, unit_b = min(units, unit_a + per_split);
-    const int DP = D + 8;                                  // padded row: an odd number of 16-byte units
-    float* qs = sm;
-    float* res = sm + GM * D;
-    __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(res + DEC_WARPS * GM * (D + 2));
-    __nv_bfloat16* sV = sK + UNIT_KEYS * DP;
-    for (int i = threadIdx.x; i < ng * D; i += blockDim.x) {
-        const int g = i / D, d = i - g * D;
-        qs[g * D + d] = __bfloat162float(q[(size_t)b * q_row_stride + (size_t)(h0 + g) * D + d]) * scale;
-    }
-
-    float m[GM], l[GM], acc[GM][EPL];
-#pragma unroll
-    for (int g = 0; g < GM; ++g) {
-        m[g] = -INFINITY; l[g] = 0.f;
-#pragma unroll
-        for (int i = 0; i < EPL; ++i) acc[g][i] = 0.f;
-    }
-    const size_t page_stride = (size_t)Hkv * VM_PAGE_TOKENS * D;
+    const int first_page = lo / BN, last_page = pos / BN;
+    const int pages = last_page - first_page + 1;
+    const int per_split = (pages + n_splits - 1) / n_splits;
+    const int page_a = first_page + split * per_split, page_b = min(last_page + 1, page_a + per_split);
+    const size_t page_stride = (size_t)Hkv * BN * D;
     const int* table = block_table + (size_t)b * max_blocks;
-    const int CH = D / 8;                                  // 16-byte chunks per row
-    for (int unit = unit_a; unit < unit_b; ++unit) {
-        const int blk0 = first_page + unit * UNIT_PAGES;
-        __syncthreads();                                   // the previous unit's tiles (and qs, the first time) are settled
-        for (int pg = 0; pg < UNIT_PAGES; ++pg) {
-            const int blk = blk0 + pg;
-            if (blk > last_page) break;
-            const int page = (blk < max_blocks) ? table[blk] : -1;
-            if (page < 0 || page >= n_pages) { if (threadIdx.x == 0 && err) atomicExch(err, 3); continue; }
-            const __nv_bfloat16* kg = kpages + (size_t)page * page_stride + (size_t)hk * VM_PAGE_TOKENS * D;
-            const __nv_bfloat16* vg = vpages + (size_t)page * page_stride + (size_t)hk * VM_PAGE_TOKENS * D;
-            for (int c = threadIdx.x; c < VM_PAGE_TOKENS * CH; c += blockDim.x) {
-                const int r = c / CH, ch = c - r * CH;
-                dec_cp_async16(sK + (size_t)(pg * VM_PAGE_TOKENS + r) * DP + ch * 8, kg + (size_t)r * D + ch * 8);
-                dec_cp_async16(sV + (size_t)(pg * VM_PAGE_TOKENS + r) * DP + ch * 8, vg + (size_t)r * D + ch * 8);
+    __nv_bfloat16* ks = sKV + (size_t)warp * 2 * BN * DP;
+    __nv_bfloat16* vs = ks + BN * DP;
+
+    // ---- the queries of this CTA's heads (rows past the last head are zero)
+    for (int c = tid; c < DEC_ROWS * CH; c += DEC_WARPS * 32) {
+        const int r = c / CH, ch = c - r * CH;
+        if (r < ng) vm_cp_async16(sQ + r * DP + ch * 8, q + (size_t)b * q_row_stride + (size_t)(h0 + r) * D + ch * 8);
+        else *reinterpret_cast<uint4*>(sQ + r * DP + ch * 8) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    auto load_page = [&](int blk) -> bool {                // the calling warp fetches K and V of one page
+        const int page = (blk < max_blocks) ? table[blk] : -1;
+        if (page < 0 || page >= n_pages) { if (lane == 0 && err) atomicExch(err, 3); return false; }
+        const __nv_bfloat16* kg = kpages + (size_t)page * page_stride + (size_t)hk * BN * D;
+        const __nv_bfloat16* vg = vpages + (size_t)page * page_stride + (size_t)hk * BN * D;
+#pragma unroll 4
+        for (int c = lane; c < BN * CH; c += 32) {
+            const int r = c / CH, ch = c - r * CH;
+            vm_cp_async16(ks + r * DP + ch * 8, kg + r * D + ch * 8);
+            vm_cp_async16(vs + r * DP + ch * 8, vg + r * D + ch * 8);
+        }
+        return true;
+    };
+    int blk = page_a + warp;
+    bool have = (blk < page_b) && load_page(blk);
+    vm_cp_async_commit();
+    vm_cp_async_wait_all();
+    __syncthreads();                                       // the queries (fetched by all threads) are in place
+
+    const int g = lane >> 2, t4 = lane & 3;
+    unsigned qa[D / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk)
+        vm_ldmatrix_x4(qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3],
+                       sQ + ((lane & 7) + 8 * ((lane >> 3) & 1)) * DP + kk * 16 + 8 * (lane >> 4));
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;     // rows g and g + 8 of the tile
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+
+    while (blk < page_b) {
+        if (have) {
+            const int key0 = blk * BN;
+            float s[BN / 8][4];
+#pragma unroll
+            for (int nb = 0; nb < BN / 8; ++nb) { s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f; }
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+                for (int nb = 0; nb < BN / 8; nb += 2) {
+                    unsigned b0, b1, b2, b3;
+                    vm_ldmatrix_x4(b0, b1, b2, b3, ks + (nb * 8 + (lane & 7) + 8 * (lane >> 4)) * DP + kk * 16 + 8 * ((lane >> 3) & 1));
+                    vm_mma_bf16_16816(s[nb], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], b0, b1);
+                    vm_mma_bf16_16816(s[nb + 1], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], b2, b3);
+                }
             }
-        }
-        asm volatile("cp.async.commit_group;\n" ::);
-        asm volatile("cp.async.wait_group 0;\n" ::);
-        __syncthreads();
-        const int base = blk0 * VM_PAGE_TOKENS + warp * 32;
-        if (base > pos || base + 31 < lo) continue;         // warp-uniform: none of this warp's keys is visible
-        {
-            const int blk = base / VM_PAGE_TOKENS;
-            const int page = (blk < max_blocks) ? table[blk] : -1;
-            if (page < 0 || page >= n_pages) continue;      // reported above; its tile was not loaded
-        }
-        const int j = base + lane;
-        const bool valid = (j >= lo && j <= pos);
-        float s[GM];
+            float mx_a = -INFINITY, mx_b = -INFINITY;
 #pragma unroll
-        for (int g = 0; g < GM; ++g) s[g] = 0.f;
-        if (valid) {
-            const uint4* krow = reinterpret_cast<const uint4*>(sK + (size_t)(warp * 32 + lane) * DP);
-            for (int ch = 0; ch < CH; ++ch) {
-                const uint4 kv = krow[ch];
-                const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&kv);
+            for (int nb = 0; nb < BN / 8; ++nb) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float2 kf = __bfloat1622float2(k2[e]);
+                for (int e = 0; e < 2; ++e) {
+                    const int key = key0 + nb * 8 + 2 * t4 + e;
+                    const bool ok = (key <= pos && key >= lo);
+                    const float va = ok ? s[nb][e] * scale_log2 : -INFINITY;
+                    const float vb = ok ? s[nb][2 + e] * scale_log2 : -INFINITY;
+                    s[nb][e] = va; s[nb][2 + e] = vb;
+                    mx_a = fmaxf(mx_a, va); mx_b = fmaxf(mx_b, vb);
+                }
+            }
+            mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1)); mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+            mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1)); mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+            const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+            const float use_a = (mn_a == -INFINITY) ? 0.f : mn_a, use_b = (mn_b == -INFINITY) ? 0.f : mn_b;
+            const float al_a = exp2f(m_a - use_a), al_b = exp2f(m_b - use_b);
+            float sum_a = 0.f, sum_b = 0.f;
+            unsigned pa[BN / 16][4];
 #pragma unroll
-                    for (int g = 0; g < GM; ++g) {
-                        if (g < ng) {
-                            s[g] = fmaf(qs[g * D + ch * 8 + 2 * e], kf.x, s[g]);
-                            s[g] = fmaf(qs[g * D + ch * 8 + 2 * e + 1], kf.y, s[g]);
-                        }
-                    }
+            for (int nb = 0; nb < BN / 8; ++nb) {
+                const float p0 = exp2f(s[nb][0] - use_a), p1 = exp2f(s[nb][1] - use_a);
+                const float p2 = exp2f(s[nb][2] - use_b), p3 = exp2f(s[nb][3] - use_b);
+                sum_a += p0 + p1; sum_b += p2 + p3;
+                pa[nb >> 1][(nb & 1) * 2 + 0] = vm_pack_bf16(p0, p1);
+                pa[nb >> 1][(nb & 1) * 2 + 1] = vm_pack_bf16(p2, p3);
+            }
+            l_a = l_a * al_a + sum_a; l_b = l_b * al_b + sum_b;        // per-thread partial sums; the quad is joined below
+            m_a = mn_a; m_b = mn_b;
+#pragma unroll
+            for (int i = 0; i < D / 8; ++i) { o[i][0] *= al_a; o[i][1] *= al_a; o[i][2] *= al_b; o[i][3] *= al_b; }
+#pragma unroll
+            for (int kk = 0; kk < BN / 16; ++kk) {
+#pragma unroll
+                for (int nb = 0; nb < D / 8; nb += 2) {
+                    unsigned b0, b1, b2, b3;
+                    vm_ldmatrix_x4_trans(b0, b1, b2, b3, vs + (kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * DP + nb * 8 + 8 * (lane >> 4));
+                    vm_mma_bf16_16816(o[nb], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b0, b1);
+                    vm_mma_bf16_16816(o[nb + 1], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b2, b3);
                 }
             }
         }
-        float p[GM];
-#pragma unroll
-        for (int g = 0; g < GM; ++g) {
-            const float sv = valid ? s[g] : -INFINITY;
-            const float mn = fmaxf(m[g], vm_warp_max(sv));           // the chunk holds at least one visible key
-            p[g] = valid ? expf(sv - mn) : 0.f;
-            const float alpha = expf(m[g] - mn);
-            l[g] = l[g] * alpha + vm_warp_sum(p[g]);
-#pragma unroll
-            for (int i = 0; i < EPL; ++i) acc[g][i] *= alpha;
-            m[g] = mn;
-        }
-        const int cnt = min(32, pos - base + 1);
-        const int first = max(0, lo - base);
-        for (int jj = first; jj < cnt; ++jj) {
-            const __nv_bfloat16* vrow = sV + (size_t)(warp * 32 + jj) * DP;
-            float vv[EPL];
-#pragma unroll
-            for (int i = 0; i < EPL; ++i) { const int d = lane + 32 * i; vv[i] = (d < D) ? __bfloat162float(vrow[d]) : 0.f; }
-#pragma unroll
-            for (int g = 0; g < GM; ++g) {
-                const float pj = __shfl_sync(0xffffffffu, p[g], jj);
-#pragma unroll
-                for (int i = 0; i < EPL; ++i) acc[g][i] = fmaf(pj, vv[i], acc[g][i]);
-            }
+        blk += DEC_WARPS;
+        if (blk < page_b) {
+            __syncwarp();                                  // every lane is done with the page before it is overwritten
+            have = load_page(blk);
+            vm_cp_async_commit();
+            vm_cp_async_wait_all();
+            __syncwarp();
         }
     }
-    __syncthreads();
-    // ---- join the CTA's warps
-    const int RW = D + 2;
+    // ---- this warp's result rows: join the quad's sums; res[warp][row] = (o[D], m, l)
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+    {
+        float* ra = res + ((size_t)warp * DEC_ROWS + g) * RW;
+        float* rb = res + ((size_t)warp * DEC_ROWS + g + 8) * RW;
 #pragma unroll
-    for (int g = 0; g < GM; ++g) {
-        if (g < ng) {
-            float* r = res + ((size_t)warp * GM + g) * RW;
-#pragma unroll
-            for (int i = 0; i < EPL; ++i) { const int d = lane + 32 * i; if (d < D) r[d] = acc[g][i]; }
-            if (lane == 0) { r[D] = m[g]; r[D + 1] = l[g]; }
+        for (int i = 0; i < D / 8; ++i) {
+            const int d = i * 8 + 2 * t4;
+            ra[d] = o[i][0]; ra[d + 1] = o[i][1]; rb[d] = o[i][2]; rb[d + 1] = o[i][3];
         }
+        if (t4 == 0) { ra[D] = m_a; ra[D + 1] = l_a; rb[D] = m_b; rb[D + 1] = l_b; }
     }
     __syncthreads();
-    // partial[b, h, split, :] = (o[D], m, l), merged over the warps
-    for (int i = threadIdx.x; i < ng * D; i += blockDim.x) {
-        const int g = i / D, d = i - g * D;
+    // partial[b, h, split, :] = (o[D], m, l), merged over the warps (max and sums in base 2)
+    for (int i = tid; i < ng * D; i += DEC_WARPS * 32) {
+        const int r = i / D, d = i - r * D;
         float M = -INFINITY;
-        for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, res[((size_t)w * GM + g) * RW + D]);
-        float o = 0.f, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, res[((size_t)w * DEC_ROWS + r) * RW + D]);
+        float acc = 0.f, L = 0.f;
+#pragma unroll
         for (int w = 0; w < DEC_WARPS; ++w) {
-            const float* r = res + ((size_t)w * GM + g) * RW;
-            const float f = (r[D] == -INFINITY) ? 0.f : expf(r[D] - M);
-            o += f * r[d]; L += f * r[D + 1];
+            const float* rr = res + ((size_t)w * DEC_ROWS + r) * RW;
+            const float f = (rr[D] == -INFINITY) ? 0.f : exp2f(rr[D] - M);
+            acc += f * rr[d]; L += f * rr[D + 1];
         }
-        float* dst = partial + (((size_t)b * H + (h0 + g)) * n_splits + split) * RW;
-        dst[d] = o;
+        float* dst = partial + (((size_t)b * H + (h0 + r)) * n_splits + split) * RW;
+        dst[d] = acc;
         if (d == 0) { dst[D] = M; dst[D + 1] = L; }
     }
-    // ---- the last CTA of this (sequence, head group) merges the splits
+    // ---- the last CTA of this (sequence, head group) to arrive merges the splits; nobody waits
     __shared__ int is_last;
     __threadfence();
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (tid == 0) {
         const int old = atomicAdd(&counters[(size_t)b * gridDim.y + blockIdx.y], 1);
         is_last = (old == n_splits - 1);
         if (is_last) counters[(size_t)b * gridDim.y + blockIdx.y] = 0;     // ready for the next launch
@@ -188,45 +205,49 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, const 
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    for (int i = threadIdx.x; i < ng * D; i += blockDim.x) {
-        const int g = i / D, d = i - g * D;
-        const float* src = partial + ((size_t)b * H + (h0 + g)) * n_splits * RW;
-        float M = -INFINITY;
-        for (int s2 = 0; s2 < n_splits; ++s2) M = fmaxf(M, __ldcg(src + (size_t)s2 * RW + D));
-        float o = 0.f, L = 0.f;
-        for (int s2 = 0; s2 < n_splits; ++s2) {
-            const float ms = __ldcg(src + (size_t)s2 * RW + D);
-            const float f = (ms == -INFINITY) ? 0.f : expf(ms - M);
-            o += f * __ldcg(src + (size_t)s2 * RW + d);
-            L += f * __ldcg(src + (size_t)s2 * RW + D + 1);
+    for (int i = tid; i < ng * D; i += DEC_WARPS * 32) {
+        const int r = i / D, d = i - r * D;
+        const float* src = partial + ((size_t)b * H + (h0 + r)) * n_splits * RW;
+        // all loads first (independent of each other), then the arithmetic: one memory latency, not n_splits
+        float ms[MAX_SPLITS], ls[MAX_SPLITS], os[MAX_SPLITS];
+#pragma unroll
+        for (int s2 = 0; s2 < MAX_SPLITS; ++s2) {
+            if (s2 < n_splits) {
+                ms[s2] = __ldcg(src + (size_t)s2 * RW + D);
+                ls[s2] = __ldcg(src + (size_t)s2 * RW + D + 1);
+                os[s2] = __ldcg(src + (size_t)s2 * RW + d);
+            } else { ms[s2] = -INFINITY; ls[s2] = 0.f; os[s2] = 0.f; }
         }
-        out[((size_t)b * H + (h0 + g)) * D + d] = __float2bfloat16_rn(o / L);
+        float M = -INFINITY;
+#pragma unroll
+        for (int s2 = 0; s2 < MAX_SPLITS; ++s2) M = fmaxf(M, ms[s2]);
+        float acc = 0.f, L = 0.f;
+#pragma unroll
+        for (int s2 = 0; s2 < MAX_SPLITS; ++s2) {
+            const float f = (ms[s2] == -INFINITY) ? 0.f : exp2f(ms[s2] - M);
+            acc += f * os[s2];
+            L += f * ls[s2];
+        }
+        out[((size_t)b * H + (h0 + r)) * D + d] = __float2bfloat16_rn(acc / L);
     }
 }
 
-template <int GM>
-int launch_decode(int epl, dim3 grid, size_t smem, cudaStream_t stream, const __nv_bfloat16* q, int q_row_stride,
-                  const __nv_bfloat16* kpages, const __nv_bfloat16* vpages, const int* block_table, int max_blocks,
-                  const int* positions, __nv_bfloat16* out, float* partial, int* counters, int H, int Hkv, int D,
-                  float scale, int window, int n_pages, int* err) {
-#define VM_DEC_CASE(E)                                                                                               \
-    case E:                                                                                                          \
-        if (smem > 48 * 1024) {                                                                                      \
-            static bool configured = false;                                                                          \
-            if (!configured) {                                                                                       \
-                cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<GM, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
-                if (e != cudaSuccess) return (int)e;                                                                 \
-                configured = true;                                                                                   \
-            }                                                                                                        \
-        }                                                                                                            \
-        attn_decode_kernel<GM, E><<<grid, DEC_WARPS * 32, smem, stream>>>(q, q_row_stride, kpages, vpages, block_table, \
-            max_blocks, positions, out, partial, counters, H, Hkv, D, scale, window, n_pages, err);                   \
-        break;
-    switch (epl) {
-        VM_DEC_CASE(1) VM_DEC_CASE(2) VM_DEC_CASE(3) VM_DEC_CASE(4)
-        default: return VM_ERR_UNSUPPORTED;
+template <int D>
+int launch_decode(dim3 grid, cudaStream_t stream, const __nv_bfloat16* q, int q_row_stride, const __nv_bfloat16* kpages,
+                  const __nv_bfloat16* vpages, const int* block_table, int max_blocks, const int* positions,
+                  __nv_bfloat16* out, float* partial, int* counters, int H, int Hkv, float scale, int window, int n_pages,
+                  int* err) {
+    constexpr int DP = D + 8;
+    const size_t smem = (size_t)(DEC_ROWS + DEC_WARPS * 2 * VM_PAGE_TOKENS) * DP * sizeof(__nv_bfloat16)
+                        + (size_t)DEC_WARPS * DEC_ROWS * (D + 2) * sizeof(float);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
     }
-#undef VM_DEC_CASE
+    vm_launch_pdl(attn_decode_kernel<D>, grid, dim3(DEC_WARPS * 32), smem, stream, q, q_row_stride, kpages, vpages, block_table,
+                  max_blocks, positions, out, partial, counters, H, Hkv, scale * 1.4426950408889634f, window, n_pages, err);
     return vm_launch_status();
 }
 
@@ -237,28 +258,27 @@ VM_API long long vm_attention_decode_scratch_floats(int B, int H, int D, int n_s
     return (long long)B * H * n_splits * (D + 2);
 }
 
-// q: [B, H, D] rows with stride q_row_stride; out: [B, H*D].  counters: at least B * Hkv * ceil(G/GM) ints, zero.
+// q: [B, H, D] rows with stride q_row_stride; out: [B, H*D].  counters: at least B * Hkv * ceil(G/16) ints, zero.
 VM_API int vm_attention_decode_bf16(const void* q, int q_row_stride, const void* kpages, const void* vpages,
                                     const int* block_table, int max_blocks, const int* positions, void* out,
                                     float* partial, int* counters, int B, int H, int Hkv, int D, int n_splits,
                                     float scale, int window, int n_pages, int* err, cudaStream_t stream) {
     if (B <= 0) return 0;
-    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || D % 8 != 0 || D > 128 || n_splits < 1 || (q_row_stride % 8) != 0)
+    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || n_splits < 1 || n_splits > MAX_SPLITS || (q_row_stride % 8) != 0)
         return VM_ERR_UNSUPPORTED;
     const int G = H / Hkv;
-    const int GM = G <= 1 ? 1 : (G <= 2 ? 2 : (G <= 4 ? 4 : 8));
-    const int groups = (G + GM - 1) / GM;
-    dim3 grid(n_splits, Hkv * groups, B);
-    const size_t smem = ((size_t)GM * D + (size_t)DEC_WARPS * GM * (D + 2)) * sizeof(float)
-                        + 2 * (size_t)UNIT_KEYS * (D + 8) * sizeof(__nv_bfloat16);
-    const int epl = (D + 31) / 32;
+    dim3 grid(n_splits, Hkv * ((G + DEC_ROWS - 1) / DEC_ROWS), B);
     const __nv_bfloat16 *qq = (const __nv_bfloat16*)q, *kk = (const __nv_bfloat16*)kpages, *vv = (const __nv_bfloat16*)vpages;
-    switch (GM) {
-        case 1: return launch_decode<1>(epl, grid, smem, stream, qq, q_row_stride, kk, vv, block_table, max_blocks, positions, (__nv_bfloat16*)out, partial, counters, H, Hkv, D, scale, window, n_pages, err);
-        case 2: return launch_decode<2>(epl, grid, smem, stream, qq, q_row_stride, kk, vv, block_table, max_blocks, positions, (__nv_bfloat16*)out, partial, counters, H, Hkv, D, scale, window, n_pages, err);
-        case 4: return launch_decode<4>(epl, grid, smem, stream, qq, q_row_stride, kk, vv, block_table, max_blocks, positions, (__nv_bfloat16*)out, partial, counters, H, Hkv, D, scale, window, n_pages, err);
-        default: return launch_decode<8>(epl, grid, smem, stream, qq, q_row_stride, kk, vv, block_table, max_blocks, positions, (__nv_bfloat16*)out, partial, counters, H, Hkv, D, scale, window, n_pages, err);
+#define VM_DEC_CASE(DD)                                                                                                \
+    case DD:                                                                                                           \
+        return launch_decode<DD>(grid, stream, qq, q_row_stride, kk, vv, block_table, max_blocks, positions,             \
+                                 (__nv_bfloat16*)out, partial, counters, H, Hkv, scale, window, n_pages, err);
+    switch (D) {
+        VM_DEC_CASE(16) VM_DEC_CASE(32) VM_DEC_CASE(48) VM_DEC_CASE(64)
+        VM_DEC_CASE(80) VM_DEC_CASE(96) VM_DEC_CASE(112) VM_DEC_CASE(128)
+        default: return VM_ERR_UNSUPPORTED;
     }
+#undef VM_DEC_CASE
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -43,6 +43,29 @@ __device__ __forceinline__ float vm_block_sum(float v, float* red) {
     return vm_warp_sum(t);
 }
 
+// ---- programmatic dependent launch: a kernel launched through vm_launch_pdl may begin (and fetch data that
+// no earlier kernel writes, i.e. weights) while its predecessor in the stream is still running; it must call
+// vm_pdl_wait() before it reads anything an earlier kernel wrote and before its first global write.
+// vm_pdl_launch_dependents() lets the successor start its own preamble.  Without the launch attribute both
+// are no-ops.
+__device__ __forceinline__ void vm_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void vm_pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+extern int vm_pdl_enabled;      // defined in elementwise.cu; switched by vm_set_pdl()
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t vm_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                        Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = vm_pdl_enabled ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 static inline int vm_launch_status() {
     cudaError_t e = cudaGetLastError();
     return static_cast<int>(e);

@@ -4,12 +4,17 @@
 // float32.  T is the activation type (float or bf16).
 #include "common.cuh"
 
+int vm_pdl_enabled = 1;
+VM_API void vm_set_pdl(int on) { vm_pdl_enabled = on ? 1 : 0; }
+
 // ---------------------------------------------------------------- embedding: out[t,:] = table[tokens[t],:]
 // Reference: src/cpu/ops/embedding.cpp:27-32.  Ids are validated on the host before the launch; the
 // kernel still refuses an id outside the table (writes zeros and raises the error word).
 template <typename W>
 __global__ void embed_gather_kernel(const W* __restrict__ table, const int* __restrict__ tokens,
                                     float* __restrict__ out, int T, int hid, int vocab, int* __restrict__ err) {
+    vm_pdl_launch_dependents();
+    vm_pdl_wait();
     const int t = blockIdx.x;
     const int id = tokens[t];
     const bool ok = (id >= 0 && id < vocab);
@@ -24,9 +29,9 @@ VM_API int vm_embed_gather(const void* table, int table_dtype, const int* tokens
     if (T <= 0) return 0;
     const int threads = hid >= 512 ? 256 : 128;
     if (table_dtype == VM_F32)
-        embed_gather_kernel<float><<<T, threads, 0, stream>>>((const float*)table, tokens, out, T, hid, vocab, err);
+        vm_launch_pdl(embed_gather_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)table, tokens, out, T, hid, vocab, err);
     else if (table_dtype == VM_BF16)
-        embed_gather_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>((const __nv_bfloat16*)table, tokens, out, T, hid, vocab, err);
+        vm_launch_pdl(embed_gather_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (const __nv_bfloat16*)table, tokens, out, T, hid, vocab, err);
     else
         return VM_ERR_UNSUPPORTED;
     return vm_launch_status();
@@ -42,6 +47,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ 
                                    T* __restrict__ out, const int* __restrict__ rows, int hid, float eps) {
     extern __shared__ float row[];          // hid floats
     __shared__ float red[32];
+    vm_pdl_launch_dependents();
+    vm_pdl_wait();
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
     float* hrow = h + (size_t)src * hid;
@@ -70,10 +77,10 @@ VM_API int vm_add_rmsnorm(float* h, const void* delta, const float* w, void* out
     if (smem > 200 * 1024) return VM_ERR_UNSUPPORTED;
     if (act_dtype == VM_F32) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        add_rmsnorm_kernel<float><<<n_out, threads, smem, stream>>>(h, (const float*)delta, w, (float*)out, rows, hid, eps);
+        vm_launch_pdl(add_rmsnorm_kernel<float>, dim3(n_out), dim3(threads), smem, stream, h, (const float*)delta, w, (float*)out, rows, hid, eps);
     } else if (act_dtype == VM_BF16) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        add_rmsnorm_kernel<__nv_bfloat16><<<n_out, threads, smem, stream>>>(h, (const __nv_bfloat16*)delta, w, (__nv_bfloat16*)out, rows, hid, eps);
+        vm_launch_pdl(add_rmsnorm_kernel<__nv_bfloat16>, dim3(n_out), dim3(threads), smem, stream, h, (const __nv_bfloat16*)delta, w, (__nv_bfloat16*)out, rows, hid, eps);
     } else {
         return VM_ERR_UNSUPPORTED;
     }

@@ -11,7 +11,7 @@
 //                        out [M, H*D], k and v into the paged cache (llama_graph.cpp:210-215)
 //
 // y = x W^T with W [N, K] row-major (K contiguous).  Every weight byte is read once per step, so the kernel
-// is organised around the weight stream: a CTA owns 8 or 16 output columns, its four warps split K, and
+// is organised around the weight stream: a CTA owns 8 or 16 output columns, its eight warps split K, and
 // each thread fetches 16 contiguous bytes of a weight row per 32-wide k block straight from global memory
 // into the B fragments of two mma.sync m16n8k16 (bf16 in, float32 accumulate).  The k indices inside a
 // block are permuted the same way for A and B, which leaves the dot product unchanged and makes the
@@ -26,7 +26,7 @@ namespace {
 enum : int { PRO_NONE = 0, PRO_RMSNORM = 1 };
 enum : int { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3, EPI_ROPE_KV = 4 };
 
-constexpr int SK_WARPS = 4;
+constexpr int SK_WARPS = 8;
 constexpr int SK_THREADS = SK_WARPS * 32;
 
 struct SkinnyParams {
@@ -57,6 +57,7 @@ skinny_gemm_kernel(const SkinnyParams p) {
     float* red = reinterpret_cast<float*>(smem + (size_t)ROWS * p.row_bytes);   // [SK_WARPS][ROWS][16]
     float* inv = red + SK_WARPS * ROWS * 16;                               // [ROWS]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    vm_pdl_launch_dependents();
 
     // ---- which output columns
     int nA, nB, head = 0;
@@ -76,7 +77,7 @@ skinny_gemm_kernel(const SkinnyParams p) {
 
     // ---- weight fragments do not depend on A: the first group of this warp's k blocks is requested before
     //      anything else, so that its DRAM latency overlaps the staging of A
-    constexpr int PF = 6;                                   // k blocks in flight per warp
+    constexpr int PF = 8;                                   // k blocks in flight per warp
     uint4 wa[PF], wb[PF];
     auto issue = [&](int kc0, int blocks, int group) {
 #pragma unroll
@@ -90,6 +91,24 @@ skinny_gemm_kernel(const SkinnyParams p) {
         }
     };
     issue(0, min(p.kc, p.K) / 32, 0);
+    vm_pdl_wait();                                          // from here on: data written by earlier kernels
+    // the epilogue's per-row facts (position, cache page) are fetched now, long before they are needed
+    int row_pos[MT], row_page[MT];
+    if (p.epi == EPI_ROPE_KV) {
+#pragma unroll
+        for (int i = 0; i < MT; ++i) {
+            const int item = tid + SK_THREADS * i;
+            const int row = item >> 3;
+            row_pos[i] = 0; row_page[i] = -1;
+            if (item < ROWS * 8 && row < p.M) {
+                row_pos[i] = p.positions[row];
+                if (head >= p.H && p.kpages != nullptr) {
+                    const int blk = row_pos[i] / VM_PAGE_TOKENS;
+                    row_page[i] = (blk < p.max_blocks) ? p.block_table[(size_t)p.seq_of_token[row] * p.max_blocks + blk] : -1;
+                }
+            }
+        }
+    }
 
     float acc[MT][2][4];
 #pragma unroll
@@ -184,7 +203,10 @@ skinny_gemm_kernel(const SkinnyParams p) {
                 red[((size_t)warp * ROWS + row) * 16 + col] = acc[mt][t][e];
             }
     __syncthreads();
-    for (int item = tid; item < ROWS * 8; item += SK_THREADS) {
+#pragma unroll
+    for (int it = 0; it < MT; ++it) {
+        const int item = tid + SK_THREADS * it;
+        if (item >= ROWS * 8) break;
         const int row = item >> 3, c = item & 7;
         if (row >= p.M) continue;
         float vA = 0.f, vB = 0.f;
@@ -218,7 +240,7 @@ skinny_gemm_kernel(const SkinnyParams p) {
                 static_cast<__nv_bfloat16*>(p.out)[(size_t)row * p.out_stride + nA + c] = __float2bfloat16_rn((sig * vA) * vB);
             } break;
             case EPI_ROPE_KV: {
-                const int pos = p.positions[row];
+                const int pos = row_pos[it];
                 float ya = vA, yb = vB;
                 int da, db;                                 // the two columns' places inside the head
                 if (head < p.H + p.Hkv && p.rot_dim > 0) {
@@ -232,8 +254,7 @@ skinny_gemm_kernel(const SkinnyParams p) {
                     __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + (size_t)row * p.out_stride + (size_t)head * p.D;
                     o[da] = __float2bfloat16_rn(ya); o[db] = __float2bfloat16_rn(yb);
                 } else if (p.kpages != nullptr) {
-                    const int blk = pos / VM_PAGE_TOKENS;
-                    const int page = (blk < p.max_blocks) ? p.block_table[(size_t)p.seq_of_token[row] * p.max_blocks + blk] : -1;
+                    const int page = row_page[it];
                     if (page < 0 || page >= p.n_pages) { if (p.err) atomicExch(p.err, 2); break; }
                     const bool is_k = head < p.H + p.Hkv;
                     const int hk = is_k ? head - p.H : head - p.H - p.Hkv;
@@ -244,6 +265,111 @@ skinny_gemm_kernel(const SkinnyParams p) {
             } break;
         }
     }
+}
+
+// The same product for MANY output columns (the vocabulary head): the warps of a CTA split N instead of K.
+// Each warp owns 8 columns over all of K, so there is no cross-warp sum and the A tile is staged once per
+// 64 columns.  Plain A (bf16), store epilogue (bf16 or float32).
+template <int MT>
+__global__ void __launch_bounds__(SK_THREADS)
+skinny_wide_kernel(const SkinnyParams p) {
+    constexpr int ROWS = 16 * MT;
+    constexpr int PF = 6;
+    extern __shared__ __align__(16) unsigned char smem[];
+    unsigned char* sA = smem;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    vm_pdl_launch_dependents();
+    const int n0 = (blockIdx.x * SK_WARPS + warp) * 8;
+    const bool live = n0 < p.N;
+    const __nv_bfloat16* wrow = p.W + (size_t)(live ? n0 + g : 0) * p.K;
+    uint4 wa[PF];
+    auto issue = [&](int first_block, int blocks) {
+#pragma unroll
+        for (int u = 0; u < PF; ++u) {
+            const int b = first_block + u;
+            if (live && b < blocks) wa[u] = *reinterpret_cast<const uint4*>(wrow + 32 * b + 8 * t4);
+        }
+    };
+    const int blocks = p.K / 32;
+    issue(0, blocks);
+    vm_pdl_wait();
+    float acc[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
+    {
+        const __nv_bfloat16* A = static_cast<const __nv_bfloat16*>(p.A);
+        const int chunks = p.K / 8;
+        for (int c = tid; c < ROWS * chunks; c += SK_THREADS) {
+            const int r = c / chunks, ch = c - r * chunks;
+            unsigned char* dst = sA + (size_t)r * p.row_bytes + ch * 16;
+            if (r < p.M) vm_cp_async16(dst, A + (size_t)r * p.K + ch * 8);
+            else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        vm_cp_async_commit();
+        vm_cp_async_wait_all();
+    }
+    __syncthreads();
+    for (int b0 = 0; b0 < blocks; b0 += PF) {
+        if (b0 > 0) issue(b0, blocks);
+#pragma unroll
+        for (int u = 0; u < PF; ++u) {
+            const int b = b0 + u;
+            if (live && b < blocks) {
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    const uint4 a_lo = *reinterpret_cast<const uint4*>(sA + (size_t)(mt * 16 + g) * p.row_bytes + (32 * b + 8 * t4) * 2);
+                    const uint4 a_hi = *reinterpret_cast<const uint4*>(sA + (size_t)(mt * 16 + g + 8) * p.row_bytes + (32 * b + 8 * t4) * 2);
+                    vm_mma_bf16_16816(acc[mt], a_lo.x, a_hi.x, a_lo.y, a_hi.y, wa[u].x, wa[u].y);
+                    vm_mma_bf16_16816(acc[mt], a_lo.z, a_hi.z, a_lo.w, a_hi.w, wa[u].z, wa[u].w);
+                }
+            }
+        }
+    }
+    if (!live) return;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int row = mt * 16 + g + 8 * half;
+            if (row >= p.M) continue;
+            const int col = n0 + 2 * t4;
+            const float v0 = acc[mt][2 * half], v1 = acc[mt][2 * half + 1];
+            if (p.epi == EPI_STORE_F32) {
+                float* o = static_cast<float*>(p.out) + (size_t)row * p.out_stride + col;
+                o[0] = v0; o[1] = v1;
+            } else {
+                __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + (size_t)row * p.out_stride + col;
+                o[0] = __float2bfloat16_rn(v0); o[1] = __float2bfloat16_rn(v1);
+            }
+        }
+    }
+}
+
+int skinny_wide_launch(SkinnyParams p, cudaStream_t stream) {
+    if (p.M <= 0) return 0;
+    if (p.M > 64 || p.K % 32 != 0 || p.K <= 0 || p.N % 8 != 0) return VM_ERR_UNSUPPORTED;
+    const int mt = (p.M + 15) / 16;
+    const int MT = mt <= 1 ? 1 : (mt <= 2 ? 2 : 4);
+    const int rows = 16 * MT;
+    int pitch = p.K * 2;
+    pitch += ((64 - pitch % 128) + 128) % 128;
+    p.row_bytes = pitch;
+    const size_t smem = (size_t)rows * pitch;
+    if (smem > 200 * 1024) return VM_ERR_UNSUPPORTED;
+    const int grid = (p.N / 8 + SK_WARPS - 1) / SK_WARPS;
+#define VM_SKW_CASE(X)                                                                                                \
+    case X: {                                                                                                         \
+        static size_t configured = 0;                                                                                 \
+        if (smem > 48 * 1024 && smem > configured) {                                                                  \
+            cudaError_t e = cudaFuncSetAttribute(skinny_wide_kernel<X>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+            if (e != cudaSuccess) return (int)e;                                                                      \
+            configured = 200 * 1024;                                                                                  \
+        }                                                                                                             \
+        vm_launch_pdl(skinny_wide_kernel<X>, dim3(grid), dim3(SK_THREADS), smem, stream, p);                          \
+    } break;
+    switch (MT) { VM_SKW_CASE(1) VM_SKW_CASE(2) VM_SKW_CASE(4) }
+#undef VM_SKW_CASE
+    return vm_launch_status();
 }
 
 int skinny_launch(SkinnyParams p, int grid, cudaStream_t stream) {
@@ -269,7 +395,7 @@ int skinny_launch(SkinnyParams p, int grid, cudaStream_t stream) {
             if (e != cudaSuccess) return (int)e;                                                                      \
             configured = 160 * 1024;                                                                                  \
         }                                                                                                             \
-        skinny_gemm_kernel<X><<<grid, SK_THREADS, smem, stream>>>(p);                                                 \
+        vm_launch_pdl(skinny_gemm_kernel<X>, dim3(grid), dim3(SK_THREADS), smem, stream, p);                          \
     } break;
     switch (MT) { VM_SK_CASE(1) VM_SK_CASE(2) VM_SK_CASE(4) }
 #undef VM_SK_CASE
@@ -286,6 +412,8 @@ VM_API int vm_skinny_linear(const void* A, int pro, const float* norm_w, float e
     p.A = A; p.pro = pro; p.norm_w = norm_w; p.eps = eps; p.W = (const __nv_bfloat16*)W; p.M = M; p.N = N; p.K = K;
     p.out = out; p.out_stride = out_stride; p.h = residual_h;
     p.epi = residual_h ? EPI_RESIDUAL : (out_f32 ? EPI_STORE_F32 : EPI_STORE_BF16);
+    if (pro == PRO_NONE && !residual_h && N >= 4096 && (size_t)((M + 15) / 16 * 16) * (K * 2 + 128) <= 200 * 1024)
+        return skinny_wide_launch(p, stream);               // many columns: warps split N, not K
     p.tiles = (N % 16 == 0 && N / 16 >= 148) ? 2 : 1;
     return skinny_launch(p, p.tiles == 2 ? N / 16 : N / 8, stream);
 }

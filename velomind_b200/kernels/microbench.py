@@ -1,0 +1,157 @@
+"""Times one kernel alone at a model's sizes: `python -m velomind_b200.kernels.microbench <kernel> [options]`.
+
+The kernel is launched `--repeat` times in one CUDA graph (as the decode step launches it) and the mean
+time per launch is printed with the bytes it has to read and the bandwidth that corresponds to.  Weights
+rotate through enough copies to exceed the L2 cache.  This is the command the ncu summaries under
+profiles/ were made with.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+
+import torch
+
+from . import ops
+
+KERNELS = ["qkv_rope", "out_residual", "gate_up_swiglu", "down_residual", "head", "attn_decode", "attn_prefill",
+           "add_rmsnorm", "sample"]
+
+
+def _time(fn, repeat: int, graph: bool = True) -> float:
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(repeat):
+                fn()
+        g.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(5):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / 5 / repeat * 1e3
+    e0.record()
+    for _ in range(repeat):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / repeat * 1e3
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("kernel", choices=KERNELS)
+    ap.add_argument("--batch", type=int, default=8, help="rows (sequences of a decode step)")
+    ap.add_argument("--ctx", type=int, default=512, help="cached tokens per sequence (attention kernels)")
+    ap.add_argument("--tokens", type=int, default=2048, help="new tokens (attn_prefill)")
+    ap.add_argument("--hidden", type=int, default=576)
+    ap.add_argument("--heads", type=int, default=9)
+    ap.add_argument("--kv-heads", type=int, default=3)
+    ap.add_argument("--head-dim", type=int, default=64)
+    ap.add_argument("--intermediate", type=int, default=1536)
+    ap.add_argument("--vocab", type=int, default=49152)
+    ap.add_argument("--splits", type=int, default=0, help="attn_decode: key splits (0: the engine's choice)")
+    ap.add_argument("--repeat", type=int, default=50)
+    ap.add_argument("--no-graph", action="store_true")
+    a = ap.parse_args(argv)
+    dev = ops.require_cuda("cuda:0")
+    M, hid, H, Hkv, D, I, V = a.batch, a.hidden, a.heads, a.kv_heads, a.head_dim, a.intermediate, a.vocab
+    bf = torch.bfloat16
+    copies = 40
+    rot = [0]
+
+    def nxt(ws):
+        rot[0] += 1
+        return ws[rot[0] % len(ws)]
+
+    h = torch.randn(M, hid, device=dev)
+    nw = torch.ones(hid, device=dev)
+    x = torch.randn(M, hid, device=dev).to(bf)
+    pos = torch.full((M,), a.ctx, dtype=torch.int32, device=dev)
+    seq = torch.arange(M, dtype=torch.int32, device=dev)
+    width = 1
+    while width < a.ctx // 64 + 1:
+        width *= 2
+    table = torch.arange(M * width, dtype=torch.int32, device=dev).view(M, width)
+    n_pages = M * width
+    inv = torch.ones(D // 2, device=dev)
+    bytes_read = 0
+    if a.kernel in ("qkv_rope", "attn_decode", "attn_prefill"):
+        kp = torch.randn(n_pages, Hkv, 64, D, device=dev).to(bf)
+        vp = torch.randn_like(kp)
+    if a.kernel == "qkv_rope":
+        ws = [torch.randn((H + 2 * Hkv) * D, hid, device=dev).to(bf) for _ in range(copies)]
+        q = torch.empty(M, H * D, device=dev, dtype=bf)
+        fn = lambda: ops.skinny_qkv_rope(h, (nw, 1e-5), nxt(ws), q, pos, seq, table, inv, D, kp, vp, H, Hkv, D)
+        bytes_read = ws[0].numel() * 2
+    elif a.kernel == "out_residual":
+        ws = [torch.randn(hid, H * D, device=dev).to(bf) for _ in range(copies)]
+        att = torch.randn(M, H * D, device=dev).to(bf)
+        fn = lambda: ops.skinny_linear(att, None, nxt(ws), None, residual=h)
+        bytes_read = ws[0].numel() * 2
+    elif a.kernel == "gate_up_swiglu":
+        ws = [torch.randn(2 * I, hid, device=dev).to(bf) for _ in range(copies)]
+        act = torch.empty(M, I, device=dev, dtype=bf)
+        fn = lambda: ops.skinny_swiglu(h, (nw, 1e-5), nxt(ws), act)
+        bytes_read = ws[0].numel() * 2
+    elif a.kernel == "down_residual":
+        ws = [torch.randn(hid, I, device=dev).to(bf) for _ in range(copies)]
+        act = torch.randn(M, I, device=dev).to(bf)
+        fn = lambda: ops.skinny_linear(act, None, nxt(ws), None, residual=h)
+        bytes_read = ws[0].numel() * 2
+    elif a.kernel == "head":
+        ws = [torch.randn(V, hid, device=dev).to(bf) for _ in range(4)]
+        logits = torch.empty(M, V, device=dev)
+        fn = lambda: ops.skinny_linear(x, None, nxt(ws), logits)
+        bytes_read = ws[0].numel() * 2
+    elif a.kernel == "attn_decode":
+        q = torch.randn(M, H * D, device=dev).to(bf)
+        splits = a.splits or ops.decode_splits(M, Hkv, H // Hkv, width)
+        partial = torch.empty(M * H * ops.MAX_DECODE_SPLITS * (D + 2), device=dev)
+        out = torch.empty(M, H * D, device=dev, dtype=bf)
+        fn = lambda: ops.attention_decode_bf16(q, H * D, kp, vp, table, pos, out, partial, ops.decode_counters(dev), H, Hkv, D,
+                                               splits, 1.0 / math.sqrt(D))
+        bytes_read = M * (a.ctx + 1) * 2 * Hkv * D * 2
+    elif a.kernel == "attn_prefill":
+        T = a.tokens
+        width = 1
+        while width < T // 64 + 1:
+            width *= 2
+        table = torch.arange(width, dtype=torch.int32, device=dev).view(1, width)
+        kp = torch.randn(width, Hkv, 64, D, device=dev).to(bf)
+        vp = torch.randn_like(kp)
+        qkv = torch.randn(T, (H + 2 * Hkv) * D, device=dev).to(bf)
+        positions = torch.arange(T, dtype=torch.int32, device=dev)
+        cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
+        out = torch.empty(T, H * D, device=dev, dtype=bf)
+        fn = lambda: ops.attention_prefill_bf16(qkv, (H + 2 * Hkv) * D, kp, vp, table, positions, cu, -(-T // 64), out, H, Hkv, D,
+                                                1.0 / math.sqrt(D))
+        bytes_read = 0
+    elif a.kernel == "add_rmsnorm":
+        out = torch.empty(M, hid, device=dev, dtype=bf)
+        fn = lambda: ops.add_rmsnorm(h, None, nw, 1e-5, out)
+        bytes_read = M * hid * 4
+    else:
+        logits = torch.randn(M, V, device=dev)
+        out = torch.empty(M, dtype=torch.int32, device=dev)
+        fn = lambda: ops.sample(logits, None, None, None, None, None, out)
+        bytes_read = M * V * 4
+    us = _time(fn, a.repeat, graph=not a.no_graph)
+    res = {"kernel": a.kernel, "rows": M, "us_per_launch": round(us, 3), "bytes_read": bytes_read,
+           "GB_per_s": round(bytes_read / us / 1e3, 1) if bytes_read else None}
+    if a.kernel == "attn_prefill":
+        flops = 4.0 * D * H * a.tokens * (a.tokens + 1) / 2
+        res["TFLOP_per_s"] = round(flops / us / 1e6, 1)
+    print(json.dumps(res))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

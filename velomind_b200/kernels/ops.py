@@ -161,9 +161,9 @@ def decode_counters(device) -> torch.Tensor:
 def decode_splits(B: int, Hkv: int, G: int, table_width: int) -> int:
     """How many CTAs share the keys of one (sequence, kv head): enough to fill the GPU, a function of the
     step's SHAPE only (so that a captured launch stays valid as sequences grow)."""
-    gm = 1 if G <= 1 else 2 if G <= 2 else 4 if G <= 4 else 8
-    groups = B * Hkv * (-(-G // gm))
-    want = -(-2 * 148 // groups)
+    groups = B * Hkv * (-(-G // 16))          # a CTA serves up to 16 query heads of one kv head
+    want = -(-148 // groups)                  # about one CTA per SM ...
+    table_width = max(1, table_width // 4)    # ... and at least a page per warp of a CTA (the width bounds the pages)
     return max(1, min(want, MAX_DECODE_SPLITS, table_width))
 
 
@@ -221,7 +221,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
         torch.mm(x, weight.t(), out_dtype=out.dtype, out=out)
 
 
-SKINNY_MAX_ROWS = 64
+SKINNY_MAX_ROWS = 16       # beyond this the library product wins (the A tile is staged once per CTA)
 SKINNY_NORM_ROWS = 16      # up to this many rows the norm is fused into the product that follows it
 
 
