@@ -238,11 +238,11 @@ def main() -> int:
         "metric": "decode tok/s at batch 8 (SmolLM2-135M shape, prompts of 512 tokens)",
         "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"model": "SmolLM2-135M shape, random weights", "global_batch": B, "seq_len": prompt_len,
-                   "context": context, "parallelism": "single GPU", "layers": layers, "layers_of_config": full_layers,
+        "config": {"model": "SmolLM2-135M shape, random weights", "global_batch": B, "seq_len": prompt_len, "context": context,
+                   "parallelism": "single GPU", "layers": layers, "layers_of_config": full_layers,
                    "hidden": cfg["hidden_size"], "heads": H, "kv_heads": cfg["num_key_value_heads"], "head_dim": D,
                    "intermediate": cfg["intermediate_size"], "vocab": vocab, "rope_theta": cfg["rope_theta"],
-                   "rms_eps": cfg["rms_norm_eps"], "tied": True, "sampling": "greedy on device",
+                   "rms_eps": cfg["rms_norm_eps"], "tied_embeddings": True, "sampling": "greedy on device",
                    "l2": "inputs larger than L2 (weights + cache > 126 MB)", "peaks": pk["source"]},
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"]},

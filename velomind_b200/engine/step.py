@@ -184,6 +184,7 @@ class Engine:
         self._graphs: Dict[Tuple, "torch.cuda.CUDAGraph"] = {}
         self.use_graphs = (GRAPHS_DEFAULT if use_graphs is None else bool(use_graphs)) and model.graph_safe
         self.graphs_captured = 0
+        self._shape_seen: Dict[Tuple, int] = {}
         self.steps_run = 0
 
     # ---- slots
@@ -303,9 +304,11 @@ class Engine:
         self.ws.end()
 
     def _replay_graph(self, ctx: StepContext, bucket, shape_key) -> None:
-        """Decode steps (one token per sequence) are launch-bound: the kernels of a step are captured once
-        per batch shape into a CUDA graph and replayed.  Everything that changes from step to step (tokens,
-        positions, lengths, block tables) lies in the descriptor buffer, which the graph reads."""
+        """Steps are launch-bound (hundreds of small kernels): the kernels of a step are captured once per
+        step shape into a CUDA graph and replayed.  Everything that changes from step to step (tokens,
+        positions, lengths, block tables) lies in the descriptor buffer, which the graph reads.  A decode
+        step's shape is (batch, table widths); any other step's shape also names each sequence's number of
+        new tokens and the wanted rows, and is recorded only when it repeats."""
         key = (bucket, shape_key, self.ws.generation)
         graph = self._graphs.get(key)
         if graph is None:
@@ -314,6 +317,7 @@ class Engine:
             ctx.capturing = True
             graph = torch.cuda.CUDAGraph()
             torch.cuda.current_stream().synchronize()
+            own, lib = ops.launch_count, ops.library_calls
             self.ws.begin(bucket)
             try:
                 with torch.cuda.graph(graph):
@@ -322,9 +326,14 @@ class Engine:
                 self.ws.abort()
                 raise
             self.ws.end()
+            # what a replay launches: counted once here, added to the counters at every replay
+            graph.launches = (ops.launch_count - own, ops.library_calls - lib)
+            ops.launch_count, ops.library_calls = own, lib
             self._graphs[key] = graph
             self.graphs_captured += 1
         graph.replay()
+        ops.launch_count += graph.launches[0]
+        ops.library_calls += graph.launches[1]
 
     def _run_chunk(self, entries, chunk, logits, row0, produced) -> int:
         cache = self.cache
@@ -381,8 +390,18 @@ class Engine:
         ctx = StepContext(self, desc, T, B, R, widths)
         ctx.logits = logits[row0: row0 + R]
         bucket = (desc.caps[0], desc.caps[1], desc.caps[2], ctx.one_token_each)   # decode steps take other scratch
-        if self.use_graphs and ctx.one_token_each and self.ws.planned(bucket):
-            self._replay_graph(ctx, bucket, (T, B, R, tuple(widths), ctx.logits.data_ptr()))
+        lens = tuple(int(x) for x in np.diff(ctx.host_cu_tokens)) if not ctx.one_token_each else ()
+        shape_key = (T, B, R, tuple(widths), ctx.logits.data_ptr(), lens)
+        use_graph = self.use_graphs and self.ws.planned(bucket)
+        if use_graph and not ctx.one_token_each:
+            # other steps (prompts) are recorded only when the very same shape comes a second time
+            seen = self._shape_seen.get(shape_key, 0) + 1
+            if len(self._shape_seen) > 4096:
+                self._shape_seen.clear()
+            self._shape_seen[shape_key] = seen
+            use_graph = seen >= 2
+        if use_graph:
+            self._replay_graph(ctx, bucket, shape_key)
         else:
             self._run_eager(ctx, bucket)
         for s, (i, a, b) in enumerate(chunk):

@@ -195,7 +195,7 @@ def attention(ctx, q: torch.Tensor, q_row_stride: int, k_pages: torch.Tensor, v_
         attention_decode_bf16(q, q_row_stride, k_pages, v_pages, block_table, ctx.positions, out, partial,
                               decode_counters(out.device), H, Hkv, D, n_splits, scale, window, ctx.err)
         ctx.ws.give(partial)
-    elif fast and not ctx.capturing:
+    elif fast:      # the tile count follows from the sequences' new-token counts, which are part of a recorded step's shape
         lens = ctx.host_cu_tokens[1:] - ctx.host_cu_tokens[:-1]
         n_tiles = int(((lens + 63) // 64).sum())
         attention_prefill_bf16(q, q_row_stride, k_pages, v_pages, block_table, ctx.positions, ctx.cu_tokens, n_tiles, out,
