@@ -273,6 +273,44 @@ def skinny_qkv_rope(x: torch.Tensor, norm, weight: torch.Tensor, q_out: torch.Te
                                         _c_int(H), _c_int(Hkv), _c_int(D), _c_int(n_pages), _ptr(err), _stream()), "skinny_qkv_rope")
 
 
+def tc_ok(M: int, K: int, weight: torch.Tensor) -> bool:
+    """True if the tensor-core (tcgen05 + TMA) products take this shape: bfloat16, rows of 16-byte multiples."""
+    return M > 0 and K % 8 == 0 and weight.dtype == torch.bfloat16 and weight.is_contiguous()
+
+
+def tc_linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor], residual: Optional[torch.Tensor] = None,
+              err: Optional[torch.Tensor] = None) -> None:
+    """out = x W^T (bf16 or float32 out) or residual += x W^T (float32), on tcgen05 tensor cores.
+    x bf16 [M, K] with unit column stride (rows may be strided), weight bf16 [N, K]."""
+    M, K = x.shape
+    N = weight.shape[0]
+    if x.stride(1) != 1:
+        raise KernelError("tc_linear: x must have unit column stride")
+    _check(library().vm_tc_linear(_ptr(x), _c_ll(x.stride(0)), _ptr(weight), _c_int(M), _c_int(N), _c_int(K), _ptr(out),
+                                  _c_int(out.stride(0) if out is not None else N),
+                                  _c_int(1 if (out is not None and out.dtype == torch.float32) else 0), _ptr(residual),
+                                  _ptr(err), _stream()), "tc_linear")
+
+
+def tc_swiglu(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, err: Optional[torch.Tensor] = None) -> None:
+    """out[M, I] = silu(x Wg^T) * (x Wu^T) with weight = [Wg; Wu] stacked [2I, K]; I a multiple of 64."""
+    M, K = x.shape
+    _check(library().vm_tc_swiglu(_ptr(x), _c_ll(x.stride(0)), _ptr(weight), _c_int(M), _c_int(out.shape[1]), _c_int(K),
+                                  _ptr(_contig(out, "out")), _ptr(err), _stream()), "tc_swiglu")
+
+
+def tc_qkv_rope(x: torch.Tensor, weight: torch.Tensor, q_out: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
+                block_table: torch.Tensor, inv_freq: Optional[torch.Tensor], rot_dim: int, k_pages: Optional[torch.Tensor],
+                v_pages: Optional[torch.Tensor], H: int, Hkv: int, D: int, err: Optional[torch.Tensor] = None) -> None:
+    """Like skinny_qkv_rope for many rows: one head per tile, rotation and cache write in the epilogue. D 64 or 128."""
+    M, K = x.shape
+    n_pages = k_pages.shape[0] if k_pages is not None else 0
+    _check(library().vm_tc_qkv_rope(_ptr(x), _c_ll(x.stride(0)), _ptr(weight), _c_int(M), _c_int(K), _ptr(_contig(q_out, "q_out")),
+                                    _ptr(positions), _ptr(seq_of_token), _ptr(block_table), _c_int(block_table.shape[1]),
+                                    _ptr(inv_freq), _c_int(rot_dim), _ptr(k_pages), _ptr(v_pages), _c_int(H), _c_int(Hkv),
+                                    _c_int(D), _c_int(n_pages), _ptr(err), _stream()), "tc_qkv_rope")
+
+
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor, seed: torch.Tensor,
            stream_id: torch.Tensor, step: torch.Tensor, out: torch.Tensor) -> None:
     """One token per row of logits float32 [R, V]: greedy where temperature <= 0 or top_p <= 0, else
