@@ -379,3 +379,75 @@ def test_skinny_qkv_rope(H, Hkv, D, K, rot):
     assert (dk.float().cpu() - kp).abs().max() <= 2e-2 * scale
     assert (dv.float().cpu() - vp).abs().max() <= 2e-2 * scale
     assert float(dk.float().abs().sum()) > 0
+
+
+# ------------------------------------------------------------------------------------------ tensor-core (tcgen05 + TMA) products
+def _err_word():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+@pytest.mark.parametrize("M", [17, 128, 300, 2048])
+@pytest.mark.parametrize("N,K", [(64, 64), (576, 576), (200, 160), (960, 576), (576, 1536), (1000, 72)])
+def test_tc_linear(M, N, K):
+    o = ops()
+    x = _bf(torch.randn(M, K, generator=_gen(M + N)))
+    w = _bf(torch.randn(N, K, generator=_gen(K)) * 0.1)
+    want = x.float() @ w.float().t()
+    big = max(1.0, float(want.abs().max()))
+    err = _err_word()
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    o.tc_linear(x.to(DEV), w.to(DEV), out, err=err)
+    assert (out.float().cpu() - want).abs().max() <= 1e-2 * big
+    out32 = torch.full((M, N + 5), float("nan"), device=DEV)                   # a strided float32 output
+    o.tc_linear(x.to(DEV), w.to(DEV), out32[:, :N], err=err)
+    assert (out32[:, :N].cpu() - want).abs().max() <= 2e-5 * big and torch.isnan(out32[:, N:]).all()
+    h = torch.randn(M, N, generator=_gen(5))
+    hd = h.to(DEV)
+    o.tc_linear(x.to(DEV), w.to(DEV), None, residual=hd, err=err)
+    assert (hd.cpu() - (h + want)).abs().max() <= 2e-5 * big
+    # x as a view with a row pitch (a slice of a wider buffer)
+    wide = torch.zeros(M, K + 24, dtype=torch.bfloat16, device=DEV)
+    wide[:, :K] = x.to(DEV)
+    o.tc_linear(wide[:, :K], w.to(DEV), out, err=err)
+    assert (out.float().cpu() - want).abs().max() <= 1e-2 * big
+    assert int(err.item()) == 0
+
+
+@pytest.mark.parametrize("M,I,K", [(40, 192, 64), (2048, 1536, 576), (129, 64, 96), (500, 2560, 960)])
+def test_tc_swiglu(M, I, K):
+    o = ops()
+    x = _bf(torch.randn(M, K, generator=_gen(M)))
+    w = _bf(torch.randn(2 * I, K, generator=_gen(K)) * 0.2)
+    gu = x.float() @ w.float().t()
+    want = torch.from_numpy(P.swiglu(gu[:, :I].numpy(), gu[:, I:].numpy()))
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    err = _err_word()
+    o.tc_swiglu(x.to(DEV), w.to(DEV), out, err)
+    assert int(err.item()) == 0
+    assert (out.float().cpu() - want).abs().max() <= 1e-2 * float(want.abs().max())
+
+
+@pytest.mark.parametrize("H,Hkv,D,K,rot", [(9, 3, 64, 576, 64), (2, 1, 128, 256, 128), (3, 3, 64, 96, 0)])
+def test_tc_qkv_rope(H, Hkv, D, K, rot):
+    o = ops()
+    lens_before, new = [3, 70, 0], [150, 1, 120]
+    T = sum(new)
+    x = _bf(torch.randn(T, K, generator=_gen(H)))
+    w = _bf(torch.randn((H + 2 * Hkv) * D, K, generator=_gen(K)) * 0.2)
+    positions = torch.cat([torch.arange(a, a + n) for a, n in zip(lens_before, new)]).int()
+    seq = torch.cat([torch.full((n,), s) for s, n in enumerate(new)]).int()
+    table = torch.tensor([[5, 1, 9], [2, 7, -1], [0, 3, -1]], dtype=torch.int32)
+    inv_freq = torch.from_numpy((1.0 / np.power(np.float32(5000.0), np.arange(rot // 2, dtype=np.float32) * 2 / max(rot, 1))).astype(np.float32)) if rot else None
+    qkv = x.float() @ w.float().t()
+    kp = torch.zeros(10, Hkv, 64, D); vp = torch.zeros_like(kp)
+    E.rope_kv_write(qkv, positions, seq, table, inv_freq, rot, kp, vp, H, Hkv, D)
+    dq = torch.full((T, H * D), float("nan"), dtype=torch.bfloat16, device=DEV)
+    dk = torch.zeros(10, Hkv, 64, D, dtype=torch.bfloat16, device=DEV); dv = torch.zeros_like(dk)
+    err = _err_word()
+    o.tc_qkv_rope(x.to(DEV), w.to(DEV), dq, positions.to(DEV), seq.to(DEV), table.to(DEV),
+                  None if inv_freq is None else inv_freq.to(DEV), rot, dk, dv, H, Hkv, D, err)
+    assert int(err.item()) == 0
+    scale = float(qkv.abs().max())
+    assert (dq.float().cpu() - qkv[:, : H * D]).abs().max() <= 1e-2 * scale
+    assert (dk.float().cpu() - kp).abs().max() <= 1e-2 * scale
+    assert (dv.float().cpu() - vp).abs().max() <= 1e-2 * scale

@@ -12,7 +12,7 @@
 // as a kernel of its own.
 //
 // One CTA computes a 128 x BN tile.  Warp 0 (one lane) is the TMA producer: cp.async.bulk.tensor loads of a
-// 128 x 64 tile of x and a BN x 64 tile of W per k block into a 4-stage ring of 128-byte-swizzled shared
+// 128 x 64 tile of x and a BN x 64 tile of W per k block into a 3-stage ring of 128-byte-swizzled shared
 // memory, completion on mbarriers.  Warp 1 (one lane) issues tcgen05.mma (cta_group::1, kind::f16, M = 128,
 // N = BN, K = 16) four times per k block and frees each stage with tcgen05.commit.  Warps 2..5 are the
 // epilogue: each reads its 32 lanes of the accumulator with tcgen05.ld, applies the fused operation and
@@ -27,7 +27,7 @@ namespace {
 
 enum : int { TC_STORE_BF16 = 0, TC_STORE_F32 = 1, TC_RESIDUAL = 2, TC_SWIGLU = 3, TC_ROPE_KV = 4 };
 
-constexpr int TC_BM = 128, TC_BK = 64, TC_STAGES = 4;
+constexpr int TC_BM = 128, TC_BK = 64, TC_STAGES = 3;     // 3 stages: two or three CTAs fit an SM, one's epilogue overlaps another's main loop
 constexpr int TC_THREADS = 192;
 constexpr uint32_t TC_WAIT_LIMIT = 1u << 20;
 
@@ -198,6 +198,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN; c0 += 32) {
                     uint32_t v[32];
+                    __syncwarp();
                     tc_ld32(taddr + c0, v);
                     tc_ld_wait();
                     const int col0 = n0 + c0;
@@ -252,6 +253,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll 1
                 for (int c0 = 0; c0 < half; c0 += 32) {
                     uint32_t lo[32], hi[32];
+                    __syncwarp();                                      // lanes that skipped the last round's stores are back
                     tc_ld32(taddr + c0, lo);
                     tc_ld32(taddr + half + c0, hi);
                     tc_ld_wait();

@@ -232,7 +232,7 @@ class Engine:
         if code:
             self.err.zero_()
             what = {1: "a token id outside the vocabulary", 2: "a cache write without a page",
-                    3: "a cache read without a page"}.get(code, f"code {code}")
+                    3: "a cache read without a page", 4: "a tensor-core kernel gave up waiting on a barrier"}.get(code, f"code {code}")
             raise CacheError(f"a kernel reported {what}")
 
     # ---- internals

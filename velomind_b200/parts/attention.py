@@ -57,29 +57,42 @@ class GroupedQueryAttention(Part):
         return CacheNeed("window" if self.window > 0 else "all", self.kv_heads, self.head_dim, self.window)
 
     def can_fuse(self, ctx, norm) -> bool:
-        """True if this step can run as: [norm + qkv + rotary + cache write] -> attention -> [out + residual]."""
-        rms = getattr(norm, "as_rms", None)
-        return (rms is not None and ctx.act_dtype == torch.bfloat16 and ops.skinny_ok(ctx.T, self.hidden, self.qkv.weight)
-                and ops.skinny_ok(ctx.T, self.heads * self.head_dim, self.out.weight) and self.head_dim % 16 == 0
-                and self.rotary_dim in (0, self.head_dim) and self.hidden % 8 == 0)
+        """True if this step can run as: [norm +] qkv + rotary + cache write -> attention -> out + residual,
+        with the weight-streaming kernels (few tokens) or the tensor-core kernels (many tokens)."""
+        if getattr(norm, "as_rms", None) is None or ctx.act_dtype != torch.bfloat16:
+            return False
+        if self.qkv.weight.dtype != torch.bfloat16 or self.out.weight.dtype != torch.bfloat16:
+            return False
+        if self.rotary_dim not in (0, self.head_dim) or self.hidden % 8 or (self.heads * self.head_dim) % 8:
+            return False
+        if ctx.T <= ops.SKINNY_MAX_ROWS:
+            return self.hidden % 32 == 0 and (self.heads * self.head_dim) % 32 == 0 and self.head_dim % 16 == 0
+        return self.head_dim in (64, 128)
 
     def forward_fused(self, ctx, h: torch.Tensor, norm) -> None:
-        """h += attention(norm(h)) in three launches (few tokens, bfloat16)."""
+        """h += attention(norm(h)): three or four launches."""
         H, Hkv, D = self.heads, self.kv_heads, self.head_dim
         q = ctx.take_tokens(H * D, torch.bfloat16)
         k_pages, v_pages, table, owns = ctx.kv()
-        x, rms = h, norm.as_rms()
-        if ctx.T > ops.SKINNY_NORM_ROWS:          # many rows: norm once, not once per CTA
-            x, rms = ctx.take_tokens(self.hidden, torch.bfloat16), None
+        kp, vp = (k_pages, v_pages) if owns else (None, None)
+        skinny = ctx.T <= ops.SKINNY_MAX_ROWS
+        if skinny and ctx.T <= ops.SKINNY_NORM_ROWS:
+            ops.skinny_qkv_rope(h, norm.as_rms(), self.qkv.weight, q, ctx.positions, ctx.seq_of_token, table, self.inv_freq,
+                                self.rotary_dim, kp, vp, H, Hkv, D, ctx.err)
+        else:
+            x = ctx.take_tokens(self.hidden, torch.bfloat16)          # many rows: norm once, not once per CTA
             norm.forward(ctx, h, None, x)
-        ops.skinny_qkv_rope(x, rms, self.qkv.weight, q, ctx.positions, ctx.seq_of_token, table, self.inv_freq,
-                            self.rotary_dim, k_pages if owns else None, v_pages if owns else None, H, Hkv, D, ctx.err)
-        if x is not h:
+            qkv_rope = ops.skinny_qkv_rope if skinny else ops.tc_qkv_rope
+            args = (x, None, self.qkv.weight) if skinny else (x, self.qkv.weight)
+            qkv_rope(*args, q, ctx.positions, ctx.seq_of_token, table, self.inv_freq, self.rotary_dim, kp, vp, H, Hkv, D, ctx.err)
             ctx.ws.give(x)
         att = ctx.take_tokens(H * D, torch.bfloat16)
         ops.attention(ctx, q, H * D, k_pages, v_pages, table, att, H, Hkv, D, self.scale, self.window)
         ctx.ws.give(q)
-        ops.skinny_linear(att, None, self.out.weight, None, residual=h)
+        if skinny:
+            ops.skinny_linear(att, None, self.out.weight, None, residual=h)
+        else:
+            ops.tc_linear(att, self.out.weight, None, residual=h, err=ctx.err)
         ctx.ws.give(att)
 
     def forward(self, ctx, x: torch.Tensor, out: torch.Tensor) -> None:

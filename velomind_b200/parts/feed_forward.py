@@ -32,22 +32,32 @@ class SwiGLU(Part):
         self.down = Linear([weights["down_proj.weight"]], bc)
 
     def can_fuse(self, ctx, norm) -> bool:
-        rms = getattr(norm, "as_rms", None)
-        return (rms is not None and ctx.act_dtype == torch.bfloat16 and ops.skinny_ok(ctx.T, self.hidden, self.gate_up.weight)
-                and ops.skinny_ok(ctx.T, self.intermediate, self.down.weight) and self.intermediate % 8 == 0
-                and self.hidden % 8 == 0)
+        if getattr(norm, "as_rms", None) is None or ctx.act_dtype != torch.bfloat16:
+            return False
+        if self.gate_up.weight.dtype != torch.bfloat16 or self.down.weight.dtype != torch.bfloat16:
+            return False
+        if ctx.T <= ops.SKINNY_MAX_ROWS:
+            return self.hidden % 32 == 0 and self.intermediate % 32 == 0
+        return self.hidden % 8 == 0 and self.intermediate % 64 == 0
 
     def forward_fused(self, ctx, h: torch.Tensor, norm) -> None:
-        """h += down(silu(gate(norm(h))) * up(norm(h))) in two launches (few tokens, bfloat16)."""
-        x, rms = h, norm.as_rms()
-        if ctx.T > ops.SKINNY_NORM_ROWS:          # many rows: norm once, not once per CTA
-            x, rms = ctx.take_tokens(self.hidden, torch.bfloat16), None
-            norm.forward(ctx, h, None, x)
+        """h += down(silu(gate(norm(h))) * up(norm(h))): two or three launches."""
         act = ctx.take_tokens(self.intermediate, torch.bfloat16)
-        ops.skinny_swiglu(x, rms, self.gate_up.weight, act)
-        if x is not h:
+        skinny = ctx.T <= ops.SKINNY_MAX_ROWS
+        if skinny and ctx.T <= ops.SKINNY_NORM_ROWS:
+            ops.skinny_swiglu(h, norm.as_rms(), self.gate_up.weight, act)
+        else:
+            x = ctx.take_tokens(self.hidden, torch.bfloat16)          # many rows: norm once, not once per CTA
+            norm.forward(ctx, h, None, x)
+            if skinny:
+                ops.skinny_swiglu(x, None, self.gate_up.weight, act)
+            else:
+                ops.tc_swiglu(x, self.gate_up.weight, act, ctx.err)
             ctx.ws.give(x)
-        ops.skinny_linear(act, None, self.down.weight, None, residual=h)
+        if skinny:
+            ops.skinny_linear(act, None, self.down.weight, None, residual=h)
+        else:
+            ops.tc_linear(act, self.down.weight, None, residual=h, err=ctx.err)
         ctx.ws.give(act)
 
     def forward(self, ctx, x: torch.Tensor, out: torch.Tensor) -> None:
