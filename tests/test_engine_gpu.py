@@ -137,3 +137,17 @@ def test_stop_token_ends_a_sequence_early(model_folders):
     assert [r.tokens for r in got] == want
     assert got[0].finish_reason == "stop" and got[0].tokens[-1] == stop
     assert eng.engine.cache.slots.held_count == 0
+
+
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_fused_tensor_core_prefill_matches_plain(model_folders, name):
+    """bfloat16 with the tcgen05 kernels (fused epilogues) switched on for every step of more than 16 tokens.
+    The tiny head sizes (16, 32) are refused by the fused qkv kernel, so the attention part falls back while the
+    feed-forward of tiny A (intermediate 192) takes the fused path; both must agree with the plain model."""
+    folder = model_folders[name]
+    requests = S.make_requests(CONFIGS[name]["vocab_size"], (150, 70, 300, 17), seed=4)
+    plain = S.plain_logits(folder, requests)
+    steps = S.steps_unequal_batches(requests, batch=2)
+    engine = _engine(folder, "bfloat16", max_tokens=64 * 16, fused_prefill_rows=17)
+    got = S.run_steps_in_process(engine, steps)
+    _compare(got, S.expected_rows(steps, requests, plain), TOL["bfloat16"])

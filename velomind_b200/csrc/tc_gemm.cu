@@ -11,12 +11,13 @@
 // The reference multiplies with cuBLAS SGEMM (src/cuda/ops/matmul.cu:87-126) and runs each elementwise step
 // as a kernel of its own.
 //
-// One CTA computes a 128 x BN tile.  Warp 0 (one lane) is the TMA producer: cp.async.bulk.tensor loads of a
-// 128 x 64 tile of x and a BN x 64 tile of W per k block into a 3-stage ring of 128-byte-swizzled shared
-// memory, completion on mbarriers.  Warp 1 (one lane) issues tcgen05.mma (cta_group::1, kind::f16, M = 128,
-// N = BN, K = 16) four times per k block and frees each stage with tcgen05.commit.  Warps 2..5 are the
-// epilogue: each reads its 32 lanes of the accumulator with tcgen05.ld, applies the fused operation and
-// writes global memory.  No multicast, no clusters.
+// CTAs are persistent: each walks over 128 x BN output tiles (tile index += grid size).  Warp 0 (one lane) is
+// the TMA producer: cp.async.bulk.tensor loads of a 128 x 64 tile of x and a BN x 64 tile of W per k block into
+// a ring of 128-byte-swizzled shared-memory stages, completion on mbarriers.  Warp 1 (one lane) issues
+// tcgen05.mma (cta_group::1, kind::f16, M = 128, N = BN, K = 16) four times per k block and frees each stage
+// with tcgen05.commit.  The accumulator is double-buffered in tensor memory (2 x BN columns): warps 2..5, the
+// epilogue, read tile t with tcgen05.ld, apply the fused operation and write global memory while the MMAs of
+// tile t+1 run.  No multicast, no clusters.
 //
 // Every wait on an mbarrier is bounded; when a wait gives up, the CTA raises an error word, waits (bounded)
 // for its own copies in flight, frees its tensor memory and returns.
@@ -27,7 +28,7 @@ namespace {
 
 enum : int { TC_STORE_BF16 = 0, TC_STORE_F32 = 1, TC_RESIDUAL = 2, TC_SWIGLU = 3, TC_ROPE_KV = 4 };
 
-constexpr int TC_BM = 128, TC_BK = 64, TC_STAGES = 3;     // 3 stages: two or three CTAs fit an SM, one's epilogue overlaps another's main loop
+constexpr int TC_BM = 128, TC_BK = 64;
 constexpr int TC_THREADS = 192;
 constexpr uint32_t TC_WAIT_LIMIT = 1u << 20;
 
@@ -40,6 +41,8 @@ struct TcParams {
     const float* inv_freq; int rot_dim;
     __nv_bfloat16* kpages; __nv_bfloat16* vpages; int H, Hkv, D, n_pages;
     int* err;                        // cache faults (2) and abandoned waits (4)
+    int tiles_m, tiles_n;
+    int tma_residual;                // the residual sum leaves through TMA reduce-add (map_h is valid)
 };
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -99,32 +102,32 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
 
 template <int BN>
 __global__ void __launch_bounds__(TC_THREADS)
-tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p) {
+tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_h, const TcParams p) {
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;                     // a power of two >= 32 (BN is 64, 128 or 256)
+    constexpr int STAGES = BN <= 64 ? 4 : 3;
+    constexpr uint32_t TMEM_COLS = 2 * BN;                                // two accumulators; a power of two >= 32
     // instruction descriptor: float32 accumulate (bits 4-5 = 1), A and B bf16 (bits 7-9, 10-12 = 1), both K-major,
     // N >> 3 in bits 17-22, M >> 4 in bits 24-28
     constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
-    extern __shared__ unsigned char smem_raw[];
-    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    __shared__ __align__(8) unsigned long long bars[2 * TC_STAGES + 1];
-    __shared__ uint32_t tmem_base_slot;
-    __shared__ int abort_flag;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];          // swizzled tiles want 1024-byte alignment (checked below)
+    unsigned char* tiles = smem_raw;
+    // no static shared memory: the bookkeeping sits behind the tiles, so that two CTAs fit one SM
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(tiles + (size_t)STAGES * STAGE_BYTES + 4 * 4096);   // full[S], empty[S], accum_full[2], accum_empty[2]
+    uint32_t& tmem_base_slot = *reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    int& abort_flag = *reinterpret_cast<int*>(bars + 2 * STAGES + 5);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * TC_BM;
-    const int tile_n = blockIdx.x;
     const int half = BN / 2;
-    // where the tile's W rows start (two row ranges for the paired epilogues)
-    int n0 = tile_n * BN, n1 = -1;
-    if (p.epi == TC_SWIGLU) { n0 = tile_n * half; n1 = p.I + n0; }
     const int num_kb = (p.K + TC_BK - 1) / TC_BK;
-    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[TC_STAGES]), accum_bar = smem_u32(&bars[2 * TC_STAGES]);
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
+    const uint32_t accf0 = smem_u32(&bars[2 * STAGES]), acce0 = smem_u32(&bars[2 * STAGES + 2]);
 
     if (threadIdx.x == 0) {
-        abort_flag = 0;
-        for (int s = 0; s < TC_STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-        mbar_init(accum_bar, 1);
+        abort_flag = (smem_u32(tiles) & 1023u) ? 1 : 0;       // misaligned tiles would give wrong sums: give up instead
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(accf0 + 8 * a, 1); mbar_init(acce0 + 8 * a, 4); }   // 4 epilogue warps free an accumulator
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {                     // one warp owns the tensor-memory allocation
@@ -140,60 +143,80 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            int issued = 0;
-            for (int kb = 0; kb < num_kb; ++kb) {
-                const int s = kb % TC_STAGES;
-                const uint32_t round = (uint32_t)(kb / TC_STAGES);
-                if (!mbar_wait(empty0 + 8 * s, (round & 1u) ^ 1u, abort_p)) break;
-                const uint32_t full = full0 + 8 * s;
-                const uint32_t a_dst = smem_u32(tiles + (size_t)s * STAGE_BYTES), b_dst = a_dst + A_BYTES;
-                mbar_expect_tx(full, STAGE_BYTES);
-                tma_load_2d(a_dst, &map_a, kb * TC_BK, m0, full);
-                if (n1 < 0) tma_load_2d(b_dst, &map_b, kb * TC_BK, n0, full);
-                else {                                   // two row ranges of W, half a tile each
+            int it = 0;                                  // k blocks issued so far, over all of this CTA's tiles
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int tile_m = tile / p.tiles_n, tile_n = tile - tile_m * p.tiles_n;
+                const int m0 = tile_m * TC_BM;
+                int n0 = tile_n * BN, n1 = -1;           // where the tile's W rows start (two ranges for swiglu)
+                if (p.epi == TC_SWIGLU) { n0 = tile_n * half; n1 = p.I + n0; }
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t round = (uint32_t)(it / STAGES);
+                    ok = mbar_wait(empty0 + 8 * s, (round & 1u) ^ 1u, abort_p);
+                    if (!ok) break;
+                    const uint32_t full = full0 + 8 * s;
+                    const uint32_t a_dst = smem_u32(tiles + (size_t)s * STAGE_BYTES), b_dst = a_dst + A_BYTES;
+                    mbar_expect_tx(full, STAGE_BYTES);
+                    tma_load_2d(a_dst, &map_a, kb * TC_BK, m0, full);
                     tma_load_2d(b_dst, &map_b, kb * TC_BK, n0, full);
-                    tma_load_2d(b_dst + B_BYTES / 2, &map_b, kb * TC_BK, n1, full);
+                    if (n1 >= 0) tma_load_2d(b_dst + B_BYTES / 2, &map_b, kb * TC_BK, n1, full);   // half a tile each
                 }
-                issued = kb + 1;
             }
             if (*abort_p) {
                 // gave up somewhere: let the copies that are still in flight land before the CTA's memory goes away
-                for (int kb = max(0, issued - TC_STAGES); kb < issued; ++kb) {
+                for (int j = max(0, it - STAGES); j < it; ++j) {
                     uint32_t done = 0;
-                    for (uint32_t it = 0; it < TC_WAIT_LIMIT && !done; ++it)
+                    for (uint32_t w = 0; w < TC_WAIT_LIMIT && !done; ++w)
                         asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                                     : "=r"(done) : "r"(full0 + 8 * (kb % TC_STAGES)), "r"((uint32_t)(kb / TC_STAGES) & 1u) : "memory");
+                                     : "=r"(done) : "r"(full0 + 8 * (j % STAGES)), "r"((uint32_t)(j / STAGES) & 1u) : "memory");
                 }
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
+            int it = 0, t = 0;
             bool ok = true;
-            for (int kb = 0; kb < num_kb && ok; ++kb) {
-                const int s = kb % TC_STAGES;
-                const uint32_t round = (uint32_t)(kb / TC_STAGES);
-                ok = mbar_wait(full0 + 8 * s, round & 1u, abort_p);
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
+                const int a = t & 1;
+                ok = mbar_wait(acce0 + 8 * a, (((uint32_t)t >> 1) & 1u) ^ 1u, abort_p);     // the epilogue has drained this accumulator
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t a_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
-                const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(b_addr);
+                const uint32_t tmem_d = tmem_base + (uint32_t)(a * BN);
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t round = (uint32_t)(it / STAGES);
+                    ok = mbar_wait(full0 + 8 * s, round & 1u, abort_p);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
+                    const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(b_addr);
 #pragma unroll
-                for (int k = 0; k < TC_BK / 16; ++k)      // +32 bytes per k step: +2 in the descriptor's 16-byte units
-                    tc_mma_bf16(tmem_base, da + 2 * k, db + 2 * k, IDESC, (kb > 0 || k > 0) ? 1u : 0u);
-                tc_commit(empty0 + 8 * s);                // the stage is free once these MMAs have read it
+                    for (int k = 0; k < TC_BK / 16; ++k)  // +32 bytes per k step: +2 in the descriptor's 16-byte units
+                        tc_mma_bf16(tmem_d, da + 2 * k, db + 2 * k, IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+                    tc_commit(empty0 + 8 * s);            // the stage is free once these MMAs have read it
+                }
+                if (ok) tc_commit(accf0 + 8 * a);         // the accumulator is complete once all MMAs are done
             }
-            if (ok) tc_commit(accum_bar);                 // the accumulator is complete once all MMAs are done
         }
     } else {
         // ------------------------------------------------------------ epilogue: warps 2..5, lanes 32 * (warp % 4) ..
         const int quarter = warp & 3;
+        int t = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
+        const int tile_m = tile / p.tiles_n, tile_n = tile - tile_m * p.tiles_n;
+        const int m0 = tile_m * TC_BM;
+        int n0 = tile_n * BN;
+        if (p.epi == TC_SWIGLU) n0 = tile_n * half;
+        const int acc = t & 1;
         const int row = m0 + quarter * 32 + lane;
         const bool row_ok = row < p.M;
-        const bool ready = __all_sync(0xffffffffu, mbar_wait(accum_bar, 0u, abort_p));   // the same answer for the whole warp
+        const bool ready = __all_sync(0xffffffffu, mbar_wait(accf0 + 8 * acc, ((uint32_t)t >> 1) & 1u, abort_p));   // one answer per warp
         tc_fence_after();
-        if (ready) {
-            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        if (!ready) break;
+        {
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
             if (p.epi == TC_STORE_BF16 || p.epi == TC_STORE_F32 || p.epi == TC_RESIDUAL) {
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -202,6 +225,29 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     tc_ld32(taddr + c0, v);
                     tc_ld_wait();
                     const int col0 = n0 + c0;
+                    if (p.epi == TC_RESIDUAL && p.tma_residual) {
+                        // h += chunk, asynchronously: the 32 x 32 float chunk goes to shared memory (128-byte swizzle, so
+                        // that the lanes' 16-byte stores spread over the banks) and a TMA reduce-add carries it to global
+                        // memory; rows and columns beyond the matrix are clipped by the copy engine
+                        if (col0 >= p.N) continue;                     // warp-uniform
+                        float* stg = reinterpret_cast<float*>(tiles + (size_t)STAGES * STAGE_BYTES) + (size_t)(warp - 2) * 1024;
+                        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the last chunk has left the buffer
+                        __syncwarp();
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int chunk = i ^ (lane & 7);
+                            *reinterpret_cast<float4*>(stg + lane * 32 + chunk * 4) =
+                                make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]), __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+                        }
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) {
+                            asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+                                         ::"l"(&map_h), "r"(col0), "r"(m0 + quarter * 32), "r"(smem_u32(stg)) : "memory");
+                            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                        }
+                        continue;
+                    }
                     if (!row_ok || col0 >= p.N) continue;
                     if (p.epi == TC_STORE_BF16) {
                         __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + (size_t)row * p.out_stride + col0;
@@ -304,6 +350,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
             }
         }
+        // this warp has read its part of the accumulator: hand it back to the MMA warp
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acce0 + 8 * acc) : "memory");
+        }
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");      // this lane's reduce-adds have landed
     }
     // ------------------------------------------------------------ teardown: everyone arrives, then the tensor memory goes back
     tc_fence_before();
@@ -354,15 +406,41 @@ int tc_launch(const void* A, long long lda, const void* W, TcParams p, int tiles
     if (rc) return rc;
     rc = make_map(&mb, W, p.epi == TC_SWIGLU ? 2 * p.I : p.N, p.K, p.K, b_box_rows);
     if (rc) return rc;
-    const size_t smem = (size_t)TC_STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024;
+    CUtensorMap mh = ma;                                   // a placeholder unless the residual leaves through TMA
+    p.tma_residual = 0;
+    if (p.epi == TC_RESIDUAL && p.N % 4 == 0 && (reinterpret_cast<uintptr_t>(p.h) & 15) == 0) {
+        EncodeTiledFn fn = encode_tiled_fn();
+        cuuint64_t dims[2] = {(cuuint64_t)p.N, (cuuint64_t)p.M};
+        cuuint64_t strides[1] = {(cuuint64_t)p.N * 4};
+        cuuint32_t box[2] = {32, 32};
+        cuuint32_t estr[2] = {1, 1};
+        if (fn && fn(&mh, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, p.h, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
+            p.tma_residual = 1;
+    }
+    constexpr int STAGES = BN <= 64 ? 4 : 3;
+    const size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 4 * 4096 + 128;   // stages, epilogue staging, barriers
     static bool configured = false;
+    static int num_sms = 0;
+    static int per_sm = 1;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+        int occ = 1;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, tc_gemm_kernel<BN>, TC_THREADS, smem) != cudaSuccess || occ < 1) occ = 1;
+        const int by_tmem = 512 / (2 * BN);                // tensor memory: 2 x BN columns per CTA of 512 per SM
+        per_sm = occ < by_tmem ? occ : by_tmem;
+        if (per_sm > 2) per_sm = 2;
         configured = true;
     }
-    dim3 grid(tiles_n, (p.M + TC_BM - 1) / TC_BM);
-    tc_gemm_kernel<BN><<<grid, TC_THREADS, smem, stream>>>(ma, mb, p);
+    p.tiles_n = tiles_n;
+    p.tiles_m = (p.M + TC_BM - 1) / TC_BM;
+    const long long tiles = (long long)p.tiles_m * p.tiles_n;
+    const int grid = (int)(tiles < (long long)num_sms * per_sm ? tiles : (long long)num_sms * per_sm);
+    tc_gemm_kernel<BN><<<grid, TC_THREADS, smem, stream>>>(ma, mb, mh, p);
     return vm_launch_status();
 }
 

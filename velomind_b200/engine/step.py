@@ -165,7 +165,8 @@ class Engine:
     """A model on one GPU with its cache: open/close sequence slots and step batches through the model."""
 
     def __init__(self, model: DecoderModel, max_tokens: int, max_slots: Optional[int] = None,
-                 max_step_tokens: int = 8192, use_graphs: Optional[bool] = None):
+                 max_step_tokens: int = 8192, use_graphs: Optional[bool] = None,
+                 fused_prefill_rows: Optional[int] = None):
         if model.device is None:
             raise RuntimeError("the model has no weights bound; use load_model()")
         self.model = model
@@ -173,6 +174,7 @@ class Engine:
         self.dtype = model.dtype
         self.vocab = model.plan.vocab_size
         self.max_step_tokens = int(max_step_tokens)
+        self.fused_prefill_rows = fused_prefill_rows      # steps with at least this many tokens use the fused tcgen05 kernels
         # pages are whole: round the budget up
         max_tokens = -(-int(max_tokens) // PAGE_TOKENS) * PAGE_TOKENS
         self.cache = SequenceCache(model.cache_needs(), model.cache_shares(), max_tokens, model.plan.max_positions,
@@ -295,6 +297,7 @@ class Engine:
         return d
 
     def _run_eager(self, ctx: StepContext, bucket) -> None:
+        ops.TC_FUSED_MIN_ROWS = self.fused_prefill_rows
         self.ws.begin(bucket)
         try:
             self.model.forward(ctx)
@@ -315,6 +318,7 @@ class Engine:
             if len(self._graphs) >= 256:
                 self._graphs.clear()
             ctx.capturing = True
+            ops.TC_FUSED_MIN_ROWS = self.fused_prefill_rows
             graph = torch.cuda.CUDAGraph()
             torch.cuda.current_stream().synchronize()
             own, lib = ops.launch_count, ops.library_calls
@@ -389,7 +393,7 @@ class Engine:
 
         ctx = StepContext(self, desc, T, B, R, widths)
         ctx.logits = logits[row0: row0 + R]
-        bucket = (desc.caps[0], desc.caps[1], desc.caps[2], ctx.one_token_each)   # decode steps take other scratch
+        bucket = (desc.caps[0], desc.caps[1], desc.caps[2], ctx.one_token_each, self.fused_prefill_rows)   # decode steps take other scratch
         lens = tuple(int(x) for x in np.diff(ctx.host_cu_tokens)) if not ctx.one_token_each else ()
         shape_key = (T, B, R, tuple(widths), ctx.logits.data_ptr(), lens)
         use_graph = self.use_graphs and self.ws.planned(bucket)

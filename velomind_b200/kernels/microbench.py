@@ -16,7 +16,7 @@ import torch
 from . import ops
 
 KERNELS = ["qkv_rope", "out_residual", "gate_up_swiglu", "down_residual", "head", "attn_decode", "attn_prefill",
-           "add_rmsnorm", "sample"]
+           "add_rmsnorm", "sample", "tc_linear", "tc_residual", "tc_swiglu", "cublas_linear"]
 
 
 def _time(fn, repeat: int, graph: bool = True) -> float:
@@ -57,6 +57,8 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, default=64)
     ap.add_argument("--intermediate", type=int, default=1536)
     ap.add_argument("--vocab", type=int, default=49152)
+    ap.add_argument("--n", type=int, default=0, help="tc_*/cublas_linear: output columns (default 2 * intermediate)")
+    ap.add_argument("--k", type=int, default=0, help="tc_*/cublas_linear: inner size (default hidden)")
     ap.add_argument("--splits", type=int, default=0, help="attn_decode: key splits (0: the engine's choice)")
     ap.add_argument("--repeat", type=int, default=50)
     ap.add_argument("--no-graph", action="store_true")
@@ -134,6 +136,23 @@ def main(argv=None) -> int:
         fn = lambda: ops.attention_prefill_bf16(qkv, (H + 2 * Hkv) * D, kp, vp, table, positions, cu, -(-T // 64), out, H, Hkv, D,
                                                 1.0 / math.sqrt(D))
         bytes_read = 0
+    elif a.kernel in ("tc_linear", "tc_residual", "tc_swiglu", "cublas_linear"):
+        T, N, K = a.tokens, a.n or 2 * I, a.k or hid
+        xs = torch.randn(T, K, device=dev).to(bf)
+        ws = [torch.randn(N, K, device=dev).to(bf) for _ in range(8)]
+        outb = torch.empty(T, N, device=dev, dtype=bf)
+        hres = torch.zeros(T, N, device=dev)
+        act = torch.empty(T, N // 2, device=dev, dtype=bf)
+        if a.kernel == "tc_linear":
+            fn = lambda: ops.tc_linear(xs, nxt(ws), outb)
+        elif a.kernel == "tc_residual":
+            fn = lambda: ops.tc_linear(xs, nxt(ws), None, residual=hres)
+        elif a.kernel == "tc_swiglu":
+            fn = lambda: ops.tc_swiglu(xs, nxt(ws), act)
+        else:
+            fn = lambda: torch.mm(xs, nxt(ws).t(), out=outb)
+        bytes_read = 0
+        flops_mm = 2.0 * T * N * K
     elif a.kernel == "add_rmsnorm":
         out = torch.empty(M, hid, device=dev, dtype=bf)
         fn = lambda: ops.add_rmsnorm(h, None, nw, 1e-5, out)
@@ -146,6 +165,9 @@ def main(argv=None) -> int:
     us = _time(fn, a.repeat, graph=not a.no_graph)
     res = {"kernel": a.kernel, "rows": M, "us_per_launch": round(us, 3), "bytes_read": bytes_read,
            "GB_per_s": round(bytes_read / us / 1e3, 1) if bytes_read else None}
+    if a.kernel in ("tc_linear", "tc_residual", "tc_swiglu", "cublas_linear"):
+        res["rows"] = a.tokens
+        res["TFLOP_per_s"] = round(flops_mm / us / 1e6, 1)
     if a.kernel == "attn_prefill":
         flops = 4.0 * D * H * a.tokens * (a.tokens + 1) / 2
         res["TFLOP_per_s"] = round(flops / us / 1e6, 1)

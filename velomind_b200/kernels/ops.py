@@ -273,6 +273,17 @@ def skinny_qkv_rope(x: torch.Tensor, norm, weight: torch.Tensor, q_out: torch.Te
                                         _c_int(H), _c_int(Hkv), _c_int(D), _c_int(n_pages), _ptr(err), _stream()), "skinny_qkv_rope")
 
 
+# Many rows (prefill): the tcgen05 kernels with fused epilogues exist and are tested, but at this model family's
+# small inner sizes (K = 576 .. 1536) the library product plus separate elementwise kernels is still faster
+# (measured: profiles/tc_gemm_vs_cublas.md), so the fused tensor-core path is taken only at or above this many
+# rows.  None: never.  Set by Engine(fused_prefill_rows=...).
+TC_FUSED_MIN_ROWS = None
+
+
+def tc_fused_rows(T: int) -> bool:
+    return TC_FUSED_MIN_ROWS is not None and T >= TC_FUSED_MIN_ROWS
+
+
 def tc_ok(M: int, K: int, weight: torch.Tensor) -> bool:
     """True if the tensor-core (tcgen05 + TMA) products take this shape: bfloat16, rows of 16-byte multiples."""
     return M > 0 and K % 8 == 0 and weight.dtype == torch.bfloat16 and weight.is_contiguous()

@@ -67,7 +67,7 @@ class GroupedQueryAttention(Part):
             return False
         if ctx.T <= ops.SKINNY_MAX_ROWS:
             return self.hidden % 32 == 0 and (self.heads * self.head_dim) % 32 == 0 and self.head_dim % 16 == 0
-        return self.head_dim in (64, 128)
+        return ops.tc_fused_rows(ctx.T) and self.head_dim in (64, 128)
 
     def forward_fused(self, ctx, h: torch.Tensor, norm) -> None:
         """h += attention(norm(h)): three or four launches."""

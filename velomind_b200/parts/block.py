@@ -24,28 +24,38 @@ class PreNormBlock:
 
     def forward(self, ctx, h, pending):
         hid = h.shape[1]
-        # Few tokens (decode): parts that can take the preceding norm into their first kernel and the residual
-        # sum into their last one do so; the step is then bound by the weights it streams, not by launches.
-        fuse_mixer = getattr(self.mixer, "can_fuse", None) is not None and self.mixer.can_fuse(ctx, self.mixer_norm)
-        fuse_ff = getattr(self.feed_forward, "can_fuse", None) is not None and self.feed_forward.can_fuse(ctx, self.feed_forward_norm)
-        if fuse_mixer and fuse_ff:
-            if pending is not None:
-                ops.residual_add(h, pending)
-                ctx.ws.give(pending)
+        # A part that can take the preceding norm into its first kernel and the residual sum into its last one
+        # (`can_fuse` / `forward_fused`) does so; otherwise norm, part and sum are separate steps, the sum being
+        # carried out by the next norm kernel.
+        if getattr(self.mixer, "can_fuse", None) is not None and self.mixer.can_fuse(ctx, self.mixer_norm):
+            self._settle(ctx, h, pending)
             self.mixer.forward_fused(ctx, h, self.mixer_norm)
+            pending = None
+        else:
+            x = ctx.take_tokens(hid, ctx.act_dtype)
+            self.mixer_norm.forward(ctx, h, pending, x)
+            ctx.ws.give(pending)
+            pending = ctx.take_tokens(hid, ctx.act_dtype)
+            self.mixer.forward(ctx, x, pending)
+            ctx.ws.give(x)
+        if getattr(self.feed_forward, "can_fuse", None) is not None and self.feed_forward.can_fuse(ctx, self.feed_forward_norm):
+            self._settle(ctx, h, pending)
             self.feed_forward.forward_fused(ctx, h, self.feed_forward_norm)
             return None
         x = ctx.take_tokens(hid, ctx.act_dtype)
-        self.mixer_norm.forward(ctx, h, pending, x)
+        self.feed_forward_norm.forward(ctx, h, pending, x)
         ctx.ws.give(pending)
-        mixed = ctx.take_tokens(hid, ctx.act_dtype)
-        self.mixer.forward(ctx, x, mixed)
-        self.feed_forward_norm.forward(ctx, h, mixed, x)
-        ctx.ws.give(mixed)
         out = ctx.take_tokens(hid, ctx.act_dtype)
         self.feed_forward.forward(ctx, x, out)
         ctx.ws.give(x)
         return out
+
+    @staticmethod
+    def _settle(ctx, h, pending) -> None:
+        """Add a delta that is still pending to the residual stream."""
+        if pending is not None:
+            ops.residual_add(h, pending)
+            ctx.ws.give(pending)
 
 
 register_part("arrangement", "prenorm", PreNormBlock)

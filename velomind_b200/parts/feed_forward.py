@@ -38,7 +38,7 @@ class SwiGLU(Part):
             return False
         if ctx.T <= ops.SKINNY_MAX_ROWS:
             return self.hidden % 32 == 0 and self.intermediate % 32 == 0
-        return self.hidden % 8 == 0 and self.intermediate % 64 == 0
+        return ops.tc_fused_rows(ctx.T) and self.hidden % 8 == 0 and self.intermediate % 64 == 0
 
     def forward_fused(self, ctx, h: torch.Tensor, norm) -> None:
         """h += down(silu(gate(norm(h))) * up(norm(h))): two or three launches."""
