@@ -60,6 +60,7 @@ def main(argv=None) -> int:
     ap.add_argument("--n", type=int, default=0, help="tc_*/cublas_linear: output columns (default 2 * intermediate)")
     ap.add_argument("--k", type=int, default=0, help="tc_*/cublas_linear: inner size (default hidden)")
     ap.add_argument("--splits", type=int, default=0, help="attn_decode: key splits (0: the engine's choice)")
+    ap.add_argument("--groups", type=int, default=4, help="attn_prefill: warp groups sharing a tile's key blocks")
     ap.add_argument("--repeat", type=int, default=50)
     ap.add_argument("--no-graph", action="store_true")
     a = ap.parse_args(argv)
@@ -134,7 +135,7 @@ def main(argv=None) -> int:
         cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
         out = torch.empty(T, H * D, device=dev, dtype=bf)
         fn = lambda: ops.attention_prefill_bf16(qkv, (H + 2 * Hkv) * D, kp, vp, table, positions, cu, -(-T // 64), out, H, Hkv, D,
-                                                1.0 / math.sqrt(D))
+                                                1.0 / math.sqrt(D), groups=a.groups)
         bytes_read = 0
     elif a.kernel in ("tc_linear", "tc_residual", "tc_swiglu", "cublas_linear"):
         T, N, K = a.tokens, a.n or 2 * I, a.k or hid

@@ -134,14 +134,15 @@ def attention_generic(q: torch.Tensor, q_row_stride: int, k_pages: torch.Tensor,
 def attention_prefill_bf16(q: torch.Tensor, q_row_stride: int, k_pages: torch.Tensor, v_pages: torch.Tensor,
                            block_table: torch.Tensor, positions: torch.Tensor, cu_tokens: torch.Tensor, n_tiles: int,
                            out: torch.Tensor, H: int, Hkv: int, D: int, scale: float, window: int = 0,
-                           err: Optional[torch.Tensor] = None) -> None:
+                           err: Optional[torch.Tensor] = None, groups: int = 1) -> None:
     """Tensor-core attention of the step's new tokens over the cache (bfloat16, D in 16..128 step 16).
-    cu_tokens int32 [B+1]: token offsets of the sequences; n_tiles = sum of ceil(new tokens / 64)."""
+    cu_tokens int32 [B+1]: token offsets of the sequences; n_tiles = sum of ceil(new tokens / 64);
+    groups (1, 2, 4): warp groups sharing a tile's key blocks (for tiles that see many keys)."""
     B = cu_tokens.shape[0] - 1
     _check(library().vm_attention_prefill_bf16(_ptr(q), _c_int(q_row_stride), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
                                                _c_int(block_table.shape[1]), _ptr(positions), _ptr(cu_tokens), _c_int(B),
                                                _c_int(n_tiles), _ptr(out), _c_int(H), _c_int(Hkv), _c_int(D), _c_f(scale),
-                                               _c_int(window), _c_int(k_pages.shape[0]), _ptr(err), _stream()),
+                                               _c_int(window), _c_int(k_pages.shape[0]), _ptr(err), _c_int(groups), _stream()),
            "attention_prefill_bf16")
 
 
@@ -198,8 +199,11 @@ def attention(ctx, q: torch.Tensor, q_row_stride: int, k_pages: torch.Tensor, v_
     elif fast:      # the tile count follows from the sequences' new-token counts, which are part of a recorded step's shape
         lens = ctx.host_cu_tokens[1:] - ctx.host_cu_tokens[:-1]
         n_tiles = int(((lens + 63) // 64).sum())
+        # the longest chain of key blocks a tile walks, and how many CTAs there are to hide it behind
+        most_blocks = (min(ctx.max_ctx_len, window + 64) if window > 0 else ctx.max_ctx_len) // 64 + 1
+        groups = 2 if most_blocks >= 8 else 1      # measured at 9 heads of 64: 2 groups 39 us, 1 group 43 us, 4 groups 46 us (2,048 tokens)
         attention_prefill_bf16(q, q_row_stride, k_pages, v_pages, block_table, ctx.positions, ctx.cu_tokens, n_tiles, out,
-                               H, Hkv, D, scale, window, ctx.err)
+                               H, Hkv, D, scale, window, ctx.err, groups)
     else:
         attention_generic(q, q_row_stride, k_pages, v_pages, block_table, ctx.positions, ctx.seq_of_token, out,
                           H, Hkv, D, scale, window, ctx.err)
