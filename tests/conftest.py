@@ -23,10 +23,11 @@ def emulated(monkeypatch):
 @pytest.fixture(scope="session")
 def model_folders(tmp_path_factory):
     """Tiny random models A and B, written once per test session into a temporary folder."""
-    from tiny_configs import TINY_A, TINY_A_INIT, TINY_B, TINY_B_INIT
+    from tiny_configs import TINY_A, TINY_A_INIT, TINY_B, TINY_B_INIT, TINY_C, TINY_C_INIT
     from velomind_b200 import write_random_model
     root = tmp_path_factory.mktemp("models")
     return {
         "tiny_a": write_random_model(str(root / "tiny_a"), TINY_A, **TINY_A_INIT),
         "tiny_b": write_random_model(str(root / "tiny_b"), TINY_B, **TINY_B_INIT),
+        "tiny_c": write_random_model(str(root / "tiny_c"), TINY_C, **TINY_C_INIT),
     }

@@ -6,15 +6,16 @@ import torch
 
 import plain_llama as P
 import schedules as S
-from tiny_configs import TINY_A, TINY_B
+from tiny_configs import TINY_A, TINY_B, TINY_C
 
 pytestmark = pytest.mark.gpu
 
 # float32: the reference's own bound between its cached and stateless paths is 1e-4 on the CPU and 1e-3 on
 # CUDA (tests/test_smollm2_e2e.cpp:306,338; tests/test_interactive.cpp:337,354); logits here are ~1.
-TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+# bfloat16: relative to the largest logit of the run (bf16 keeps 8 bits; measured about 1 % after two or three layers).
+TOL = {"float32": 2e-5, "bfloat16": 2e-2}
 LENGTHS = (5, 9, 2, 70, 130, 64, 65, 200, 33, 1)
-CONFIGS = {"tiny_a": TINY_A, "tiny_b": TINY_B}
+CONFIGS = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C}
 
 
 def _engine(folder, dtype, max_tokens=2048, **kw):
@@ -26,16 +27,17 @@ def _engine(folder, dtype, max_tokens=2048, **kw):
 def _compare(got, want, tol):
     assert set(got) == set(want)
     worst = 0.0
+    scale = max(1.0, max(float(np.abs(v).max()) for v in want.values()))
     for step in want:
         assert got[step].shape == want[step].shape, step
         assert np.isfinite(got[step]).all(), step
         worst = max(worst, float(np.abs(got[step] - want[step]).max()))
-    assert worst <= tol, f"max |logit - plain| = {worst:.3e} > {tol}"
+    assert worst <= tol * scale, f"max |logit - plain| = {worst:.3e} > {tol} x {scale:.2f}"
     return worst
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c"])
 @pytest.mark.parametrize("cut", ["whole", "tail", "batches"])
 def test_cuts_match_plain(model_folders, name, dtype, cut):
     folder = model_folders[name]
@@ -139,7 +141,7 @@ def test_stop_token_ends_a_sequence_early(model_folders):
     assert eng.engine.cache.slots.held_count == 0
 
 
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c"])
 def test_fused_tensor_core_prefill_matches_plain(model_folders, name):
     """bfloat16 with the tcgen05 kernels (fused epilogues) switched on for every step of more than 16 tokens.
     The tiny head sizes (16, 32) are refused by the fused qkv kernel, so the attention part falls back while the

@@ -11,7 +11,7 @@ from tiny_configs import TINY_A, TINY_B
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+TOL = {"float32": 2e-5, "bfloat16": 2e-2}     # times the largest logit (at least 1)
 
 
 def _replay(folder, dtype, steps, out, max_tokens):
@@ -42,9 +42,10 @@ def test_replay_three_cuts(model_folders, tmp_path, name, cfg, dtype):
     out = str(tmp_path / "out")
     _replay(folder, dtype, steps, out, max_tokens=64 * 8)
     want = S.expected_rows(steps, all_requests, all_plain)
+    scale = max(1.0, max(float(np.abs(v).max()) for v in want.values()))
     for step, rows in want.items():
         got = np.fromfile(os.path.join(out, f"{step}.f32"), dtype="<f4").reshape(-1, cfg["vocab_size"])
         assert got.shape == rows.shape, (step, owner[step])
         err = float(np.abs(got - rows).max())
-        assert err <= TOL[dtype], f"step {step} of cut {owner[step]!r}: max |logit - plain| = {err:.3e}"
+        assert err <= TOL[dtype] * scale, f"step {step} of cut {owner[step]!r}: max |logit - plain| = {err:.3e}"
     assert sorted(int(f[:-4]) for f in os.listdir(out)) == sorted(want)
