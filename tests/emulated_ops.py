@@ -110,12 +110,23 @@ def sample(logits, temperature, top_p, seed, stream_id, step, out):
         out[r] = P.sample_top_p(logits[r].numpy(), float(temperature[r]), float(top_p[r]), u)
 
 
+def decode_advance(sampled, tokens, positions, ctx_len, draw_step, history, iteration):
+    B = sampled.shape[0]
+    it = int(iteration[0])
+    tokens[:B] = sampled.clamp(min=0)
+    positions += 1
+    ctx_len += 1
+    draw_step += 1
+    history[it * B:(it + 1) * B] = sampled
+    iteration += 1
+
+
 def require_cuda(device):
     return torch.device("cpu")
 
 
 NAMES = ["embed_gather", "add_rmsnorm", "residual_add", "swiglu", "convert", "rope_kv_write", "attention_generic",
-         "attention", "linear", "sample", "require_cuda"]
+         "attention", "linear", "sample", "decode_advance", "require_cuda"]
 
 
 def install(monkeypatch):
@@ -137,5 +148,6 @@ def install(monkeypatch):
     monkeypatch.setattr(step, "GRAPHS_DEFAULT", False)
     monkeypatch.setattr(step, "_host_buffer", lambda n, dtype: torch.empty(n, dtype=dtype))
     monkeypatch.setattr(step, "_new_event", lambda: _Event())
+    monkeypatch.setattr(step, "_sync_stream", lambda: None)
     monkeypatch.setattr(sampler, "_host_buffer", lambda shape, dtype: torch.empty(shape, dtype=dtype))
     monkeypatch.setattr(sampler, "_sync", lambda: None)

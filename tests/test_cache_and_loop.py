@@ -285,3 +285,35 @@ def test_generation_with_stand_in_kernels_matches_plain(emulated, model_folders)
     assert np.abs(te.forward_full_logits(prompts[0]).numpy() - ref).max() < 5e-6
     te.reset_session()
     assert te.session_length == 0 and te.engine.cache.slots.held_count == 0
+
+
+class FakeRunStepper(FakeStepper):
+    """FakeStepper that can also queue several decode steps (next token = last + 1, like its logits say)."""
+    MAX_DECODE_RUN = 5
+
+    def __init__(self, *a, **kw):
+        super().__init__(*a, **kw)
+        self.runs = []
+
+    def decode_many(self, slots, last_tokens, params, streams, draw_steps, k):
+        assert all(s in self.open_slots for s in slots) and 1 <= k <= self.MAX_DECODE_RUN
+        self.runs.append((list(slots), list(last_tokens), list(draw_steps), k))
+        return np.array([[(t + 1 + j) % self.vocab for t in last_tokens] for j in range(k)], dtype=np.int32)
+
+
+def test_loop_with_queued_decode_runs_gives_the_same_tokens():
+    reqs = [Request([1, 2, 3], SamplingParams(0.0, 0.9, 9)), Request([10], SamplingParams(0.0, 0.9, 12)),
+            Request([40, 41], SamplingParams(0.0, 0.9, 2))]
+    base = GenerationLoop(FakeStepper(), GreedyHostSampler(), 100, 4, default_stop=(15,)).run(reqs)
+    st = FakeRunStepper()
+    loop = GenerationLoop(st, GreedyHostSampler(), 100, 4, default_stop=(15,), steps_per_sync=8)
+    got = loop.run(reqs)
+    assert [r.tokens for r in got] == [r.tokens for r in base] and [r.finish_reason for r in got] == [r.finish_reason for r in base]
+    assert got[1].tokens == [11, 12, 13, 14, 15] and got[1].finish_reason == "stop"     # ended inside a run; the rest is dropped
+    # request 2 may take only one more token after the prompts' step, so that step is a single one; then a run of the
+    # stepper's cap (5), inside which request 1 stops; then what request 0's budget leaves (2)
+    assert [k for *_, k in st.runs] == [5, 2]
+    assert st.runs[0][0] == [0, 1] and st.runs[0][2] == [2, 2]      # slots and draw counters of the first run
+    assert st.runs[1][0] == [0] and st.runs[1][1] == [10] and st.runs[1][2] == [7]
+    assert not st.open_slots
+    assert loop.timing.generated_tokens == sum(len(r.tokens) for r in got)

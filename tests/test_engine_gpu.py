@@ -153,3 +153,24 @@ def test_fused_tensor_core_prefill_matches_plain(model_folders, name):
     engine = _engine(folder, "bfloat16", max_tokens=64 * 16, fused_prefill_rows=17)
     got = S.run_steps_in_process(engine, steps)
     _compare(got, S.expected_rows(steps, requests, plain), TOL["bfloat16"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_queued_decode_runs_equal_single_steps(model_folders, dtype):
+    """Decode steps queued on the GPU with the tokens fed back there give the same tokens as one step at a time:
+    greedy and sampled, sequences of unequal lengths crossing page boundaries, one of them stopping inside a run."""
+    import velomind_b200 as vm
+    folder = model_folders["tiny_c"]
+    prompts = [list(range(1, 60)), [7, 8, 9], list(range(100, 230)), [5]]
+    eng = vm.load(folder, dtype=dtype, max_tokens=4096)
+    for temperature, top_p in ((0.0, 1.0), (0.9, 0.95)):
+        one = eng.generate(prompts, temperature=temperature, top_p=top_p, max_tokens=40, seed=11, stop_tokens=(), steps_per_sync=1)
+        stop = one[1].tokens[9]
+        ref = eng.generate(prompts, temperature=temperature, top_p=top_p, max_tokens=40, seed=11, stop_tokens=(stop,), steps_per_sync=1)
+        for k in (8, 64):
+            got = eng.generate(prompts, temperature=temperature, top_p=top_p, max_tokens=40, seed=11, stop_tokens=(stop,), steps_per_sync=k)
+            assert [r.tokens for r in got] == [r.tokens for r in ref]
+            assert [r.finish_reason for r in got] == [r.finish_reason for r in ref]
+        assert any(r.finish_reason == "stop" for r in ref)
+    assert eng.engine.cache.slots.held_count == 0 and eng.engine.cache.tokens_held() == 0
+    eng.engine.cache.check()

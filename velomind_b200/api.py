@@ -111,14 +111,15 @@ class TextEngine:
 
     def generate(self, prompts: Sequence[Union[str, Sequence[int]]], temperature: float = 0.7, top_p: float = 0.9,
                  max_tokens: int = 32, seed: int = 42, stop_tokens: Optional[Sequence[int]] = None,
-                 on_token: Optional[Callable[[int, int, str], None]] = None) -> List[Result]:
+                 on_token: Optional[Callable[[int, int, str], None]] = None, steps_per_sync: int = 8) -> List[Result]:
         """Generate for a batch of prompts (token id lists, or text if a tokenizer is loaded).
-        `on_token(index, token, piece)` is called for every new token; `piece` is its text (or "[id]")."""
+        `on_token(index, token, piece)` is called for every new token; `piece` is its text (or "[id]").
+        `steps_per_sync`: decode steps queued on the GPU before the host reads their tokens (1: every step)."""
         engine = self._need()
         stops = tuple(stop_tokens) if stop_tokens is not None else self.default_stop_tokens()
         requests = [Request(self.encode(p), SamplingParams(temperature, top_p, max_tokens, seed, stops), stream=i)
                     for i, p in enumerate(prompts)]
-        loop = GenerationLoop(engine, self.sampler, engine.cache.n_pages, self.config.max_batch, stops)
+        loop = GenerationLoop(engine, self.sampler, engine.cache.n_pages, self.config.max_batch, stops, steps_per_sync)
         streamers = [TextStreamer(self.tokenizer) for _ in requests]
         callback = None
         if on_token is not None:

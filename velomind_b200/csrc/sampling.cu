@@ -185,3 +185,36 @@ VM_API int vm_sample(const float* logits, long long row_stride, int R, int V, co
     sample_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(logits, row_stride, V, temperature, top_p, seed, stream_id, step, out);
     return vm_launch_status();
 }
+
+// ---------------------------------------------------------------- feeding sampled tokens back on the device
+// After a decode step has been sampled: the sampled token becomes the next step's input, every sequence moves one
+// place on, the draw counters advance, and the token is kept in `history[iteration, :]` for the host to read later.
+// With this the host can queue several decode steps without waiting for the tokens of each.
+__global__ void decode_advance_kernel(const int* __restrict__ sampled, int* __restrict__ tokens, int* __restrict__ positions,
+                                      int* __restrict__ ctx_len, long long* __restrict__ draw_step, int* __restrict__ history,
+                                      int* __restrict__ iteration, int B) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    const int it = *iteration;
+    if (b < B) {
+        const int tok = sampled[b];
+        tokens[b] = tok < 0 ? 0 : tok;          // a row without a valid choice keeps the step well-formed; the host sees -1
+        positions[b] += 1;
+        ctx_len[b] += 1;
+        draw_step[b] += 1;
+        history[(size_t)it * B + b] = tok;
+    }
+    __syncthreads();
+    if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) {
+        // every block reads `iteration` before this block (the last one to start in practice) bumps it; with one block
+        // (B <= 1024) the barrier above makes that exact
+        *iteration = it + 1;
+    }
+}
+
+VM_API int vm_decode_advance(const int* sampled, int* tokens, int* positions, int* ctx_len, long long* draw_step,
+                             int* history, int* iteration, int B, cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (B > 1024) return VM_ERR_UNSUPPORTED;     // one block, so that the iteration counter is read by all before it moves
+    decode_advance_kernel<<<1, ((B + 31) / 32) * 32, 0, stream>>>(sampled, tokens, positions, ctx_len, draw_step, history, iteration, B);
+    return vm_launch_status();
+}

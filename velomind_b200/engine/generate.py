@@ -80,9 +80,14 @@ class GenerationLoop:
     """Runs requests through a stepper (`open`, `close`, `step`) with a sampler
     (`sample(logits, params, streams, steps) -> token per row`)."""
 
-    def __init__(self, stepper, sampler, total_pages: int, max_batch: int, default_stop: Sequence[int] = ()):
+    def __init__(self, stepper, sampler, total_pages: int, max_batch: int, default_stop: Sequence[int] = (),
+                 steps_per_sync: int = 1):
         self.stepper = stepper
         self.sampler = sampler
+        # > 1: decode steps are queued in runs of up to this many, their tokens fed back on the device, and the host
+        # looks at the tokens once per run (the stepper needs `decode_many`); a sequence that ends inside a run costs
+        # the run's remaining steps for that sequence, nothing else
+        self.steps_per_sync = max(1, int(steps_per_sync))
         self.total_pages = int(total_pages)
         self.max_batch = int(max_batch)
         self.default_stop = tuple(default_stop)
@@ -97,6 +102,15 @@ class GenerationLoop:
         for batch in plan_batches(requests, self.total_pages, self.max_batch):
             self._run_batch(requests, batch, results, on_token)
         return results
+
+    def _run_length(self, requests, results, live, step_no) -> int:
+        """How many decode steps to queue before looking at the tokens: 1 for the prompts' step, for steppers without
+        `decode_many`, and when steps_per_sync is 1; never beyond what the sequence closest to its budget may still take."""
+        if step_no == 0 or self.steps_per_sync <= 1 or not hasattr(self.stepper, "decode_many"):
+            return 1
+        room = min(requests[i].params.max_tokens - len(results[i].tokens) for i, _ in live)
+        limit = getattr(self.stepper, "MAX_DECODE_RUN", self.steps_per_sync)
+        return max(1, min(self.steps_per_sync, room, limit))
 
     def _run_batch(self, requests, batch, results, on_token) -> None:
         stepper = self.stepper
@@ -115,41 +129,55 @@ class GenerationLoop:
             feed = {i: list(requests[i].prompt) for i, _ in live}
             step_no = 0
             while live:
-                entries = [Entry(slot, feed[i], [len(feed[i]) - 1]) for i, slot in live]
-                logits = stepper.step(entries)
-                tokens = self.sampler.sample(
-                    logits, [requests[i].params for i, _ in live],
-                    [requests[i].stream for i, _ in live],
-                    [len(results[i].tokens) for i, _ in live])
+                run = self._run_length(requests, results, live, step_no)
+                if run > 1:
+                    rows = stepper.decode_many(
+                        [slot for _, slot in live], [feed[i][0] for i, _ in live], [requests[i].params for i, _ in live],
+                        [requests[i].stream for i, _ in live], [len(results[i].tokens) for i, _ in live], run)
+                else:
+                    entries = [Entry(slot, feed[i], [len(feed[i]) - 1]) for i, slot in live]
+                    logits = stepper.step(entries)
+                    rows = [self.sampler.sample(
+                        logits, [requests[i].params for i, _ in live],
+                        [requests[i].stream for i, _ in live],
+                        [len(results[i].tokens) for i, _ in live])]
                 now = time.perf_counter()
                 if step_no == 0:
                     self.timing.prefill_seconds += now - t0
                 else:
                     self.timing.decode_seconds += now - t0
-                    self.timing.decode_steps += 1
+                    self.timing.decode_steps += len(rows)
                 t0 = now
+                ended = set()
+                for tokens in rows:                      # one row of tokens per step of the run
+                    for (i, slot), tok in zip(live, tokens):
+                        if i in ended:
+                            continue                     # the sequence ended earlier in this run: the rest is not its output
+                        tok = int(tok)
+                        res, par = results[i], requests[i].params
+                        res.tokens.append(tok)
+                        self.timing.generated_tokens += 1
+                        if on_token is not None:
+                            on_token(i, tok)
+                        stops = par.stop_tokens if par.stop_tokens else self.default_stop
+                        if tok in stops:
+                            res.finish_reason = "stop"
+                        elif len(res.tokens) >= par.max_tokens:
+                            res.finish_reason = "length"
+                        elif tok < 0:
+                            res.finish_reason = "error"
+                        if res.finish_reason:
+                            ended.add(i)
+                        else:
+                            feed[i] = [tok]
                 still = []
-                for (i, slot), tok in zip(live, tokens):
-                    tok = int(tok)
-                    res, par = results[i], requests[i].params
-                    res.tokens.append(tok)
-                    self.timing.generated_tokens += 1
-                    if on_token is not None:
-                        on_token(i, tok)
-                    stops = par.stop_tokens if par.stop_tokens else self.default_stop
-                    if tok in stops:
-                        res.finish_reason = "stop"
-                    elif len(res.tokens) >= par.max_tokens:
-                        res.finish_reason = "length"
-                    elif tok < 0:
-                        res.finish_reason = "error"
-                    if res.finish_reason:
-                        stepper.close(slot)          # the slot and its pages are free for the next batch at once
+                for (i, slot) in live:
+                    if i in ended:
+                        stepper.close(slot)              # the slot and its pages are free for the next batch at once
                     else:
-                        feed[i] = [tok]
                         still.append((i, slot))
                 live = still
-                step_no += 1
+                step_no += len(rows)
         except Exception:
             for _, slot in live:
                 try:

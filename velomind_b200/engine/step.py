@@ -55,6 +55,10 @@ def _new_event():
     return torch.cuda.Event()
 
 
+def _sync_stream() -> None:
+    torch.cuda.current_stream().synchronize()
+
+
 class Descriptors:
     """The integers that describe one step, laid out in one pinned host buffer and one device buffer of
     the same layout, so that a step costs one host-to-device copy."""
@@ -187,6 +191,7 @@ class Engine:
         self.use_graphs = (GRAPHS_DEFAULT if use_graphs is None else bool(use_graphs)) and model.graph_safe
         self.graphs_captured = 0
         self._shape_seen: Dict[Tuple, int] = {}
+        self._run_state = None
         self.steps_run = 0
 
     # ---- slots
@@ -228,6 +233,104 @@ class Engine:
         self.steps_run += 1
         return logits[:n_rows]
 
+    # ---- several decode steps without the host in between
+    MAX_DECODE_RUN = 64
+
+    def decode_many(self, slots: Sequence[int], last_tokens: Sequence[int], params, streams: Sequence[int],
+                    draw_steps: Sequence[int], k: int) -> np.ndarray:
+        """Feed `last_tokens` (one per slot) and decode `k` tokens for every slot: each step's sampled tokens are
+        fed back ON THE DEVICE (no host round trip between steps).  `params[i]` are SamplingParams, `streams[i]`
+        and `draw_steps[i]` the Philox stream and counter of sequence i's next draw.  Returns int32 [k, B]: the
+        tokens sampled after each step.  The host decides afterwards where a sequence really ended; every slot's
+        length has grown by k."""
+        B = len(slots)
+        k = int(k)
+        if k < 1 or k > self.MAX_DECODE_RUN:
+            raise ValueError(f"decode_many: k must be in 1..{self.MAX_DECODE_RUN}")
+        entries = [Entry(s, [int(t)], [0]) for s, t in zip(slots, last_tokens)]
+        self._validate(entries, extra=k - 1)
+        st = self._decode_state(B)
+        desc, T, _, R, widths, new_len, _ = self._describe(entries, [(i, 0, 1) for i in range(B)], reserve_extra=k - 1)
+        hf, hi = st["host_f"].numpy(), st["host_i"].numpy()
+        for r, p in enumerate(params):
+            hf[0, r], hf[1, r] = p.temperature, p.top_p
+            hi[0, r], hi[1, r], hi[2, r] = p.seed, streams[r], draw_steps[r]
+        st["dev_f"].copy_(st["host_f"], non_blocking=True)
+        st["dev_i"].copy_(st["host_i"], non_blocking=True)
+        st["iteration"].zero_()
+        ctx = StepContext(self, desc, T, B, R, widths)
+        logits = self._logits_buffer(B)
+        ctx.logits = logits[:B]
+        bucket = (desc.caps[0], desc.caps[1], desc.caps[2], True, self.fused_prefill_rows)
+
+        def one_step():
+            self.model.forward(ctx)
+            ops.sample(ctx.logits, st["dev_f"][0, :B], st["dev_f"][1, :B], st["dev_i"][0, :B], st["dev_i"][1, :B],
+                       st["dev_i"][2, :B], st["sampled"][:B])
+            ops.decode_advance(st["sampled"][:B], ctx.tokens, ctx.positions, ctx.ctx_len, st["dev_i"][2, :B],
+                               st["history"], st["iteration"])
+
+        if self.use_graphs and self.ws.planned(bucket):
+            key = ("run", bucket, (B, tuple(widths), logits.data_ptr(), st["sampled"].data_ptr()), self.ws.generation)
+            graph = self._graphs.get(key)
+            if graph is None:
+                ctx.capturing = True
+                ops.TC_FUSED_MIN_ROWS = self.fused_prefill_rows
+                graph = torch.cuda.CUDAGraph()
+                torch.cuda.current_stream().synchronize()
+                own, lib = ops.launch_count, ops.library_calls
+                self.ws.begin(bucket)
+                try:
+                    with torch.cuda.graph(graph):
+                        one_step()
+                except Exception:
+                    self.ws.abort()
+                    raise
+                self.ws.end()
+                graph.launches = (ops.launch_count - own, ops.library_calls - lib)
+                ops.launch_count, ops.library_calls = own, lib
+                self._graphs[key] = graph
+                self.graphs_captured += 1
+            for _ in range(k):
+                graph.replay()
+            ops.launch_count += k * graph.launches[0]
+            ops.library_calls += k * graph.launches[1]
+        else:
+            for _ in range(k):
+                ops.TC_FUSED_MIN_ROWS = self.fused_prefill_rows
+                self.ws.begin(bucket)
+                try:
+                    one_step()
+                except Exception:
+                    self.ws.abort()
+                    raise
+                self.ws.end()
+        st["history_host"][: k * B].copy_(st["history"][: k * B], non_blocking=True)
+        _sync_stream()
+        for i, e in enumerate(entries):
+            self.cache.commit(e.slot, new_len[i] + k - 1)
+        self.steps_run += k
+        return st["history_host"].numpy()[: k * B].reshape(k, B).copy()
+
+    def _decode_state(self, B: int):
+        """Device buffers of the sampler and of the token feedback, sized for a batch of at least B."""
+        st = self._run_state
+        if st is None or st["cap"] < B:
+            cap = _bucket(B, floor=8)
+            st = {
+                "cap": cap,
+                "host_f": _host_buffer(2 * cap, torch.float32).view(2, cap),
+                "host_i": _host_buffer(3 * cap, torch.int64).view(3, cap),
+                "dev_f": torch.empty((2, cap), dtype=torch.float32, device=self.device),
+                "dev_i": torch.empty((3, cap), dtype=torch.int64, device=self.device),
+                "sampled": torch.empty(cap, dtype=torch.int32, device=self.device),
+                "history": torch.empty(self.MAX_DECODE_RUN * cap, dtype=torch.int32, device=self.device),
+                "history_host": _host_buffer(self.MAX_DECODE_RUN * cap, torch.int32),
+                "iteration": torch.zeros(1, dtype=torch.int32, device=self.device),
+            }
+            self._run_state = st
+        return st
+
     def raise_if_error(self) -> None:
         """Synchronise and raise if a kernel reported a fault of the step's descriptors (no page, bad id)."""
         code = int(self.err.item())
@@ -238,7 +341,7 @@ class Engine:
             raise CacheError(f"a kernel reported {what}")
 
     # ---- internals
-    def _validate(self, entries: Sequence[Entry]) -> None:
+    def _validate(self, entries: Sequence[Entry], extra: int = 0) -> None:
         seen = set()
         need: Dict[int, int] = {}
         for e in entries:
@@ -257,7 +360,7 @@ class Engine:
             for w in e.want:
                 if not 0 <= int(w) < n:
                     raise ValueError(f"slot {e.slot}: wanted place {int(w)} outside the {n} tokens of this step")
-            new_len = self.cache.length[e.slot] + n
+            new_len = self.cache.length[e.slot] + n + extra
             if new_len > self.cache.max_positions:
                 raise CacheError(f"slot {e.slot} would reach {new_len} tokens; the model's limit is {self.cache.max_positions}")
             need[e.slot] = new_len
@@ -339,15 +442,17 @@ class Engine:
         ops.launch_count += graph.launches[0]
         ops.library_calls += graph.launches[1]
 
-    def _run_chunk(self, entries, chunk, logits, row0, produced) -> int:
+    def _describe(self, entries, chunk, reserve_extra: int = 0):
+        """Reserve cache room for a chunk of a step and write its descriptors; returns (desc, T, B, R, widths,
+        new lengths, wanted (entry, place) pairs).  `reserve_extra` tokens of room are reserved beyond the chunk's
+        own (decode runs that queue several steps)."""
         cache = self.cache
         B = len(chunk)
         T = sum(b - a for _, a, b in chunk)
-        rows: List[int] = []
         new_len: List[int] = []
         for (i, a, b) in chunk:
             e = entries[i]
-            cache.reserve(e.slot, cache.length[e.slot] + (b - a))
+            cache.reserve(e.slot, cache.length[e.slot] + (b - a) + reserve_extra)
         # widths of the block tables of this batch, per group (power of two, at most the table's width)
         widths = []
         for g in cache.groups:
@@ -390,6 +495,11 @@ class Engine:
             for s, (i, _, _) in enumerate(chunk):
                 tab[s, :] = group.block_table[entries[i].slot, :w]
         desc.upload()
+        return desc, T, B, R, widths, new_len, wanted_here
+
+    def _run_chunk(self, entries, chunk, logits, row0, produced) -> int:
+        cache = self.cache
+        desc, T, B, R, widths, new_len, wanted_here = self._describe(entries, chunk)
 
         ctx = StepContext(self, desc, T, B, R, widths)
         ctx.logits = logits[row0: row0 + R]

@@ -337,6 +337,15 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor,
                                _ptr(seed), _ptr(stream_id), _ptr(step), _ptr(out), _stream()), "sample")
 
 
+def decode_advance(sampled: torch.Tensor, tokens: torch.Tensor, positions: torch.Tensor, ctx_len: torch.Tensor,
+                   draw_step: torch.Tensor, history: torch.Tensor, iteration: torch.Tensor) -> None:
+    """After sampling a decode step: tokens <- sampled, positions/ctx_len/draw_step += 1, history[iteration] <- sampled,
+    iteration += 1 (all on the device, so that several steps can be queued without the host)."""
+    B = sampled.shape[0]
+    _check(library().vm_decode_advance(_ptr(sampled), _ptr(tokens), _ptr(positions), _ptr(ctx_len), _ptr(draw_step),
+                                       _ptr(history), _ptr(iteration), _c_int(B), _stream()), "decode_advance")
+
+
 def require_cuda(device) -> torch.device:
     """The device an engine may run on, or a loud refusal."""
     dev = torch.device(device)
