@@ -174,3 +174,37 @@ def test_queued_decode_runs_equal_single_steps(model_folders, dtype):
         assert any(r.finish_reason == "stop" for r in ref)
     assert eng.engine.cache.slots.held_count == 0 and eng.engine.cache.tokens_held() == 0
     eng.engine.cache.check()
+
+
+@pytest.fixture(scope="module")
+def wide_folder(tmp_path_factory):
+    """SmolLM2-135M's layer sizes (hidden 576, 9/3 heads of 64, intermediate 1536, vocabulary 49152, tied) with
+    four layers: the kernels run at the sizes the benchmark runs them at."""
+    import velomind_b200 as vm
+    cfg = dict(vm.SMOLLM2_135M, num_hidden_layers=4)
+    return vm.write_random_model(str(tmp_path_factory.mktemp("wide") / "m"), cfg, seed=5, std=0.03, norm_jitter=0.2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_production_widths_match_plain(wide_folder, dtype):
+    requests = S.make_requests(49152, (300, 40, 129), seed=8)
+    plain = S.plain_logits(wide_folder, requests)
+    engine = _engine(wide_folder, dtype, max_tokens=64 * 16, max_step_tokens=256)     # the 300-token prompt is cut in two
+    for cut in (S.steps_whole(requests), S.steps_tail_one_by_one(requests, tail=20), S.steps_unequal_batches(requests)):
+        got = S.run_steps_in_process(engine, cut)
+        _compare(got, S.expected_rows(cut, requests, plain), TOL[dtype])
+    if dtype == "bfloat16":
+        fused = _engine(wide_folder, dtype, max_tokens=64 * 16, fused_prefill_rows=17)
+        cut = S.steps_unequal_batches(requests)
+        _compare(S.run_steps_in_process(fused, cut), S.expected_rows(cut, requests, plain), TOL[dtype])
+
+
+def test_float32_cuts_agree_bit_for_bit_in_attention_order(wide_folder):
+    """float32: whole, one-by-one and batched runs of the same request differ only by the library product's
+    rounding (the attention kernel's reduction order does not depend on the cut)."""
+    requests = S.make_requests(49152, (150,), seed=9)
+    engine = _engine(wide_folder, "float32", max_tokens=64 * 8)
+    a = S.run_steps_in_process(engine, S.steps_whole(requests))[0]
+    tail = S.run_steps_in_process(engine, S.steps_tail_one_by_one(requests, tail=32))
+    b = np.concatenate([tail[k] for k in sorted(tail)])
+    assert np.abs(a - b).max() <= 2e-6 * max(1.0, float(np.abs(a).max()))
