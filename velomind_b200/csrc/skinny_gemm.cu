@@ -19,330 +19,24 @@
 //
 // Sizes: K % 32 == 0, N % 8 == 0 (16 for the two-tile forms), head size % 16 == 0, I % 8 == 0; M <= 64.
 // Anything else is refused with VM_ERR_UNSUPPORTED and the caller uses the library product.
-#include "mma.cuh"
+#include "skinny_body.cuh"
 
 namespace {
 
-enum : int { PRO_NONE = 0, PRO_RMSNORM = 1 };
-enum : int { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3, EPI_ROPE_KV = 4 };
-
-constexpr int SK_WARPS = 8;
-constexpr int SK_THREADS = SK_WARPS * 32;
-
-struct SkinnyParams {
-    const void* A;               // bf16 [M, K] (PRO_NONE) or float32 residual [M, K] (PRO_RMSNORM)
-    const float* norm_w;         // [K]
-    float eps;
-    const __nv_bfloat16* W;      // [N, K]
-    int M, N, K;
-    int pro, epi, tiles;         // tiles: n8 tiles per CTA (1 or 2)
-    void* out;                   // bf16 or float32 [M, out_stride]
-    int out_stride;
-    float* h;                    // residual [M, N]
-    int I;                       // swiglu: rows of Wg (and of Wu)
-    // rope_kv
-    const int* positions; const int* seq_of_token; const int* block_table; int max_blocks;
-    const float* inv_freq; int rot_dim;
-    __nv_bfloat16* kpages; __nv_bfloat16* vpages; int H, Hkv, D, n_pages; int* err;
-    int kc;                      // k chunk staged in shared memory at a time (multiple of 32)
-    int row_bytes;               // shared-memory row pitch of the A tile, == 64 mod 128
-};
+using namespace vmsk;
 
 template <int MT>
 __global__ void __launch_bounds__(SK_THREADS)
 skinny_gemm_kernel(const SkinnyParams p) {
-    constexpr int ROWS = 16 * MT;
     extern __shared__ __align__(16) unsigned char smem[];
-    unsigned char* sA = smem;                                              // ROWS x row_bytes
-    float* red = reinterpret_cast<float*>(smem + (size_t)ROWS * p.row_bytes);   // [SK_WARPS][ROWS][16]
-    float* inv = red + SK_WARPS * ROWS * 16;                               // [ROWS]
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
-    vm_pdl_launch_dependents();
-
-    // ---- which output columns
-    int nA, nB, head = 0;
-    if (p.epi == EPI_SWIGLU) { nA = 8 * blockIdx.x; nB = p.I + nA; }
-    else if (p.epi == EPI_ROPE_KV) {
-        const int per_head = p.D / 16;
-        head = blockIdx.x / per_head;
-        const int sub = blockIdx.x - head * per_head;
-        if (head < p.H + p.Hkv && p.rot_dim > 0) { nA = head * p.D + 8 * sub; nB = nA + p.D / 2; }   // rotary pair (j, j + D/2)
-        else { nA = head * p.D + 16 * sub; nB = nA + 8; }
-    }
-    else if (p.tiles == 2) { nA = 16 * blockIdx.x; nB = nA + 8; }
-    else { nA = 8 * blockIdx.x; nB = nA; }
-    const __nv_bfloat16* wA = p.W + (size_t)(nA + g) * p.K;
-    const __nv_bfloat16* wB = p.W + (size_t)(nB + g) * p.K;
-    const bool two = (p.tiles == 2);
-
-    // ---- weight fragments do not depend on A: the first group of this warp's k blocks is requested before
-    //      anything else, so that its DRAM latency overlaps the staging of A
-    constexpr int PF = 8;                                   // k blocks in flight per warp
-    uint4 wa[PF], wb[PF];
-    auto issue = [&](int kc0, int blocks, int group) {
-#pragma unroll
-        for (int u = 0; u < PF; ++u) {
-            const int b = warp + SK_WARPS * (group * PF + u);
-            if (b < blocks) {
-                const int k = kc0 + 32 * b + 8 * t4;
-                wa[u] = *reinterpret_cast<const uint4*>(wA + k);
-                if (two) wb[u] = *reinterpret_cast<const uint4*>(wB + k);
-            }
-        }
-    };
-    issue(0, min(p.kc, p.K) / 32, 0);
-    vm_pdl_wait();                                          // from here on: data written by earlier kernels
-    // the epilogue's per-row facts (position, cache page) are fetched now, long before they are needed
-    int row_pos[MT], row_page[MT];
-    if (p.epi == EPI_ROPE_KV) {
-#pragma unroll
-        for (int i = 0; i < MT; ++i) {
-            const int item = tid + SK_THREADS * i;
-            const int row = item >> 3;
-            row_pos[i] = 0; row_page[i] = -1;
-            if (item < ROWS * 8 && row < p.M) {
-                row_pos[i] = p.positions[row];
-                if (head >= p.H && p.kpages != nullptr) {
-                    const int blk = row_pos[i] / VM_PAGE_TOKENS;
-                    row_page[i] = (blk < p.max_blocks) ? p.block_table[(size_t)p.seq_of_token[row] * p.max_blocks + blk] : -1;
-                }
-            }
-        }
-    }
-
-    float acc[MT][2][4];
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-        for (int t = 0; t < 2; ++t) acc[mt][t][0] = acc[mt][t][1] = acc[mt][t][2] = acc[mt][t][3] = 0.f;
-
-    for (int kc0 = 0; kc0 < p.K; kc0 += p.kc) {
-        const int kc = min(p.kc, p.K - kc0);
-        if (kc0 > 0) __syncthreads();                       // the previous chunk has been consumed
-        // ---- stage A[:, kc0 : kc0+kc] as bf16
-        if (p.pro == PRO_NONE) {
-            const __nv_bfloat16* A = static_cast<const __nv_bfloat16*>(p.A);
-            const int chunks = kc / 8;
-            for (int c = tid; c < ROWS * chunks; c += SK_THREADS) {
-                const int r = c / chunks, ch = c - r * chunks;
-                unsigned char* dst = sA + (size_t)r * p.row_bytes + ch * 16;
-                if (r < p.M) vm_cp_async16(dst, A + (size_t)r * p.K + kc0 + ch * 8);
-                else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
-            }
-            vm_cp_async_commit();
-            vm_cp_async_wait_all();
-        } else {
-            // x * w as bf16 (the row's 1/rms is applied to the float32 sums in the epilogue: a row scale
-            // commutes with the product); a warp owns whole rows and sums their squares on the way
-            const float* h = static_cast<const float*>(p.A);
-            const int quads = kc / 4;
-            for (int r = warp; r < ROWS; r += SK_WARPS) {
-                unsigned char* dst = sA + (size_t)r * p.row_bytes;
-                if (r >= p.M) {
-                    for (int qd = lane; qd < quads; qd += 32) *reinterpret_cast<uint2*>(dst + qd * 8) = make_uint2(0u, 0u);
-                    continue;
-                }
-                const float4* hrow = reinterpret_cast<const float4*>(h + (size_t)r * p.K + kc0);
-                const float4* wrow = reinterpret_cast<const float4*>(p.norm_w + kc0);
-                float ss = 0.f;
-                for (int q0 = lane; q0 < quads; q0 += 32 * 4) {
-                    float4 x[4], w[4];
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const int qd = q0 + 32 * u;
-                        if (qd < quads) { x[u] = hrow[qd]; w[u] = wrow[qd]; }
-                    }
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const int qd = q0 + 32 * u;
-                        if (qd < quads) {
-                            ss += x[u].x * x[u].x + x[u].y * x[u].y + x[u].z * x[u].z + x[u].w * x[u].w;
-                            uint2 v;
-                            v.x = vm_pack_bf16(x[u].x * w[u].x, x[u].y * w[u].y);
-                            v.y = vm_pack_bf16(x[u].z * w[u].z, x[u].w * w[u].w);
-                            *reinterpret_cast<uint2*>(dst + qd * 8) = v;
-                        }
-                    }
-                }
-                ss = vm_warp_sum(ss);
-                if (lane == 0) inv[r] = (kc0 == 0 ? 0.f : inv[r]) + ss;        // sum of squares so far
-            }
-        }
-        __syncthreads();
-        // ---- this warp's k blocks of the chunk: block b covers k = kc0 + 32 b .. + 31
-        const int blocks = kc / 32;
-        for (int group = 0; warp + SK_WARPS * group * PF < blocks; ++group) {
-            if (group > 0 || kc0 > 0) issue(kc0, blocks, group);
-#pragma unroll
-            for (int u = 0; u < PF; ++u) {
-                const int b = warp + SK_WARPS * (group * PF + u);
-                if (b < blocks) {
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) {
-                        const uint4 a_lo = *reinterpret_cast<const uint4*>(sA + (size_t)(mt * 16 + g) * p.row_bytes + (32 * b + 8 * t4) * 2);
-                        const uint4 a_hi = *reinterpret_cast<const uint4*>(sA + (size_t)(mt * 16 + g + 8) * p.row_bytes + (32 * b + 8 * t4) * 2);
-                        vm_mma_bf16_16816(acc[mt][0], a_lo.x, a_hi.x, a_lo.y, a_hi.y, wa[u].x, wa[u].y);
-                        vm_mma_bf16_16816(acc[mt][0], a_lo.z, a_hi.z, a_lo.w, a_hi.w, wa[u].z, wa[u].w);
-                        if (two) {
-                            vm_mma_bf16_16816(acc[mt][1], a_lo.x, a_hi.x, a_lo.y, a_hi.y, wb[u].x, wb[u].y);
-                            vm_mma_bf16_16816(acc[mt][1], a_lo.z, a_hi.z, a_lo.w, a_hi.w, wb[u].z, wb[u].w);
-                        }
-                    }
-                }
-            }
-        }
-    }
-    // ---- join the warps' partial sums: red[warp][row][col], col 0..7 = tile A, 8..15 = tile B
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-        for (int t = 0; t < 2; ++t)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int row = mt * 16 + g + 8 * (e >> 1), col = t * 8 + 2 * t4 + (e & 1);
-                red[((size_t)warp * ROWS + row) * 16 + col] = acc[mt][t][e];
-            }
-    __syncthreads();
-#pragma unroll
-    for (int it = 0; it < MT; ++it) {
-        const int item = tid + SK_THREADS * it;
-        if (item >= ROWS * 8) break;
-        const int row = item >> 3, c = item & 7;
-        if (row >= p.M) continue;
-        float vA = 0.f, vB = 0.f;
-#pragma unroll
-        for (int w = 0; w < SK_WARPS; ++w) {
-            vA += red[((size_t)w * ROWS + row) * 16 + c];
-            vB += red[((size_t)w * ROWS + row) * 16 + 8 + c];
-        }
-        if (p.pro == PRO_RMSNORM) {
-            const float rs = 1.0f / sqrtf(inv[row] / (float)p.K + p.eps);       // inv[] holds the row's sum of squares
-            vA *= rs; vB *= rs;
-        }
-        switch (p.epi) {
-            case EPI_STORE_BF16: {
-                __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + (size_t)row * p.out_stride;
-                o[nA + c] = __float2bfloat16_rn(vA);
-                if (two) o[nB + c] = __float2bfloat16_rn(vB);
-            } break;
-            case EPI_STORE_F32: {
-                float* o = static_cast<float*>(p.out) + (size_t)row * p.out_stride;
-                o[nA + c] = vA;
-                if (two) o[nB + c] = vB;
-            } break;
-            case EPI_RESIDUAL: {
-                float* o = p.h + (size_t)row * p.N;
-                o[nA + c] += vA;
-                if (two) o[nB + c] += vB;
-            } break;
-            case EPI_SWIGLU: {
-                const float sig = 1.0f / (1.0f + expf(-vA));
-                static_cast<__nv_bfloat16*>(p.out)[(size_t)row * p.out_stride + nA + c] = __float2bfloat16_rn((sig * vA) * vB);
-            } break;
-            case EPI_ROPE_KV: {
-                const int pos = row_pos[it];
-                float ya = vA, yb = vB;
-                int da, db;                                 // the two columns' places inside the head
-                if (head < p.H + p.Hkv && p.rot_dim > 0) {
-                    da = (nA - head * p.D) + c; db = da + p.D / 2;
-                    float s, co;
-                    sincosf((float)pos * p.inv_freq[da], &s, &co);
-                    ya = vA * co - vB * s;
-                    yb = vB * co + vA * s;
-                } else { da = (nA - head * p.D) + c; db = da + 8; }
-                if (head < p.H) {
-                    __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + (size_t)row * p.out_stride + (size_t)head * p.D;
-                    o[da] = __float2bfloat16_rn(ya); o[db] = __float2bfloat16_rn(yb);
-                } else if (p.kpages != nullptr) {
-                    const int page = row_page[it];
-                    if (page < 0 || page >= p.n_pages) { if (p.err) atomicExch(p.err, 2); break; }
-                    const bool is_k = head < p.H + p.Hkv;
-                    const int hk = is_k ? head - p.H : head - p.H - p.Hkv;
-                    __nv_bfloat16* dst = (is_k ? p.kpages : p.vpages) + (size_t)page * ((size_t)p.Hkv * VM_PAGE_TOKENS * p.D)
-                                         + ((size_t)hk * VM_PAGE_TOKENS + pos % VM_PAGE_TOKENS) * p.D;
-                    dst[da] = __float2bfloat16_rn(ya); dst[db] = __float2bfloat16_rn(yb);
-                }
-            } break;
-        }
-    }
+    skinny_body<MT, true>(p, blockIdx.x, smem);
 }
 
-// The same product for MANY output columns (the vocabulary head): the warps of a CTA split N instead of K.
-// Each warp owns 8 columns over all of K, so there is no cross-warp sum and the A tile is staged once per
-// 64 columns.  Plain A (bf16), store epilogue (bf16 or float32).
 template <int MT>
 __global__ void __launch_bounds__(SK_THREADS)
 skinny_wide_kernel(const SkinnyParams p) {
-    constexpr int ROWS = 16 * MT;
-    constexpr int PF = 6;
     extern __shared__ __align__(16) unsigned char smem[];
-    unsigned char* sA = smem;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
-    vm_pdl_launch_dependents();
-    const int n0 = (blockIdx.x * SK_WARPS + warp) * 8;
-    const bool live = n0 < p.N;
-    const __nv_bfloat16* wrow = p.W + (size_t)(live ? n0 + g : 0) * p.K;
-    uint4 wa[PF];
-    auto issue = [&](int first_block, int blocks) {
-#pragma unroll
-        for (int u = 0; u < PF; ++u) {
-            const int b = first_block + u;
-            if (live && b < blocks) wa[u] = *reinterpret_cast<const uint4*>(wrow + 32 * b + 8 * t4);
-        }
-    };
-    const int blocks = p.K / 32;
-    issue(0, blocks);
-    vm_pdl_wait();
-    float acc[MT][4];
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
-    {
-        const __nv_bfloat16* A = static_cast<const __nv_bfloat16*>(p.A);
-        const int chunks = p.K / 8;
-        for (int c = tid; c < ROWS * chunks; c += SK_THREADS) {
-            const int r = c / chunks, ch = c - r * chunks;
-            unsigned char* dst = sA + (size_t)r * p.row_bytes + ch * 16;
-            if (r < p.M) vm_cp_async16(dst, A + (size_t)r * p.K + ch * 8);
-            else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
-        }
-        vm_cp_async_commit();
-        vm_cp_async_wait_all();
-    }
-    __syncthreads();
-    for (int b0 = 0; b0 < blocks; b0 += PF) {
-        if (b0 > 0) issue(b0, blocks);
-#pragma unroll
-        for (int u = 0; u < PF; ++u) {
-            const int b = b0 + u;
-            if (live && b < blocks) {
-#pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-                    const uint4 a_lo = *reinterpret_cast<const uint4*>(sA + (size_t)(mt * 16 + g) * p.row_bytes + (32 * b + 8 * t4) * 2);
-                    const uint4 a_hi = *reinterpret_cast<const uint4*>(sA + (size_t)(mt * 16 + g + 8) * p.row_bytes + (32 * b + 8 * t4) * 2);
-                    vm_mma_bf16_16816(acc[mt], a_lo.x, a_hi.x, a_lo.y, a_hi.y, wa[u].x, wa[u].y);
-                    vm_mma_bf16_16816(acc[mt], a_lo.z, a_hi.z, a_lo.w, a_hi.w, wa[u].z, wa[u].w);
-                }
-            }
-        }
-    }
-    if (!live) return;
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-            const int row = mt * 16 + g + 8 * half;
-            if (row >= p.M) continue;
-            const int col = n0 + 2 * t4;
-            const float v0 = acc[mt][2 * half], v1 = acc[mt][2 * half + 1];
-            if (p.epi == EPI_STORE_F32) {
-                float* o = static_cast<float*>(p.out) + (size_t)row * p.out_stride + col;
-                o[0] = v0; o[1] = v1;
-            } else {
-                __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + (size_t)row * p.out_stride + col;
-                o[0] = __float2bfloat16_rn(v0); o[1] = __float2bfloat16_rn(v1);
-            }
-        }
-    }
+    skinny_wide_body<MT, true>(p, blockIdx.x, smem);
 }
 
 int skinny_wide_launch(SkinnyParams p, cudaStream_t stream) {
