@@ -208,3 +208,30 @@ def test_float32_cuts_agree_bit_for_bit_in_attention_order(wide_folder):
     tail = S.run_steps_in_process(engine, S.steps_tail_one_by_one(requests, tail=32))
     b = np.concatenate([tail[k] for k in sorted(tail)])
     assert np.abs(a - b).max() <= 2e-6 * max(1.0, float(np.abs(a).max()))
+
+
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_c"])
+@pytest.mark.parametrize("persistent", [True, False])
+def test_greedy_decode_tokens_are_near_argmax_of_plain(model_folders, name, persistent):
+    """bfloat16 greedy decoding, through the persistent decode kernel and part by part: every generated token must be
+    (within bf16's error) a maximum of the plain model's logits at its place; and both ways must really be taken."""
+    import velomind_b200 as vm
+    folder = model_folders[name]
+    cfg, w = P.read_model(folder)
+    V = CONFIGS[name]["vocab_size"]
+    rng = np.random.default_rng(3)
+    prompts = [[int(t) for t in rng.integers(0, V, n)] for n in (70, 3, 129, 20, 64)]
+    model = vm.load_model(folder, torch.bfloat16, "cuda:0")
+    engine = vm.Engine(model, 64 * 32, persistent_decode=persistent)
+    assert (engine.mega is not None and engine.mega.ok) == persistent, getattr(engine.mega, "why", "")
+    loop = vm.GenerationLoop(engine, vm.DeviceSampler(engine.device), engine.cache.n_pages, 16, steps_per_sync=8)
+    out = loop.run([vm.Request(p, vm.SamplingParams(temperature=0.0, max_tokens=30), stream=i) for i, p in enumerate(prompts)])
+    engine.raise_if_error()
+    for p, r in zip(prompts, out):
+        assert len(r.tokens) == 30
+        ref = P.forward_logits(cfg, w, p + r.tokens[:-1])
+        scale = max(1.0, float(np.abs(ref).max()))
+        for j, tok in enumerate(r.tokens):
+            row = ref[len(p) - 1 + j]
+            assert row[tok] >= row.max() - 2 * TOL["bfloat16"] * scale, (j, tok, int(row.argmax()))
+    assert engine.cache.slots.held_count == 0

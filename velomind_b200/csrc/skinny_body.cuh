@@ -133,7 +133,7 @@ __device__ __forceinline__ void skinny_body(const SkinnyParams& p, const int ite
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
                         const int qd = q0 + 32 * u;
-                        if (qd < quads) { x[u] = hrow[qd]; w[u] = wrow[qd]; }
+                        if (qd < quads) { x[u] = __ldcg(hrow + qd); w[u] = wrow[qd]; }     // h: from L2, another SM may have written it
                     }
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
@@ -214,9 +214,9 @@ __device__ __forceinline__ void skinny_body(const SkinnyParams& p, const int ite
                 if (two) o[nB + c] = vB;
             } break;
             case EPI_RESIDUAL: {
-                float* o = p.h + (size_t)row * p.N;
-                o[nA + c] += vA;
-                if (two) o[nB + c] += vB;
+                float* o = p.h + (size_t)row * p.N;          // read from L2: another SM may have written h earlier in a persistent kernel
+                o[nA + c] = __ldcg(o + nA + c) + vA;
+                if (two) o[nB + c] = __ldcg(o + nB + c) + vB;
             } break;
             case EPI_SWIGLU: {
                 const float sig = 1.0f / (1.0f + expf(-vA));

@@ -25,8 +25,9 @@ namespace {
 
 using namespace vmsk;
 
+// (two CTAs per SM for up to 16 rows: 192 gate/up items then fit the GPU at once)
 template <int MT>
-__global__ void __launch_bounds__(SK_THREADS)
+__global__ void __launch_bounds__(SK_THREADS, MT == 1 ? 2 : 1)
 skinny_gemm_kernel(const SkinnyParams p) {
     extern __shared__ __align__(16) unsigned char smem[];
     skinny_body<MT, true>(p, blockIdx.x, smem);

@@ -20,6 +20,7 @@ from ..cache.pages import PAGE_TOKENS, CacheError
 from ..cache.store import SequenceCache
 from ..kernels import ops
 from .arena import Workspace
+from .mega import MAX_ROWS as MEGA_MAX_ROWS, MegaPlan
 from .model import DecoderModel
 
 
@@ -170,7 +171,7 @@ class Engine:
 
     def __init__(self, model: DecoderModel, max_tokens: int, max_slots: Optional[int] = None,
                  max_step_tokens: int = 8192, use_graphs: Optional[bool] = None,
-                 fused_prefill_rows: Optional[int] = None):
+                 fused_prefill_rows: Optional[int] = None, persistent_decode: bool = False):
         if model.device is None:
             raise RuntimeError("the model has no weights bound; use load_model()")
         self.model = model
@@ -192,6 +193,9 @@ class Engine:
         self.graphs_captured = 0
         self._shape_seen: Dict[Tuple, int] = {}
         self._run_state = None
+        # one persistent kernel per decode step where the model allows it (engine/mega.py); measured slower than the graph of
+        # dependent launches so far (profiles/decode_persistent_kernel.md), hence off unless asked for
+        self.mega = MegaPlan(model, self.cache) if (persistent_decode and self.dtype == torch.bfloat16) else None
         self.steps_run = 0
 
     # ---- slots
@@ -263,8 +267,14 @@ class Engine:
         ctx.logits = logits[:B]
         bucket = (desc.caps[0], desc.caps[1], desc.caps[2], True, self.fused_prefill_rows)
 
+        mega = self.mega is not None and self.mega.ok and B <= MEGA_MAX_ROWS
+        bucket = bucket + ("mega",) if mega else bucket
+
         def one_step():
-            self.model.forward(ctx)
+            if mega:
+                self.mega.run(ctx)
+            else:
+                self.model.forward(ctx)
             ops.sample(ctx.logits, st["dev_f"][0, :B], st["dev_f"][1, :B], st["dev_i"][0, :B], st["dev_i"][1, :B],
                        st["dev_i"][2, :B], st["sampled"][:B])
             ops.decode_advance(st["sampled"][:B], ctx.tokens, ctx.positions, ctx.ctx_len, st["dev_i"][2, :B],
