@@ -10,6 +10,8 @@ returns float32 logits at the wanted places.
 """
 from __future__ import annotations
 
+import gc
+
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -110,7 +112,7 @@ class StepContext:
     """
 
     def __init__(self, engine: "Engine", desc: Descriptors, T: int, B: int, R: int, table_widths: Sequence[int]):
-        self.engine = engine
+        self.schedule = engine.model.plan.schedule      # (no reference to the engine itself: a kept context would tie a cycle)
         self.cache: SequenceCache = engine.cache
         self.ws: Workspace = engine.ws
         self.act_dtype: torch.dtype = engine.dtype
@@ -130,13 +132,20 @@ class StepContext:
         self.host_cu_tokens = desc.h("cu_tokens")[:B + 1]
         self.host_ctx_len = desc.h("ctx_len")[:B]
         self.host_slots = desc.h("slots")[:B]
+        self.run: Optional[int] = None
+        self.logits: Optional[torch.Tensor] = None
+        # `capturing`: True while the step is recorded into a CUDA graph: no choice may depend on this step's lengths,
+        # only on its shape (T, B, R, table widths)
+        self.refresh()
+
+    def refresh(self) -> None:
+        """Re-read what depends on the values (not the shape) of the descriptors: a kept context serves a new step."""
+        B, T = self.B, self.T
         self.max_ctx_len = int(self.host_ctx_len.max()) if B else 0
         self.max_new = int(np.diff(self.host_cu_tokens).max()) if B else 0
         self.one_token_each = (self.max_new == 1 and T == B)
-        self.run: Optional[int] = None
-        self.logits: Optional[torch.Tensor] = None
-        self.capturing = False          # True while the step is recorded into a CUDA graph: no choice may depend
-        #                                 on this step's lengths, only on its shape (T, B, R, table widths)
+        self.run = None
+        self.capturing = False
 
     # ---- scratch
     def take_tokens(self, cols: int, dtype: torch.dtype) -> torch.Tensor:
@@ -157,7 +166,7 @@ class StepContext:
         g, layer = self.cache.where(self.run)
         group = self.cache.groups[g]
         k, v = group.layer(layer)
-        owns = self.engine.model.plan.schedule[self.run].cache_of is None
+        owns = self.schedule[self.run].cache_of is None
         return k, v, self.tables[g], owns
 
     def state(self) -> Optional[torch.Tensor]:
@@ -193,6 +202,7 @@ class Engine:
         self.graphs_captured = 0
         self._shape_seen: Dict[Tuple, int] = {}
         self._run_state = None
+        self._contexts: Dict[Tuple, StepContext] = {}
         # one persistent kernel per decode step where the model allows it (engine/mega.py); measured slower than the graph of
         # dependent launches so far (profiles/decode_persistent_kernel.md), hence off unless asked for
         self.mega = MegaPlan(model, self.cache) if (persistent_decode and self.dtype == torch.bfloat16) else None
@@ -262,7 +272,7 @@ class Engine:
         st["dev_f"].copy_(st["host_f"], non_blocking=True)
         st["dev_i"].copy_(st["host_i"], non_blocking=True)
         st["iteration"].zero_()
-        ctx = StepContext(self, desc, T, B, R, widths)
+        ctx = self._context(desc, T, B, R, widths)
         logits = self._logits_buffer(B)
         ctx.logits = logits[:B]
         bucket = (desc.caps[0], desc.caps[1], desc.caps[2], True, self.fused_prefill_rows)
@@ -284,23 +294,7 @@ class Engine:
             key = ("run", bucket, (B, tuple(widths), logits.data_ptr(), st["sampled"].data_ptr()), self.ws.generation)
             graph = self._graphs.get(key)
             if graph is None:
-                ctx.capturing = True
-                ops.TC_FUSED_MIN_ROWS = self.fused_prefill_rows
-                graph = torch.cuda.CUDAGraph()
-                torch.cuda.current_stream().synchronize()
-                own, lib = ops.launch_count, ops.library_calls
-                self.ws.begin(bucket)
-                try:
-                    with torch.cuda.graph(graph):
-                        one_step()
-                except Exception:
-                    self.ws.abort()
-                    raise
-                self.ws.end()
-                graph.launches = (ops.launch_count - own, ops.library_calls - lib)
-                ops.launch_count, ops.library_calls = own, lib
-                self._graphs[key] = graph
-                self.graphs_captured += 1
+                graph = self._record(ctx, bucket, key, one_step)
             for _ in range(k):
                 graph.replay()
             ops.launch_count += k * graph.launches[0]
@@ -419,6 +413,37 @@ class Engine:
             raise
         self.ws.end()
 
+    def _record(self, ctx: StepContext, bucket, key, body) -> "torch.cuda.CUDAGraph":
+        """Record `body()` (the launches of one step) into a CUDA graph and keep it under `key`."""
+        if len(self._graphs) >= 256:
+            self._graphs.clear()
+        ctx.capturing = True
+        ops.TC_FUSED_MIN_ROWS = self.fused_prefill_rows
+        graph = torch.cuda.CUDAGraph()
+        torch.cuda.current_stream().synchronize()
+        own, lib = ops.launch_count, ops.library_calls
+        self.ws.begin(bucket)
+        # the collector must not free another engine's graphs meanwhile: destroying a graph is not allowed while a
+        # stream records, and ends the recording with an error
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph):
+                body()
+        except Exception:
+            self.ws.abort()
+            raise
+        finally:
+            if collecting:
+                gc.enable()
+        self.ws.end()
+        # what a replay launches: counted once here, added to the counters at every replay
+        graph.launches = (ops.launch_count - own, ops.library_calls - lib)
+        ops.launch_count, ops.library_calls = own, lib
+        self._graphs[key] = graph
+        self.graphs_captured += 1
+        return graph
+
     def _replay_graph(self, ctx: StepContext, bucket, shape_key) -> None:
         """Steps are launch-bound (hundreds of small kernels): the kernels of a step are captured once per
         step shape into a CUDA graph and replayed.  Everything that changes from step to step (tokens,
@@ -428,26 +453,7 @@ class Engine:
         key = (bucket, shape_key, self.ws.generation)
         graph = self._graphs.get(key)
         if graph is None:
-            if len(self._graphs) >= 256:
-                self._graphs.clear()
-            ctx.capturing = True
-            ops.TC_FUSED_MIN_ROWS = self.fused_prefill_rows
-            graph = torch.cuda.CUDAGraph()
-            torch.cuda.current_stream().synchronize()
-            own, lib = ops.launch_count, ops.library_calls
-            self.ws.begin(bucket)
-            try:
-                with torch.cuda.graph(graph):
-                    self.model.forward(ctx)
-            except Exception:
-                self.ws.abort()
-                raise
-            self.ws.end()
-            # what a replay launches: counted once here, added to the counters at every replay
-            graph.launches = (ops.launch_count - own, ops.library_calls - lib)
-            ops.launch_count, ops.library_calls = own, lib
-            self._graphs[key] = graph
-            self.graphs_captured += 1
+            graph = self._record(ctx, bucket, key, lambda: self.model.forward(ctx))
         graph.replay()
         ops.launch_count += graph.launches[0]
         ops.library_calls += graph.launches[1]
@@ -481,37 +487,71 @@ class Engine:
         desc.wait_reusable()
         tok, pos, sot = desc.h("tokens"), desc.h("positions"), desc.h("seq_of_token")
         cu, slots, ctx_len, lrows = desc.h("cu_tokens"), desc.h("slots"), desc.h("ctx_len"), desc.h("logit_rows")
-        t0 = 0
-        cu[0] = 0
-        start_of = {}
-        for s, (i, a, b) in enumerate(chunk):
-            e = entries[i]
-            n = b - a
-            base = cache.length[e.slot]
-            tok[t0: t0 + n] = np.asarray(e.tokens[a:b], dtype=np.int32)
-            pos[t0: t0 + n] = np.arange(base, base + n, dtype=np.int32)
-            sot[t0: t0 + n] = s
-            slots[s] = e.slot
-            ctx_len[s] = base + n
-            new_len.append(base + n)
-            start_of[i] = t0 - a
-            t0 += n
-            cu[s + 1] = t0
-        for r, (i, w) in enumerate(wanted_here):
-            lrows[r] = start_of[i] + w
-        for g, group in enumerate(cache.groups):
-            w = widths[g]
-            tab = desc.h(f"table{g}").reshape(desc.caps[1], w)
-            for s, (i, _, _) in enumerate(chunk):
-                tab[s, :] = group.block_table[entries[i].slot, :w]
+        if T == B:
+            # one token per sequence (decode): everything in whole-array operations
+            slot_ids = np.fromiter((entries[i].slot for i, _, _ in chunk), dtype=np.int64, count=B)
+            base = np.fromiter((cache.length[int(x)] for x in slot_ids), dtype=np.int32, count=B)
+            tok[:B] = np.fromiter((entries[i].tokens[a] for i, a, _ in chunk), dtype=np.int32, count=B)
+            pos[:B] = base
+            sot[:B] = np.arange(B, dtype=np.int32)
+            cu[:B + 1] = np.arange(B + 1, dtype=np.int32)
+            slots[:B] = slot_ids
+            ctx_len[:B] = base + 1
+            new_len = (base + 1).tolist()
+            order = {i: s for s, (i, _, _) in enumerate(chunk)}
+            for r, (i, w) in enumerate(wanted_here):
+                lrows[r] = order[i]
+            for g, group in enumerate(cache.groups):
+                w = widths[g]
+                desc.h(f"table{g}").reshape(desc.caps[1], w)[:B] = group.block_table[slot_ids, :w]
+        else:
+            t0 = 0
+            cu[0] = 0
+            start_of = {}
+            for s, (i, a, b) in enumerate(chunk):
+                e = entries[i]
+                n = b - a
+                base = cache.length[e.slot]
+                tok[t0: t0 + n] = np.asarray(e.tokens[a:b], dtype=np.int32)
+                pos[t0: t0 + n] = np.arange(base, base + n, dtype=np.int32)
+                sot[t0: t0 + n] = s
+                slots[s] = e.slot
+                ctx_len[s] = base + n
+                new_len.append(base + n)
+                start_of[i] = t0 - a
+                t0 += n
+                cu[s + 1] = t0
+            for r, (i, w) in enumerate(wanted_here):
+                lrows[r] = start_of[i] + w
+            for g, group in enumerate(cache.groups):
+                w = widths[g]
+                tab = desc.h(f"table{g}").reshape(desc.caps[1], w)
+                for s, (i, _, _) in enumerate(chunk):
+                    tab[s, :] = group.block_table[entries[i].slot, :w]
         desc.upload()
         return desc, T, B, R, widths, new_len, wanted_here
+
+    def _context(self, desc, T: int, B: int, R: int, widths) -> StepContext:
+        """The step's view of its descriptors.  Decode steps come in few shapes, and building the dozen tensor views
+        costs as much host time as the rest of the step, so those contexts are kept and refreshed."""
+        if T != B:
+            return StepContext(self, desc, T, B, R, widths)
+        key = (id(desc), T, B, R, tuple(widths))
+        ctx = self._contexts.get(key)
+        if ctx is None:
+            if len(self._contexts) > 64:
+                self._contexts.clear()
+            ctx = StepContext(self, desc, T, B, R, widths)
+            self._contexts[key] = ctx
+        else:
+            ctx.refresh()
+        return ctx
 
     def _run_chunk(self, entries, chunk, logits, row0, produced) -> int:
         cache = self.cache
         desc, T, B, R, widths, new_len, wanted_here = self._describe(entries, chunk)
 
-        ctx = StepContext(self, desc, T, B, R, widths)
+        ctx = self._context(desc, T, B, R, widths)
         ctx.logits = logits[row0: row0 + R]
         bucket = (desc.caps[0], desc.caps[1], desc.caps[2], ctx.one_token_each, self.fused_prefill_rows)   # decode steps take other scratch
         lens = tuple(int(x) for x in np.diff(ctx.host_cu_tokens)) if not ctx.one_token_each else ()

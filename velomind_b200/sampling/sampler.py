@@ -49,10 +49,15 @@ class DeviceSampler:
 
     def _alloc(self, rows: int) -> None:
         self.rows = rows
-        self.host_f = _host_buffer((2, rows), torch.float32)
-        self.host_i = _host_buffer((3, rows), torch.int64)
-        self.dev_f = torch.empty((2, rows), dtype=torch.float32, device=self.device)
-        self.dev_i = torch.empty((3, rows), dtype=torch.int64, device=self.device)
+        # one byte buffer: int64 seed, stream, step [3, rows], then float32 temperature, top_p [2, rows]: ONE host-to-device copy
+        nbytes = 3 * 8 * rows + 2 * 4 * rows
+        self.host = _host_buffer((nbytes,), torch.uint8)
+        self.dev = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
+        split = 3 * 8 * rows
+        self.host_i = self.host[:split].view(torch.int64).view(3, rows)
+        self.host_f = self.host[split:].view(torch.float32).view(2, rows)
+        self.dev_i = self.dev[:split].view(torch.int64).view(3, rows)
+        self.dev_f = self.dev[split:].view(torch.float32).view(2, rows)
         self.out = torch.empty(rows, dtype=torch.int32, device=self.device)
         self.out_host = _host_buffer((rows,), torch.int32)
 
@@ -69,9 +74,8 @@ class DeviceSampler:
         for r, p in enumerate(params):
             hf[0, r], hf[1, r] = p.temperature, p.top_p
             hi[0, r], hi[1, r], hi[2, r] = p.seed, streams[r], steps[r]
-        self.dev_f.copy_(self.host_f, non_blocking=True)
-        self.dev_i.copy_(self.host_i, non_blocking=True)
-        ops.sample(logits, self.dev_f[0], self.dev_f[1], self.dev_i[0], self.dev_i[1], self.dev_i[2], self.out)
+        self.dev.copy_(self.host, non_blocking=True)
+        ops.sample(logits, self.dev_f[0, :R], self.dev_f[1, :R], self.dev_i[0, :R], self.dev_i[1, :R], self.dev_i[2, :R], self.out)
         self.out_host.copy_(self.out, non_blocking=True)
         _sync()
         return self.out_host.numpy()[:R].copy()
