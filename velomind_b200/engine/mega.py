@@ -18,6 +18,38 @@ from ..kernels import ops
 MAX_ROWS = 16
 
 
+def uniform_layers(model, cache):
+    """The layers of `model` as the fused decode kernels see them: (per-run descriptions, the first mixer's, the first
+    feed-forward's), if every run is pre-norm (RMSNorm) grouped-query attention + SwiGLU in bfloat16, all alike in
+    their sizes, each owning its cache in one unwindowed group.  Raises _NotApplicable otherwise."""
+    plan = model.plan
+    if model.dtype != torch.bfloat16:
+        raise _NotApplicable("compute dtype is not bfloat16")
+    if any(e.cache_of is not None for e in plan.schedule):
+        raise _NotApplicable("a run reads another run's cache")
+    if len(cache.groups) != 1 or cache.groups[0].need.kind != "all":
+        raise _NotApplicable("more than one cache group, or a windowed one")
+    infos = []
+    for entry in plan.schedule:
+        block = model.layers[entry.layer].block
+        info = getattr(block, "fused_decode_info", lambda: None)()
+        if info is None or info["mixer"]["kind"] != "grouped_query_attention" or info["feed_forward"]["kind"] != "swiglu":
+            raise _NotApplicable("a layer is not pre-norm attention + SwiGLU in bfloat16")
+        infos.append(info)
+    m0, f0 = infos[0]["mixer"], infos[0]["feed_forward"]
+    keys_m = ("hidden", "heads", "kv_heads", "head_dim", "scale", "window", "rotary_dim")
+    for info in infos:
+        if any(info["mixer"][k] != m0[k] for k in keys_m) or info["feed_forward"]["intermediate"] != f0["intermediate"]:
+            raise _NotApplicable("layers differ in their sizes")
+        if info["mixer"]["inv_freq"] is not m0["inv_freq"] and not (
+                info["mixer"]["inv_freq"] is not None and m0["inv_freq"] is not None
+                and torch.equal(info["mixer"]["inv_freq"], m0["inv_freq"])):
+            raise _NotApplicable("layers differ in their rotary frequencies")
+    if m0["hidden"] != plan.hidden_size:
+        raise _NotApplicable("the mixers' width is not the model's")
+    return infos, m0, f0
+
+
 class MegaPlan:
     def __init__(self, model, cache):
         self.ok = False
@@ -29,29 +61,8 @@ class MegaPlan:
             self.why = str(e)
 
     def _build(self, model, cache) -> None:
+        infos, m0, f0 = uniform_layers(model, cache)
         plan = model.plan
-        if model.dtype != torch.bfloat16:
-            raise _NotApplicable("compute dtype is not bfloat16")
-        if any(e.cache_of is not None for e in plan.schedule):
-            raise _NotApplicable("a run reads another run's cache")
-        if len(cache.groups) != 1 or cache.groups[0].need.kind != "all":
-            raise _NotApplicable("more than one cache group, or a windowed one")
-        infos = []
-        for entry in plan.schedule:
-            block = model.layers[entry.layer].block
-            info = getattr(block, "fused_decode_info", lambda: None)()
-            if info is None or info["mixer"]["kind"] != "grouped_query_attention" or info["feed_forward"]["kind"] != "swiglu":
-                raise _NotApplicable("a layer is not pre-norm attention + SwiGLU in bfloat16")
-            infos.append(info)
-        m0, f0 = infos[0]["mixer"], infos[0]["feed_forward"]
-        keys_m = ("hidden", "heads", "kv_heads", "head_dim", "scale", "window", "rotary_dim")
-        for info in infos:
-            if any(info["mixer"][k] != m0[k] for k in keys_m) or info["feed_forward"]["intermediate"] != f0["intermediate"]:
-                raise _NotApplicable("layers differ in their sizes")
-            if info["mixer"]["inv_freq"] is not m0["inv_freq"] and not (
-                    info["mixer"]["inv_freq"] is not None and m0["inv_freq"] is not None
-                    and torch.equal(info["mixer"]["inv_freq"], m0["inv_freq"])):
-                raise _NotApplicable("layers differ in their rotary frequencies")
         self.hid, self.H, self.Hkv, self.D = m0["hidden"], m0["heads"], m0["kv_heads"], m0["head_dim"]
         self.I, self.V = f0["intermediate"], plan.vocab_size
         self.scale, self.window, self.rot_dim, self.inv_freq = m0["scale"], m0["window"], m0["rotary_dim"], m0["inv_freq"]

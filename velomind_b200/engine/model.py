@@ -97,6 +97,12 @@ class DecoderModel:
             ctx.run = run
             pending = self.layers[entry.layer].block.forward(ctx, h, pending)
         ctx.run = None
+        return self.finish(ctx, h, pending)
+
+    def finish(self, ctx, h: torch.Tensor, pending) -> torch.Tensor:
+        """Final norm and head on the wanted rows of the residual stream `h` (plus `pending`, a product not yet added
+        to it); gives `h` and `pending` back to the workspace."""
+        hid = self.plan.hidden_size
         logits = ctx.logits
         x = ctx.take_rows(hid, ctx.act_dtype)
         if ctx.R > 0:

@@ -1,10 +1,11 @@
-"""Builds and loads the CUDA kernel library (`csrc/*.cu` -> one shared object) and nothing else.
+"""Builds and loads the CUDA kernel libraries (`csrc/*.cu` -> shared objects) and nothing else.
 
 The kernels are plain CUDA with `extern "C"` launchers; they are compiled with
 nvcc for sm_100a and loaded through ctypes, so the build needs neither the
 torch headers nor a writable HOME.  The first call compiles what is missing or
 out of date (a few files in parallel, a progress line now and then on stderr);
-later calls find the library by the hash of its sources and flags.
+later calls find the library by the hash of its sources and flags.  The kernels every engine needs are one
+library ("core"); each optional decode kernel is a library of its own, compiled when an engine first asks for it.
 
 There is no fallback: if the library cannot be built or loaded, every kernel
 call raises `KernelLibraryError`.
@@ -27,6 +28,8 @@ CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC"]
 LIB_NAME = "libvelomind_b200_kernels.so"
+# optional kernels, each a library of its own (group name -> source files); everything else is the "core" library
+OPTIONAL = {"decode_cluster": ["decode_cluster.cu"], "decode_mega": ["decode_mega.cu"]}
 
 
 class KernelLibraryError(RuntimeError):
@@ -34,11 +37,24 @@ class KernelLibraryError(RuntimeError):
 
 
 _lock = threading.Lock()
-_lib: Optional[ctypes.CDLL] = None
+_libs = {}
 
 
-def sources() -> List[str]:
-    return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cu"))
+def groups() -> List[str]:
+    return ["core"] + sorted(OPTIONAL)
+
+
+def sources(group: str = "core") -> List[str]:
+    if group in OPTIONAL:
+        return [os.path.join(CSRC, f) for f in OPTIONAL[group]]
+    if group != "core":
+        raise KernelLibraryError(f"no kernel library named {group!r}")
+    held_back = {f for fs in OPTIONAL.values() for f in fs}
+    return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cu") and f not in held_back)
+
+
+def lib_name(group: str = "core") -> str:
+    return LIB_NAME if group == "core" else f"libvelomind_b200_{group}.so"
 
 
 def _headers() -> List[str]:
@@ -53,9 +69,9 @@ def _nvcc() -> str:
                              "the kernels cannot be compiled")
 
 
-def _digest() -> str:
+def _digest(group: str = "core") -> str:
     h = hashlib.sha256()
-    for p in sources() + _headers():
+    for p in sources(group) + _headers():
         h.update(os.path.basename(p).encode())
         with open(p, "rb") as f:
             h.update(f.read())
@@ -105,19 +121,20 @@ def _compile_one(nvcc: str, src: str, obj: str, verbose_ptxas: bool) -> None:
             f.write(r.stderr)
 
 
-def build(force: bool = False, verbose_ptxas: bool = False) -> str:
-    """Compile the library if its sources changed; return the path of the shared object."""
+def build(force: bool = False, verbose_ptxas: bool = False, group: str = "core") -> str:
+    """Compile the library `group` if its sources changed; return the path of the shared object."""
     bdir = build_dir()
-    digest = _digest()
-    target = os.path.join(bdir, LIB_NAME)
-    stamp = os.path.join(bdir, "sources.sha")
+    digest = _digest(group)
+    name = lib_name(group)
+    target = os.path.join(bdir, name)
+    stamp = os.path.join(bdir, "sources.sha" if group == "core" else f"sources.{group}.sha")
     if not force and os.path.isfile(target) and os.path.isfile(stamp):
         with open(stamp) as f:
             if f.read().strip() == digest:
                 return target
     nvcc = _nvcc()
-    srcs = sources()
-    _say(f"compiling {len(srcs)} CUDA files for sm_100a into {bdir} (first call only)")
+    srcs = sources(group)
+    _say(f"compiling {len(srcs)} CUDA file{'s' if len(srcs) > 1 else ''} ({group}) for sm_100a into {bdir} (first call only)")
     t0 = time.time()
     done = threading.Event()
 
@@ -138,7 +155,7 @@ def build(force: bool = False, verbose_ptxas: bool = False) -> str:
         r = subprocess.run([nvcc, *ARCH_FLAGS, "-shared", "-o", tmp_target, *objs, "-lcudart"],
                            capture_output=True, text=True)
         if r.returncode != 0:
-            raise KernelLibraryError(f"linking {LIB_NAME} failed:\n{r.stdout}\n{r.stderr}")
+            raise KernelLibraryError(f"linking {name} failed:\n{r.stdout}\n{r.stderr}")
         os.replace(tmp_target, target)
         with open(stamp, "w") as f:
             f.write(digest)
@@ -149,20 +166,23 @@ def build(force: bool = False, verbose_ptxas: bool = False) -> str:
                 pass
     finally:
         done.set()
-    _say(f"kernel library ready ({time.time() - t0:.0f} s)")
+    _say(f"kernel library {name} ready ({time.time() - t0:.0f} s)")
     return target
 
 
-def library() -> ctypes.CDLL:
-    """The loaded kernel library; built at the first call if need be."""
-    global _lib
-    if _lib is not None:
-        return _lib
+def library(group: str = "core") -> ctypes.CDLL:
+    """The loaded kernel library `group`; built at the first call if need be.  The optional libraries use symbols
+    of the core library, which is therefore loaded first and globally."""
+    lib = _libs.get(group)
+    if lib is not None:
+        return lib
+    if group != "core":
+        library("core")
     with _lock:
-        if _lib is None:
-            path = build()
+        if group not in _libs:
+            path = build(group=group)
             try:
-                _lib = ctypes.CDLL(path)
+                _libs[group] = ctypes.CDLL(path, mode=ctypes.RTLD_GLOBAL)
             except OSError as e:
                 raise KernelLibraryError(f"cannot load {path}: {e}") from None
-    return _lib
+    return _libs[group]
