@@ -6,7 +6,8 @@
 // online form of src/cpu/ops/fused_attention.cpp:84-135); the G = H / Hkv query heads that share a kv
 // head (src/cpu/ops/repeat_kv.cpp:51-61) are served by one CTA, so each key and value is read once.
 //
-// grid = (n_splits, Hkv * ceil(G / 16), B), 128 threads.  A CTA's key range is a whole number of cache
+// grid = (n_splits, Hkv * ceil(G / 16), B), 128 threads; or, with one split and no more CTAs than SMs, 320 threads
+// (ten warps, a cache page each: a sequence of up to 640 tokens is one round, and no partial result leaves the CTA).  A CTA's key range is a whole number of cache
 // pages, computed on the device from the sequence's length: the launch shape does not depend on the
 // lengths, so the launch can sit in a CUDA graph.  Head sizes 16, 32, ..., 128.  Scratch (global memory beyond inputs and outputs):
 // float partials [B, H, n_splits, D + 2] and one int counter per (B, kv-head group), which must be zero
@@ -16,34 +17,36 @@
 namespace {
 
 constexpr int DEC_WARPS = 4;
+constexpr int DEC_WARPS_WIDE = 10;
+constexpr int DEC_WIDE_MAX_CTAS = 148;
 using namespace vmad;
 
-template <int D>
-__global__ void __launch_bounds__(DEC_WARPS * 32)
+template <int D, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, const __nv_bfloat16* __restrict__ kpages,
                    const __nv_bfloat16* __restrict__ vpages, const int* __restrict__ block_table, int max_blocks,
                    const int* __restrict__ positions, __nv_bfloat16* __restrict__ out, float* __restrict__ partial,
                    int* __restrict__ counters, int H, int Hkv, float scale_log2, int window, int n_pages,
                    int* __restrict__ err) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    attn_decode_body<D, DEC_WARPS, true>(q, q_row_stride, kpages, vpages, block_table, max_blocks, positions, out, partial,
+    attn_decode_body<D, WARPS, true>(q, q_row_stride, kpages, vpages, block_table, max_blocks, positions, out, partial,
                                          counters, H, Hkv, scale_log2, window, n_pages, err, blockIdx.x, gridDim.x, blockIdx.y,
                                          gridDim.y, blockIdx.z, smem_raw);
 }
 
-template <int D>
+template <int D, int WARPS>
 int launch_decode(dim3 grid, cudaStream_t stream, const __nv_bfloat16* q, int q_row_stride, const __nv_bfloat16* kpages,
                   const __nv_bfloat16* vpages, const int* block_table, int max_blocks, const int* positions,
                   __nv_bfloat16* out, float* partial, int* counters, int H, int Hkv, float scale, int window, int n_pages,
                   int* err) {
-    const size_t smem = attn_decode_smem_bytes<D, DEC_WARPS>();
+    const size_t smem = attn_decode_smem_bytes<D, WARPS>();
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    vm_launch_pdl(attn_decode_kernel<D>, grid, dim3(DEC_WARPS * 32), smem, stream, q, q_row_stride, kpages, vpages, block_table,
+    vm_launch_pdl(attn_decode_kernel<D, WARPS>, grid, dim3(WARPS * 32), smem, stream, q, q_row_stride, kpages, vpages, block_table,
                   max_blocks, positions, out, partial, counters, H, Hkv, scale * 1.4426950408889634f, window, n_pages, err);
     return vm_launch_status();
 }
@@ -66,10 +69,16 @@ VM_API int vm_attention_decode_bf16(const void* q, int q_row_stride, const void*
     const int G = H / Hkv;
     dim3 grid(n_splits, Hkv * ((G + DEC_ROWS - 1) / DEC_ROWS), B);
     const __nv_bfloat16 *qq = (const __nv_bfloat16*)q, *kk = (const __nv_bfloat16*)kpages, *vv = (const __nv_bfloat16*)vpages;
+    // one split and a CTA per SM at most: ten warps per CTA, if their pages fit into shared memory
+    const bool wide = n_splits == 1 && (long long)grid.y * grid.z <= DEC_WIDE_MAX_CTAS;
 #define VM_DEC_CASE(DD)                                                                                                \
     case DD:                                                                                                           \
-        return launch_decode<DD>(grid, stream, qq, q_row_stride, kk, vv, block_table, max_blocks, positions,             \
-                                 (__nv_bfloat16*)out, partial, counters, H, Hkv, scale, window, n_pages, err);
+        if (wide && attn_decode_smem_bytes<DD, DEC_WARPS_WIDE>() <= 227 * 1024)                                        \
+            return launch_decode<DD, DEC_WARPS_WIDE>(grid, stream, qq, q_row_stride, kk, vv, block_table, max_blocks,  \
+                                                     positions, (__nv_bfloat16*)out, partial, counters, H, Hkv, scale, \
+                                                     window, n_pages, err);                                            \
+        return launch_decode<DD, DEC_WARPS>(grid, stream, qq, q_row_stride, kk, vv, block_table, max_blocks, positions, \
+                                            (__nv_bfloat16*)out, partial, counters, H, Hkv, scale, window, n_pages, err);
     switch (D) {
         VM_DEC_CASE(16) VM_DEC_CASE(32) VM_DEC_CASE(48) VM_DEC_CASE(64)
         VM_DEC_CASE(80) VM_DEC_CASE(96) VM_DEC_CASE(112) VM_DEC_CASE(128)

@@ -163,6 +163,25 @@ attn_decode_body(const __nv_bfloat16* __restrict__ q, int q_row_stride, const __
         if (t4 == 0) { ra[D] = m_a; ra[D + 1] = l_a; rb[D] = m_b; rb[D + 1] = l_b; }
     }
     __syncthreads();
+    if (n_splits == 1) {
+        // one CTA holds all keys of the sequence: the warps' rows are joined straight into the output
+        for (int i = tid; i < ng * D; i += DEC_WARPS * 32) {
+            const int r = i / D, d = i - r * D;
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, res[((size_t)w * DEC_ROWS + r) * RW + D]);
+            float acc = 0.f, L = 0.f;
+#pragma unroll
+            for (int w = 0; w < DEC_WARPS; ++w) {
+                const float* rr = res + ((size_t)w * DEC_ROWS + r) * RW;
+                const float f = (rr[D] == -INFINITY) ? 0.f : exp2f(rr[D] - M);
+                acc += f * rr[d]; L += f * rr[D + 1];
+            }
+            out[((size_t)b * H + (h0 + r)) * D + d] = __float2bfloat16_rn(acc / L);
+        }
+        __syncthreads();                                   // shared memory may be reused for another item
+        return;
+    }
     // partial[b, h, split, :] = (o[D], m, l), merged over the warps (max and sums in base 2)
     for (int i = tid; i < ng * D; i += DEC_WARPS * 32) {
         const int r = i / D, d = i - r * D;

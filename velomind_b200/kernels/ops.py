@@ -159,10 +159,15 @@ def decode_counters(device) -> torch.Tensor:
     return _decode_counters[key]
 
 
+DECODE_ONE_CTA_BLOCKS = 16     # block tables up to this wide (1,024 tokens): at most two rounds of pages for ten warps
+
+
 def decode_splits(B: int, Hkv: int, G: int, table_width: int) -> int:
     """How many CTAs share the keys of one (sequence, kv head): enough to fill the GPU, a function of the
     step's SHAPE only (so that a captured launch stays valid as sequences grow)."""
     groups = B * Hkv * (-(-G // 16))          # a CTA serves up to 16 query heads of one kv head
+    if groups <= 148 and table_width <= DECODE_ONE_CTA_BLOCKS:
+        return 1                              # short sequences: one CTA of ten warps holds all pages, nothing is merged across CTAs
     want = -(-148 // groups)                  # about one CTA per SM ...
     table_width = max(1, table_width // 4)    # ... and at least a page per warp of a CTA (the width bounds the pages)
     return max(1, min(want, MAX_DECODE_SPLITS, table_width))
