@@ -50,10 +50,15 @@ __device__ __forceinline__ ArgBest better(ArgBest a, ArgBest b) {   // larger va
     return a;
 }
 
+// CACHED: the row's unnormalised probabilities are computed once and kept in dynamic shared memory (V floats; NaN
+// logits are marked by -1), so the passes of the nucleus search read shared memory; otherwise every pass recomputes them
+// from the logits in global memory (vocabularies too large for shared memory).
+template <bool CACHED>
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, long long row_stride, int V, const float* __restrict__ temperature,
               const float* __restrict__ top_p, const long long* __restrict__ seed, const long long* __restrict__ stream_id,
               const long long* __restrict__ step, int* __restrict__ out) {
+    extern __shared__ __align__(16) float sraw[];
     __shared__ double redd[32];
     __shared__ float redv[32];
     __shared__ int redi[32];
@@ -64,9 +69,32 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int V, con
     const float temp = temperature ? temperature[row] : 0.f;
     const float tp = top_p ? top_p[row] : 1.f;
 
-    // ---- maximum (NaN skipped) with its first index
+    // ---- maximum (NaN skipped) with its first index; four values per load where the row is 16-byte aligned
     ArgBest best{-INFINITY, -1};
-    for (int i = tid; i < V; i += blockDim.x) {
+    int scalar_from = 0;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        const int V4 = V >> 2;
+        const float4* x4 = reinterpret_cast<const float4*>(x);
+        constexpr int U = 4;
+        for (int i0 = tid; i0 < V4; i0 += SAMPLE_THREADS * U) {
+            float4 v[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int i = i0 + u * SAMPLE_THREADS;
+                v[u] = (i < V4) ? x4[i] : make_float4(NAN, NAN, NAN, NAN);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int i = 4 * (i0 + u * SAMPLE_THREADS);
+                if (v[u].x == v[u].x) best = better(best, ArgBest{v[u].x, i});
+                if (v[u].y == v[u].y) best = better(best, ArgBest{v[u].y, i + 1});
+                if (v[u].z == v[u].z) best = better(best, ArgBest{v[u].z, i + 2});
+                if (v[u].w == v[u].w) best = better(best, ArgBest{v[u].w, i + 3});
+            }
+        }
+        scalar_from = V4 << 2;
+    }
+    for (int i = scalar_from + tid; i < V; i += blockDim.x) {
         const float v = x[i];
         if (v != v) continue;
         best = better(best, ArgBest{v, i});
@@ -99,17 +127,26 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int V, con
         max_v = fm;
     }
     const float inv_t = 1.0f / temp;
-    auto prob_raw = [&](int i) -> float {
+    // unnormalised probability of token i, or a negative number for a NaN logit
+    auto raw_of = [&](int i) -> float {
         const float v = x[i];
-        return (v != v) ? 0.f : expf((v - max_v) * inv_t);
+        return (v != v) ? -1.f : expf((v - max_v) * inv_t);
     };
+    auto raw = [&](int i) -> float { return CACHED ? sraw[i] : raw_of(i); };
     double part = 0.0;
-    for (int i = tid; i < V; i += blockDim.x) part += (double)prob_raw(i);
-    const double total = block_sum_d(part, redd);
+    for (int i = tid; i < V; i += blockDim.x) {
+        const float r = raw_of(i);
+        if (CACHED) sraw[i] = r;
+        part += (double)(r < 0.f ? 0.f : r);
+    }
+    const double total = block_sum_d(part, redd);          // (its barriers also publish the cached values)
     const float inv_sum = (float)(1.0 / total);
-    auto prob = [&](int i) -> float { return prob_raw(i) * inv_sum; };
+    // normalised probability; negative for a NaN logit (never in the nucleus)
+    auto prob = [&](int i) -> float { const float r = raw(i); return r < 0.f ? -1.f : r * inv_sum; };
 
     // ---- nucleus threshold: the largest tau with sum{p_i >= tau} >= top_p (bisection on the float bits)
+    // Search: four-way instead of two-way, three thresholds per pass over the probabilities (16 passes, not 31; measured
+    // at 49,152 tokens: 7 and 15 thresholds per pass are no faster), and only what lies between the thresholds is summed again.
     float tau = 0.f;
     if (tp < 1.0f) {
         float pmax = 0.f;
@@ -121,32 +158,78 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int V, con
         pmax = 0.f;
         for (int k = 0; k < (int)(blockDim.x >> 5); ++k) pmax = fmaxf(pmax, redv[k]);
         uint32_t lo = 0u, hi = __float_as_uint(pmax) + 1u;   // cond(lo) holds or tau stays 0; cond(hi) fails
+        constexpr int WAYS = 3;
+        double* many = sums;                                  // [warps][WAYS] partial sums (sums[] is free until the walk)
+        double above = 0.0;                                   // the mass of p >= hi: known from the pass that lowered hi
         while (hi - lo > 1u) {
-            const uint32_t mid = lo + (hi - lo) / 2u;
-            const float th = __uint_as_float(mid);
-            double s = 0.0;
-            for (int i = tid; i < V; i += blockDim.x) { const float p = prob(i); if (p >= th) s += (double)p; }
-            s = block_sum_d(s, redd);
-            if (s >= (double)tp) lo = mid; else hi = mid;
+            const uint32_t stepw = (hi - lo + WAYS) / (WAYS + 1);      // thresholds lo + j * stepw, j = 1..WAYS, below hi
+            float th[WAYS];
+            double sj[WAYS];
+#pragma unroll
+            for (int j = 0; j < WAYS; ++j) {
+                const unsigned long long t = (unsigned long long)lo + (unsigned long long)(j + 1) * stepw;
+                th[j] = (t < (unsigned long long)hi) ? __uint_as_float((uint32_t)t) : INFINITY;
+                sj[j] = 0.0;
+            }
+            const float f_lo = __uint_as_float(lo + stepw), f_hi = __uint_as_float(hi);
+            for (int i = tid; i < V; i += blockDim.x) {
+                const float p = prob(i);
+                if (p >= f_lo && p < f_hi) {                 // only what lies between the thresholds is summed again
+                    const double pd = (double)p;
+#pragma unroll
+                    for (int j = 0; j < WAYS; ++j) if (p >= th[j]) sj[j] += pd;
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < WAYS; ++j) sj[j] = warp_sum_d(sj[j]);
+            __syncthreads();
+            if (lane == 0) {
+#pragma unroll
+                for (int j = 0; j < WAYS; ++j) many[warp * WAYS + j] = sj[j];
+            }
+            __syncthreads();
+            if (warp == 0 && lane < WAYS) {                   // one thread per threshold joins the warps, in warp order
+                double sum = 0.0;
+                for (int k = 0; k < (int)(blockDim.x >> 5); ++k) sum += many[k * WAYS + lane];
+                redd[lane] = sum;
+            }
+            __syncthreads();
+            uint32_t new_lo = lo, new_hi = hi;
+            double new_above = above;
+#pragma unroll
+            for (int j = 0; j < WAYS; ++j) {
+                const unsigned long long t = (unsigned long long)lo + (unsigned long long)(j + 1) * stepw;
+                if (t < (unsigned long long)new_hi) {
+                    const double sum = above + redd[j];       // mass of p >= t: what lies above hi, plus [t, hi)
+                    if (sum >= (double)tp) new_lo = (uint32_t)t; else { new_hi = (uint32_t)t; new_above = sum; }
+                }
+            }
+            lo = new_lo; hi = new_hi; above = new_above;
         }
         tau = __uint_as_float(lo);
+        __syncthreads();
     }
 
     // ---- mass of the nucleus and the walk in index order
     const int chunk = (V + blockDim.x - 1) / blockDim.x;
     const int i0 = min(V, tid * chunk), i1 = min(V, i0 + chunk);
     double mine = 0.0;
-    for (int i = i0; i < i1; ++i) { const float v = x[i]; const float p = prob(i); if (v == v && p >= tau) mine += (double)p; }
-    sums[tid] = mine;
-    __syncthreads();
-    if (tid == 0) {
-        double acc = 0.0;
-        for (int k = 0; k < (int)blockDim.x; ++k) { const double s = sums[k]; sums[k] = acc; acc += s; }
-        redd[0] = acc;          // mass
-        s_choice = 0x7fffffff;
+    for (int i = i0; i < i1; ++i) { const float p = prob(i); if (p >= 0.f && p >= tau) mine += (double)p; }
+    // exclusive running sums over the threads' chunks: a scan inside each warp, then over the warps' totals
+    double incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const double up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
     }
     __syncthreads();
-    const double mass = redd[0];
+    if (lane == 31) redd[warp] = incl;
+    if (tid == 0) s_choice = 0x7fffffff;
+    __syncthreads();
+    double offset = 0.0, mass = 0.0;
+    for (int k = 0; k < (int)(blockDim.x >> 5); ++k) { const double t = redd[k]; if (k < warp) offset += t; mass += t; }
+    sums[tid] = offset + incl - mine;
+    __syncthreads();
     uint32_t c[4];
     const unsigned long long st = (unsigned long long)(step ? step[row] : 0), sid = (unsigned long long)(stream_id ? stream_id[row] : 0);
     const unsigned long long sd = (unsigned long long)(seed ? seed[row] : 0);
@@ -159,8 +242,8 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int V, con
     if (before <= r) {
         double acc = before;
         for (int i = i0; i < i1; ++i) {
-            const float v = x[i]; const float p = prob(i);
-            if (v == v && p >= tau) {
+            const float p = prob(i);
+            if (p >= 0.f && p >= tau) {
                 acc += (double)p;
                 if (acc >= r) { atomicMin(&s_choice, i); break; }
             }
@@ -171,18 +254,31 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int V, con
         int choice = s_choice;
         if (choice == 0x7fffffff) {       // rounding left the running sum short of r: the last member
             choice = -1;
-            for (int i = V - 1; i >= 0; --i) { const float v = x[i]; if (v == v && prob(i) >= tau) { choice = i; break; } }
+            for (int i = V - 1; i >= 0; --i) { const float p = prob(i); if (p >= 0.f && p >= tau) { choice = i; break; } }
         }
         out[row] = choice;
     }
 }
+
+constexpr int SAMPLE_CACHE_LIMIT = 200 * 1024;      // bytes of dynamic shared memory for a row's probabilities
 
 VM_API int vm_sample(const float* logits, long long row_stride, int R, int V, const float* temperature,
                      const float* top_p, const long long* seed, const long long* stream_id, const long long* step,
                      int* out, cudaStream_t stream) {
     if (R <= 0) return 0;
     if (V <= 0) return VM_ERR_BAD_ARG;
-    sample_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(logits, row_stride, V, temperature, top_p, seed, stream_id, step, out);
+    const size_t cache = (size_t)V * sizeof(float);
+    if (cache <= SAMPLE_CACHE_LIMIT) {
+        static bool configured = false;
+        if (!configured) {
+            cudaError_t e = cudaFuncSetAttribute(sample_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SAMPLE_CACHE_LIMIT);
+            if (e != cudaSuccess) return (int)e;
+            configured = true;
+        }
+        sample_kernel<true><<<R, SAMPLE_THREADS, cache, stream>>>(logits, row_stride, V, temperature, top_p, seed, stream_id, step, out);
+    } else {
+        sample_kernel<false><<<R, SAMPLE_THREADS, 0, stream>>>(logits, row_stride, V, temperature, top_p, seed, stream_id, step, out);
+    }
     return vm_launch_status();
 }
 

@@ -137,6 +137,8 @@ def main(argv=None) -> int:
     ap.add_argument("--groups", type=int, default=4, help="attn_prefill: warp groups sharing a tile's key blocks")
     ap.add_argument("--layers", type=int, default=6, help="decode_cluster: layers of the random model")
     ap.add_argument("--clusters", type=int, default=0, help="decode_cluster: deal the batch out to at most this many clusters")
+    ap.add_argument("--temp", type=float, default=0.0, help="sample: temperature (0: greedy)")
+    ap.add_argument("--top-p", type=float, default=0.9, help="sample: nucleus mass, with --temp")
     ap.add_argument("--repeat", type=int, default=50)
     ap.add_argument("--no-graph", action="store_true")
     a = ap.parse_args(argv)
@@ -237,9 +239,16 @@ def main(argv=None) -> int:
         fn = lambda: ops.add_rmsnorm(h, None, nw, 1e-5, out)
         bytes_read = M * hid * 4
     else:
-        logits = torch.randn(M, V, device=dev)
+        logits = torch.randn(M, V, device=dev) * 3.0
         out = torch.empty(M, dtype=torch.int32, device=dev)
-        fn = lambda: ops.sample(logits, None, None, None, None, None, out)
+        if a.temp > 0:
+            temps = torch.full((M,), a.temp, device=dev)
+            tps = torch.full((M,), a.top_p, device=dev)
+            seeds = torch.full((M,), 42, dtype=torch.int64, device=dev)
+            ids = torch.arange(M, dtype=torch.int64, device=dev)
+            fn = lambda: ops.sample(logits, temps, tps, seeds, ids, ids, out)
+        else:
+            fn = lambda: ops.sample(logits, None, None, None, None, None, out)
         bytes_read = M * V * 4
     us = _time(fn, a.repeat, graph=not a.no_graph)
     res = {"kernel": a.kernel, "rows": M, "us_per_launch": round(us, 3), "bytes_read": bytes_read,
