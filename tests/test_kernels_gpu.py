@@ -37,8 +37,9 @@ def test_embed_gather(table_dtype):
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-6), (torch.bfloat16, 2e-2)])
 @pytest.mark.parametrize("hid", [200, 576, 4100])
-def test_add_rmsnorm(dtype, tol, hid):
-    T, eps = 19, 3e-6
+@pytest.mark.parametrize("T", [19, 131])          # few rows: a block per row; many rows (bfloat16): a warp per row, four values per load
+def test_add_rmsnorm(dtype, tol, hid, T):
+    eps = 3e-6
     h = torch.randn(T, hid, generator=_gen(2)) * 3
     delta = torch.randn(T, hid, generator=_gen(3)).to(dtype)
     w = 1 + 0.2 * torch.randn(hid, generator=_gen(4))
@@ -62,8 +63,9 @@ def test_add_rmsnorm(dtype, tol, hid):
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-6), (torch.bfloat16, 1e-2)])
-def test_swiglu_residual_convert(dtype, tol):
-    T, I = 23, 100
+@pytest.mark.parametrize("I", [100, 200])          # 200: the bfloat16 kernel with eight values per load
+def test_swiglu_residual_convert(dtype, tol, I):
+    T = 23
     gu = (torch.randn(T, 2 * I, generator=_gen(5)) * 2).to(dtype)
     out = torch.empty(T, I, dtype=dtype, device=DEV)
     ops().swiglu(gu.to(DEV), out)

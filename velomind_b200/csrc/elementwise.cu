@@ -69,12 +69,62 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ 
     }
 }
 
+// The same for bfloat16 activations and hid % 4 == 0, four values per load and store; one WARP per output row (no
+// block-wide barrier), the row's sums kept in the warp's shared memory between the two passes.
+constexpr int NORM_VEC_WARPS = 4;
+__global__ void __launch_bounds__(NORM_VEC_WARPS * 32)
+add_rmsnorm_bf16_vec_kernel(float* __restrict__ h, const __nv_bfloat16* __restrict__ delta, const float* __restrict__ w,
+                            __nv_bfloat16* __restrict__ out, const int* __restrict__ rows, int n_out, int hid, float eps) {
+    extern __shared__ __align__(16) float vrow[];        // [warps][hid]
+    vm_pdl_launch_dependents();
+    vm_pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = blockIdx.x * NORM_VEC_WARPS + warp;
+    if (r >= n_out) return;
+    const int src = rows ? rows[r] : r;
+    float4* hrow = reinterpret_cast<float4*>(h + (size_t)src * hid);
+    const uint2* drow = delta ? reinterpret_cast<const uint2*>(delta + (size_t)src * hid) : nullptr;
+    float4* mine = reinterpret_cast<float4*>(vrow + (size_t)warp * hid);
+    const int n4 = hid >> 2;
+    float ss = 0.f;
+    for (int i = lane; i < n4; i += 32) {
+        float4 v = hrow[i];
+        if (drow) {
+            const uint2 d = drow[i];
+            const __nv_bfloat162 d01 = *reinterpret_cast<const __nv_bfloat162*>(&d.x), d23 = *reinterpret_cast<const __nv_bfloat162*>(&d.y);
+            v.x += __low2float(d01); v.y += __high2float(d01); v.z += __low2float(d23); v.w += __high2float(d23);
+            if (!rows) hrow[i] = v;
+        }
+        mine[i] = v;
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    ss = vm_warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)hid + eps);
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+    uint2* orow = reinterpret_cast<uint2*>(out + (size_t)r * hid);
+    for (int i = lane; i < n4; i += 32) {
+        const float4 v = mine[i], ww = w4[i];
+        const __nv_bfloat162 o01 = __floats2bfloat162_rn(v.x * inv * ww.x, v.y * inv * ww.y);
+        const __nv_bfloat162 o23 = __floats2bfloat162_rn(v.z * inv * ww.z, v.w * inv * ww.w);
+        uint2 o;
+        o.x = *reinterpret_cast<const unsigned*>(&o01); o.y = *reinterpret_cast<const unsigned*>(&o23);
+        orow[i] = o;
+    }
+}
+
 VM_API int vm_add_rmsnorm(float* h, const void* delta, const float* w, void* out, const int* rows, int n_out,
                           int hid, float eps, int act_dtype, cudaStream_t stream) {
     if (n_out <= 0) return 0;
     const int threads = hid >= 1024 ? 256 : 128;
     const size_t smem = (size_t)hid * sizeof(float);
     if (smem > 200 * 1024) return VM_ERR_UNSUPPORTED;
+    if (act_dtype == VM_BF16 && hid % 4 == 0 && smem * NORM_VEC_WARPS <= 48 * 1024 && n_out >= 64 &&
+        ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(w)) & 15) == 0 &&
+        ((reinterpret_cast<uintptr_t>(delta) | reinterpret_cast<uintptr_t>(out)) & 7) == 0) {
+        vm_launch_pdl(add_rmsnorm_bf16_vec_kernel, dim3((n_out + NORM_VEC_WARPS - 1) / NORM_VEC_WARPS), dim3(NORM_VEC_WARPS * 32),
+                      smem * NORM_VEC_WARPS, stream, h, (const __nv_bfloat16*)delta, w, (__nv_bfloat16*)out, rows, n_out, hid, eps);
+        return vm_launch_status();
+    }
     if (act_dtype == VM_F32) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         vm_launch_pdl(add_rmsnorm_kernel<float>, dim3(n_out), dim3(threads), smem, stream, h, (const float*)delta, w, (float*)out, rows, hid, eps);
@@ -120,8 +170,34 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
     }
 }
 
+// bfloat16, I % 8 == 0: eight values per load and store
+__global__ void swiglu_bf16_vec_kernel(const uint4* __restrict__ gu, uint4* __restrict__ out, size_t n8, int I8) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n8; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / I8;
+        const int i = (int)(idx - t * I8);
+        const uint4 g4 = gu[t * 2 * I8 + i], u4 = gu[t * 2 * I8 + I8 + i];
+        const unsigned gw[4] = {g4.x, g4.y, g4.z, g4.w}, uw[4] = {u4.x, u4.y, u4.z, u4.w};
+        unsigned ow[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(&gw[k]), u2 = *reinterpret_cast<const __nv_bfloat162*>(&uw[k]);
+            const float ga = __low2float(g2), gb = __high2float(g2);
+            const float sa = 1.0f / (1.0f + expf(-ga)), sb = 1.0f / (1.0f + expf(-gb));
+            const __nv_bfloat162 o2 = __floats2bfloat162_rn((sa * ga) * __low2float(u2), (sb * gb) * __high2float(u2));
+            ow[k] = *reinterpret_cast<const unsigned*>(&o2);
+        }
+        out[idx] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+}
+
 VM_API int vm_swiglu(const void* gate_up, void* out, int T, int I, int act_dtype, cudaStream_t stream) {
     if (T <= 0) return 0;
+    if (act_dtype == VM_BF16 && I % 8 == 0 && ((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+        const size_t n8 = (size_t)T * (I / 8);
+        const size_t want8 = (n8 + 255) / 256;
+        swiglu_bf16_vec_kernel<<<(int)(want8 < 148 * 16 ? want8 : 148 * 16), 256, 0, stream>>>((const uint4*)gate_up, (uint4*)out, n8, I / 8);
+        return vm_launch_status();
+    }
     const size_t n = (size_t)T * I;
     const int threads = 256;
     const size_t want = (n + threads - 1) / threads;
