@@ -162,7 +162,7 @@ def _attention_case(H, Hkv, D, lens_before, new, window, seed, spike=True):
     return Q, K, V
 
 
-def _run_attention(kind, dtype, H, Hkv, D, lens_before, new, window, seed=0):
+def _run_attention(kind, dtype, H, Hkv, D, lens_before, new, window, seed=0, groups=1):
     o = ops()
     Q, K, V = _attention_case(H, Hkv, D, lens_before, new, window, seed)
     scale = 1.0 / math.sqrt(D)
@@ -196,6 +196,10 @@ def _run_attention(kind, dtype, H, Hkv, D, lens_before, new, window, seed=0):
         n_tiles = sum(-(-n // 64) for n in new)
         o.attention_prefill_bf16(d(qkv), stride, d(kp), d(vp), d(table), d(positions), d(cu), n_tiles, out, H, Hkv, D, scale,
                                  window, err)
+    elif kind == "prefill_tc":
+        n_tiles = sum(-(-n // 128) for n in new)
+        o.attention_prefill_tc_bf16(d(qkv), stride, d(kp), d(vp), d(table), d(positions), d(cu), n_tiles, out, H, Hkv, D, scale,
+                                    window, err, groups)
     else:
         B = len(new)
         n_splits = o.decode_splits(B, Hkv, H // Hkv, table.shape[1])
@@ -228,6 +232,17 @@ def test_attention_generic(dtype, tol, H, Hkv, D, window):
 def test_attention_prefill_bf16(H, Hkv, D, window):
     # whole prompts of awkward lengths, a continued sequence (chunked prefill), single tokens
     got, want = _run_attention("prefill", torch.bfloat16, H, Hkv, D, [0, 130, 63, 0, 200, 0], [200, 67, 2, 1, 1, 64], window)
+    assert np.isfinite(got).all() and np.abs(got - want).max() <= 2e-2
+
+
+@pytest.mark.parametrize("H,Hkv", [(9, 3), (4, 4), (5, 1)])
+@pytest.mark.parametrize("window", [0, 70, 64, 200])
+@pytest.mark.parametrize("groups", [1, 2, 4])
+def test_attention_prefill_tcgen05(H, Hkv, window, groups):
+    """The tensor-memory kernel (head size 64): prompts of awkward lengths around its 128-token tiles and 64-key
+    blocks, a continued sequence, single tokens, one long prompt."""
+    got, want = _run_attention("prefill_tc", torch.bfloat16, H, Hkv, 64, [0, 130, 63, 0, 200, 0, 0, 17],
+                               [200, 67, 2, 1, 1, 128, 129, 600], window, groups=groups)
     assert np.isfinite(got).all() and np.abs(got - want).max() <= 2e-2
 
 

@@ -15,7 +15,7 @@ import torch
 
 from . import ops
 
-KERNELS = ["qkv_rope", "out_residual", "gate_up_swiglu", "down_residual", "head", "attn_decode", "attn_prefill",
+KERNELS = ["qkv_rope", "out_residual", "gate_up_swiglu", "down_residual", "head", "attn_decode", "attn_prefill", "attn_prefill_tc",
            "add_rmsnorm", "sample", "tc_linear", "tc_residual", "tc_swiglu", "cublas_linear", "decode_cluster"]
 
 
@@ -166,7 +166,7 @@ def main(argv=None) -> int:
     n_pages = M * width
     inv = torch.ones(D // 2, device=dev)
     bytes_read = 0
-    if a.kernel in ("qkv_rope", "attn_decode", "attn_prefill"):
+    if a.kernel in ("qkv_rope", "attn_decode", "attn_prefill", "attn_prefill_tc"):
         kp = torch.randn(n_pages, Hkv, 64, D, device=dev).to(bf)
         vp = torch.randn_like(kp)
     if a.kernel == "qkv_rope":
@@ -202,7 +202,7 @@ def main(argv=None) -> int:
         fn = lambda: ops.attention_decode_bf16(q, H * D, kp, vp, table, pos, out, partial, ops.decode_counters(dev), H, Hkv, D,
                                                splits, 1.0 / math.sqrt(D))
         bytes_read = M * (a.ctx + 1) * 2 * Hkv * D * 2
-    elif a.kernel == "attn_prefill":
+    elif a.kernel in ("attn_prefill", "attn_prefill_tc"):
         T = a.tokens
         width = 1
         while width < T // 64 + 1:
@@ -214,8 +214,13 @@ def main(argv=None) -> int:
         positions = torch.arange(T, dtype=torch.int32, device=dev)
         cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
         out = torch.empty(T, H * D, device=dev, dtype=bf)
-        fn = lambda: ops.attention_prefill_bf16(qkv, (H + 2 * Hkv) * D, kp, vp, table, positions, cu, -(-T // 64), out, H, Hkv, D,
-                                                1.0 / math.sqrt(D), groups=a.groups)
+        if a.kernel == "attn_prefill_tc":
+            err = torch.zeros(1, dtype=torch.int32, device=dev)
+            fn = lambda: ops.attention_prefill_tc_bf16(qkv, (H + 2 * Hkv) * D, kp, vp, table, positions, cu, -(-T // 128), out, H, Hkv,
+                                                       D, 1.0 / math.sqrt(D), 0, err, a.groups)
+        else:
+            fn = lambda: ops.attention_prefill_bf16(qkv, (H + 2 * Hkv) * D, kp, vp, table, positions, cu, -(-T // 64), out, H, Hkv, D,
+                                                    1.0 / math.sqrt(D), groups=a.groups)
         bytes_read = 0
     elif a.kernel in ("tc_linear", "tc_residual", "tc_swiglu", "cublas_linear"):
         T, N, K = a.tokens, a.n or 2 * I, a.k or hid

@@ -146,6 +146,23 @@ def attention_prefill_bf16(q: torch.Tensor, q_row_stride: int, k_pages: torch.Te
            "attention_prefill_bf16")
 
 
+def attention_prefill_tc_bf16(q: torch.Tensor, q_row_stride: int, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                              block_table: torch.Tensor, positions: torch.Tensor, cu_tokens: torch.Tensor, n_tiles: int,
+                              out: torch.Tensor, H: int, Hkv: int, D: int, scale: float, window: int = 0,
+                              err: Optional[torch.Tensor] = None, groups: int = 1) -> None:
+    """The same attention on tcgen05 (tensor-memory accumulators), head size 64 only: a CTA per 128 new tokens and
+    head.  n_tiles = sum of ceil(new tokens / 128); groups (1, 2, 4): groups of 128 threads that take a tile's key
+    blocks in turn."""
+    B = cu_tokens.shape[0] - 1
+    _check(library().vm_attention_prefill_tc_bf16(_ptr(q), _c_int(q_row_stride), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+                                                  _c_int(block_table.shape[1]), _ptr(positions), _ptr(cu_tokens), _c_int(B),
+                                                  _c_int(n_tiles), _ptr(out), _c_int(H), _c_int(Hkv), _c_int(D), _c_f(scale),
+                                                  _c_int(window), _c_int(k_pages.shape[0]), _ptr(err), _c_int(groups), _stream()),
+           "attention_prefill_tc_bf16")
+
+
+TC_ATTENTION = True            # head size 64: prefill attention on tcgen05 instead of mma.sync
+
 _decode_counters = {}
 DECODE_COUNTERS = 1 << 16
 MAX_DECODE_SPLITS = 16
@@ -203,15 +220,25 @@ def attention(ctx, q: torch.Tensor, q_row_stride: int, k_pages: torch.Tensor, v_
         ctx.ws.give(partial)
     elif fast:      # the tile count follows from the sequences' new-token counts, which are part of a recorded step's shape
         lens = ctx.host_cu_tokens[1:] - ctx.host_cu_tokens[:-1]
-        n_tiles = int(((lens + 63) // 64).sum())
         # the longest chain of key blocks a tile walks, and how many CTAs there are to hide it behind
         most_blocks = (min(ctx.max_ctx_len, window + 64) if window > 0 else ctx.max_ctx_len) // 64 + 1
+        if TC_ATTENTION and D == 64 and err_ok(ctx):
+            attention_prefill_tc_bf16(q, q_row_stride, k_pages, v_pages, block_table, ctx.positions, ctx.cu_tokens,
+                                      int(((lens + 127) // 128).sum()), out, H, Hkv, D, scale, window, ctx.err,
+                                      4 if most_blocks >= 16 else (2 if most_blocks >= 4 else 1))
+            return
+        n_tiles = int(((lens + 63) // 64).sum())
         groups = 2 if most_blocks >= 8 else 1      # measured at 9 heads of 64: 2 groups 39 us, 1 group 43 us, 4 groups 46 us (2,048 tokens)
         attention_prefill_bf16(q, q_row_stride, k_pages, v_pages, block_table, ctx.positions, ctx.cu_tokens, n_tiles, out,
                                H, Hkv, D, scale, window, ctx.err, groups)
     else:
         attention_generic(q, q_row_stride, k_pages, v_pages, block_table, ctx.positions, ctx.seq_of_token, out,
                           H, Hkv, D, scale, window, ctx.err)
+
+
+def err_ok(ctx) -> bool:
+    """True if the step has an error word for kernels that may give up a wait."""
+    return getattr(ctx, "err", None) is not None
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
