@@ -278,3 +278,23 @@ def test_cluster_decode_kernel_many_rows_and_far_keys(model_folders):
             row = ref[len(p) - 1 + j]
             assert row[tok] >= row.max() - 2 * TOL["bfloat16"] * scale, (len(p), j, tok, int(row.argmax()))
     assert engine.cache.slots.held_count == 0
+
+
+def test_long_prompt_takes_the_tcgen05_attention(model_folders):
+    """A prompt long enough for the tensor-memory attention kernel (head size 64, more than 1,280 keys), alone and next
+    to a short one, then a few tokens one by one; logits at places spread over the prompt against the plain model."""
+    from velomind_b200.kernels import ops as O
+    folder = model_folders["tiny_c"]
+    requests = S.make_requests(CONFIGS["tiny_c"]["vocab_size"], (1500, 40), seed=13)
+    plain = S.plain_logits(folder, requests)
+    a, b = requests["r0"], requests["r1"]
+    want_a = [0, 63, 64, 127, 128, 700, 1279, 1280, 1400, 1494]
+    steps = [{"step": 0, "entries": [{"id": "r0", "tokens": a[:1495], "want": want_a}, {"id": "r1", "tokens": b, "want": [39]}], "end": ["r1"]}]
+    for j in range(1495, 1500):
+        steps.append({"step": len(steps), "entries": [{"id": "r0", "tokens": [a[j]], "want": [0]}], "end": ["r0"] if j == 1499 else []})
+    before = O.tc_attention_calls
+    engine = _engine(folder, "bfloat16", max_tokens=2048)
+    got = S.run_steps_in_process(engine, steps)
+    engine.raise_if_error()
+    assert O.tc_attention_calls > before
+    _compare(got, S.expected_rows(steps, requests, plain), TOL["bfloat16"])

@@ -237,7 +237,7 @@ def test_attention_prefill_bf16(H, Hkv, D, window):
 
 @pytest.mark.parametrize("H,Hkv", [(9, 3), (4, 4), (5, 1)])
 @pytest.mark.parametrize("window", [0, 70, 64, 200])
-@pytest.mark.parametrize("groups", [1, 2, 4])
+@pytest.mark.parametrize("groups", [1, 2, 3, 4])
 def test_attention_prefill_tcgen05(H, Hkv, window, groups):
     """The tensor-memory kernel (head size 64): prompts of awkward lengths around its 128-token tiles and 64-key
     blocks, a continued sequence, single tokens, one long prompt."""

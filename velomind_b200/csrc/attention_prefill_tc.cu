@@ -18,9 +18,9 @@
 //                  output registers, which it rescales itself when the maximum moves
 // The softmax, not the products, is what a tile costs (64 x 128 exponentials and as many roundings per block go through
 // one SM's special-function units), and the last tiles of a long prompt see the most keys.  So a tile may belong to a
-// CLUSTER of NC CTAs (1, 2 or 4) on NC SMs: CTA c takes the tile's key blocks c, c + NC, ..., and at the end the CTAs
-// exchange their rows (sums, maximum, denominator) through distributed shared memory, each joining and storing 128 / NC
-// of the tile's rows.
+// CLUSTER of NC CTAs (1 to 4) on NC SMs: CTA c takes the tile's key blocks c, c + NC, ..., and at the end the CTAs
+// exchange their rows (sums, maximum, denominator) through distributed shared memory, each joining and storing every
+// NC-th row of the tile.
 // Q, K and V reach shared memory through cp.async with the swizzle applied to the destination (the next page is in
 // flight while this one is worked on).  The one mbarrier wait (completion of the MMAs, signalled by tcgen05.commit)
 // is bounded: when it gives up, the CTA raises error word 4, drains its copies, frees its tensor memory and returns.
@@ -36,7 +36,7 @@ constexpr int TA_Q_BYTES = TA_BM * 128, TA_KV_BYTES = TA_BN * 128, TA_P_BYTES = 
 constexpr int TA_WORK_BYTES = 4 * TA_KV_BYTES + TA_P_BYTES;                  // K[2], V[2], P
 constexpr int TA_SMEM = TA_Q_BYTES + TA_WORK_BYTES + 128;                    // + barrier, tensor-memory slot, flag
 constexpr int TA_RW = TA_D + 4;                                              // floats of an exchanged row: sums, maximum, denominator, padding
-static_assert(TA_RW * 4 * TA_BM <= TA_WORK_BYTES, "the exchanged rows must fit into the K, V and P buffers");
+static_assert(TA_RW * 4 * (TA_BM + 3) <= TA_WORK_BYTES, "the exchanged rows must fit into the K, V and P buffers");
 
 __device__ __forceinline__ uint32_t ta_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void ta_cp_async16(uint32_t dst, const void* gmem, bool pred) {
@@ -137,11 +137,10 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, co
     const int n_steps = (n_blocks - grp + NG - 1) / NG;            // this group's blocks: grp, grp + NG, ...
     const size_t page_stride = (size_t)Hkv * BN * D;
     const int* table = block_table + (size_t)seq * max_blocks;
-    const uint32_t bar_addr = ta_u32(&bars[0]);
-
     if (tid == 0) {
         abort_flag = (ta_u32(smem_raw) & 1023u) ? 1 : 0;    // misaligned tiles would give wrong sums: give up instead
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_addr) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(ta_u32(&bars[0])) : "memory");     // scores done
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(ta_u32(&bars[3])) : "memory");     // P V done
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (tid < 32) {                                         // one warp owns the tensor-memory allocation
@@ -155,31 +154,34 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, co
         ta_cp_async16(ta_u32(sQ) + r * 128 + ((ch ^ (r & 7)) << 4),
                       q + (size_t)(t0 + (r < n_rows ? r : 0)) * q_row_stride + (size_t)h * D + ch * 8, r < n_rows);
     }
-    ta_commit_group();
-    auto load_kv = [&](int step, int buf) {
+    auto load_page = [&](int step, bool values) {           // K or V of this CTA's block `step` into buffer step & 1
+        if (step >= n_steps) return;
         const int blk = blk_lo + grp + step * NG;
         int page = (blk < max_blocks) ? table[blk] : -1;
         const bool ok = (page >= 0 && page < n_pages);
         if (!ok) { if (gt == 0 && err) atomicExch(err, 3); page = 0; }
-        const __nv_bfloat16* kg = kpages + (size_t)page * page_stride + (size_t)hk * BN * D;
-        const __nv_bfloat16* vg = vpages + (size_t)page * page_stride + (size_t)hk * BN * D;
-        const uint32_t ks = ta_u32(sK) + buf * TA_KV_BYTES, vs = ta_u32(sV) + buf * TA_KV_BYTES;
+        const __nv_bfloat16* src = (values ? vpages : kpages) + (size_t)page * page_stride + (size_t)hk * BN * D;
+        const uint32_t dst = ta_u32(values ? sV : sK) + (step & 1) * TA_KV_BYTES;
         for (int c = gt; c < BN * 8; c += TA_THREADS) {
             const int r = c >> 3, ch = c & 7;
-            const uint32_t off = r * 128 + ((ch ^ (r & 7)) << 4);
-            ta_cp_async16(ks + off, kg + r * D + ch * 8, ok);
-            ta_cp_async16(vs + off, vg + r * D + ch * 8, ok);
+            ta_cp_async16(dst + r * 128 + ((ch ^ (r & 7)) << 4), src + r * D + ch * 8, ok);
         }
     };
-    if (n_steps > 0) load_kv(0, 0);
+    // copy groups, always in this order: [Q, K(0)], [K(1)], [V(0)], then per step i: [K(i+2)], [V(i+1)]
+    load_page(0, false);
     ta_commit_group();
-    ta_wait_group<1>();                                     // this thread's part of Q has landed
+    load_page(1, false);
+    ta_commit_group();
+    load_page(0, true);
+    ta_commit_group();
+    ta_wait_group<2>();                                     // Q and K(0) have landed
     ta_fence_async_smem();
     ta_fence_before();
-    __syncthreads();                                        // Q, the barrier and the allocation
+    __syncthreads();                                        // Q, K(0), the barriers and the allocation
     ta_fence_after();
     const uint32_t tmem_base = tmem_slot;
     volatile int* abort_p = &abort_flag;
+    const uint32_t bar_s = ta_u32(&bars[0]), bar_pv = ta_u32(&bars[3]);
 
     // ---- this thread's query row
     const int row = gt;
@@ -191,93 +193,109 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, co
     float o[D];
 #pragma unroll
     for (int d = 0; d < D; ++d) o[d] = 0.f;
-    uint32_t phase = 0;
-    bool ok = true;
-
-    for (int step = 0; step < n_steps; ++step) {
-        const int buf = step & 1;
-        if (step + 1 < n_steps) load_kv(step + 1, buf ^ 1);
-        ta_commit_group();
-        ta_wait_group<1>();                                 // this step's K and V (and Q) have landed
-        ta_fence_async_smem();                              // ... and are visible to the tensor cores' reads
-        __syncthreads();
-        if (*abort_p) { ok = false; break; }                // (a thread that gave up set the flag before this barrier)
-        if (gt == 0) {
-            ta_fence_after();
-            const uint64_t dq = ta_desc(ta_u32(sQ)), dk = ta_desc(ta_u32(sK) + buf * TA_KV_BYTES);
-#pragma unroll
-            for (int k = 0; k < D / 16; ++k)               // +32 bytes per k step: +2 in the descriptors' 16-byte units
-                ta_mma(tmem_base, dq + 2 * k, dk + 2 * k, IDESC_S, k > 0 ? 1u : 0u);
-            ta_commit(bar_addr);
-        }
-        ta_wait(bar_addr, phase, abort_p);                  // (on failure the flag is set and seen after the next barrier)
-        phase ^= 1u;
+    uint32_t phase_s = 0, phase_pv = 0;
+    bool ok = !*abort_p;
+    const uint64_t dq = ta_desc(ta_u32(sQ)), dp = ta_desc(ta_u32(sP));
+    auto issue_s = [&](int step) {                          // S = Q K(step)^T: +32 bytes per k step, +2 in the descriptors' units
         ta_fence_after();
+        const uint64_t dk = ta_desc(ta_u32(sK) + (step & 1) * TA_KV_BYTES);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) ta_mma(tmem_base, dq + 2 * k, dk + 2 * k, IDESC_S, k > 0 ? 1u : 0u);
+        ta_commit(bar_s);
+    };
+    if (ok && n_steps > 0 && gt == 0) issue_s(0);
 
-        // ---- this row's 64 scores: mask, online softmax in base 2 on the raw scores, probabilities to shared memory
-        const int key0 = (blk_lo + grp + step * NG) * BN;
-        float p_sum = 0.f, mx = -INFINITY;
+    // The steps overlap: while the threads work on the scores of block i, the tensor cores already multiply Q with
+    // K(i+1) (the scores of block i are in registers by then) and finish P(i-1) V(i-1), which is only added to the
+    // output rows after the probabilities of block i are known.
+    for (int step = 0; ok && step < n_steps; ++step) {
+        ta_wait(bar_s, phase_s, abort_p);                   // (on failure the flag is set and seen after the next barrier)
+        phase_s ^= 1u;
+        ta_fence_after();
         uint32_t sv[2][32];
         ta_ld32(t_s, sv[0]);
         ta_ld32(t_s + 32, sv[1]);
+        load_page(step + 2, false);                         // K(step)'s buffer is free: the product that read it is done
+        ta_commit_group();
         ta_ld_wait();
+        ta_wait_group<2>();                                 // K(step + 1) has landed (newer: V(step), K(step + 2))
+        ta_fence_async_smem();
+        ta_fence_before();
+        __syncthreads();                                    // every thread has its scores: the columns may be written again
+        if (*abort_p) { ok = false; break; }
+        if (gt == 0 && step + 1 < n_steps) issue_s(step + 1);
+
+        // ---- this row's 64 scores: mask, online softmax in base 2 on the raw scores
+        const int key0 = (blk_lo + grp + step * NG) * BN;
+        float mx = -INFINITY;
         const bool interior = (key0 + BN - 1 <= pos_r) && (key0 >= lo_r);
+        if (!interior) {
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                float s = __uint_as_float(sv[hf][j]);
-                if (!interior) { const int key = key0 + hf * 32 + j; if (!(key <= pos_r && key >= lo_r)) s = -INFINITY; }
-                sv[hf][j] = __float_as_uint(s);
-                mx = fmaxf(mx, s);
+            for (int j = 0; j < 64; ++j) {
+                const int key = key0 + j;
+                if (!(key <= pos_r && key >= lo_r)) sv[j >> 5][j & 31] = 0xff800000u;     // -inf
             }
         }
+#pragma unroll
+        for (int j = 0; j < 64; ++j) mx = fmaxf(mx, __uint_as_float(sv[j >> 5][j & 31]));
         const float mn = fmaxf(m, mx);
         const float use = (mn == -INFINITY) ? 0.f : mn;     // the row sees nothing yet
         const float alpha = ta_exp2((m - use) * scale_log2);
         const float off = -use * scale_log2;
-        unsigned char* prow = sP + row * 128;
+        float p_sum = 0.f;
+        uint32_t pw[32];                                    // the probabilities, two bf16 per word
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {                       // eight probabilities (16 bytes) per store, swizzled like the rest
-            float pv[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                const int j = c * 8 + e;
-                pv[e] = ta_exp2(fmaf(__uint_as_float(sv[j >> 5][j & 31]), scale_log2, off));
-                p_sum += pv[e];
-            }
-            uint4 w;
-            w.x = vm_pack_bf16(pv[0], pv[1]); w.y = vm_pack_bf16(pv[2], pv[3]);
-            w.z = vm_pack_bf16(pv[4], pv[5]); w.w = vm_pack_bf16(pv[6], pv[7]);
-            *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = w;
+        for (int j = 0; j < 64; j += 2) {
+            const float p0 = ta_exp2(fmaf(__uint_as_float(sv[j >> 5][j & 31]), scale_log2, off));
+            const float p1 = ta_exp2(fmaf(__uint_as_float(sv[(j + 1) >> 5][(j + 1) & 31]), scale_log2, off));
+            p_sum += p0 + p1;
+            pw[j >> 1] = vm_pack_bf16(p0, p1);
         }
         l = l * alpha + p_sum;
         m = mn;
+        // ---- the previous block's P V is done by now: add it, then rescale; its P tile and its V buffer are free
+        if (step > 0) {
+            ta_wait(bar_pv, phase_pv, abort_p);
+            phase_pv ^= 1u;
+            ta_fence_after();
+            ta_ld32(t_pv, sv[0]);
+            ta_ld32(t_pv + 32, sv[1]);
+            ta_ld_wait();
 #pragma unroll
-        for (int d = 0; d < D; ++d) o[d] *= alpha;
-        ta_fence_async_smem();                              // P is read by the tensor cores
+            for (int d = 0; d < D; ++d) o[d] += __uint_as_float(sv[d >> 5][d & 31]);
+        }
+        load_page(step + 1, true);                          // V(step + 1) into the buffer V(step - 1) was in
+        ta_commit_group();
+        if (alpha != 1.f) {
+#pragma unroll
+            for (int d = 0; d < D; ++d) o[d] *= alpha;
+        }
+        unsigned char* prow = sP + row * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c)                         // eight probabilities (16 bytes) per store, swizzled like the rest
+            *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(pw[4 * c], pw[4 * c + 1], pw[4 * c + 2], pw[4 * c + 3]);
+        ta_wait_group<2>();                                 // V(step) has landed (newer: K(step + 2), V(step + 1))
+        ta_fence_async_smem();                              // P and V are read by the tensor cores
         ta_fence_before();
         __syncthreads();
         if (*abort_p) { ok = false; break; }
-        if (gt == 0) {
+        if (gt == 0) {                                      // P: +32 bytes per 16 keys; V: 16 key rows = 2048 bytes = +128
             ta_fence_after();
-            const uint64_t dp = ta_desc(ta_u32(sP)), dv = ta_desc(ta_u32(sV) + buf * TA_KV_BYTES);
+            const uint64_t dv = ta_desc(ta_u32(sV) + (step & 1) * TA_KV_BYTES);
 #pragma unroll
-            for (int k = 0; k < BN / 16; ++k)              // P: +32 bytes per 16 keys; V: 16 key rows = 2048 bytes = +128
-                ta_mma(tmem_base + 64, dp + 2 * k, dv + 128 * k, IDESC_PV, k > 0 ? 1u : 0u);
-            ta_commit(bar_addr);
+            for (int k = 0; k < BN / 16; ++k) ta_mma(tmem_base + 64, dp + 2 * k, dv + 128 * k, IDESC_PV, k > 0 ? 1u : 0u);
+            ta_commit(bar_pv);
         }
-        ta_wait(bar_addr, phase, abort_p);
-        phase ^= 1u;
+    }
+    if (ok && n_steps > 0) {                                // the last block's P V
+        ta_wait(bar_pv, phase_pv, abort_p);
         ta_fence_after();
+        uint32_t sv[2][32];
         ta_ld32(t_pv, sv[0]);
         ta_ld32(t_pv + 32, sv[1]);
         ta_ld_wait();
 #pragma unroll
         for (int d = 0; d < D; ++d) o[d] += __uint_as_float(sv[d >> 5][d & 31]);
-        ta_fence_before();
-        __syncthreads();                                    // tensor memory, P and this step's K and V may be written again
-        if (*abort_p) { ok = false; break; }
     }
     ta_wait_group<0>();
     ta_fence_before();
@@ -297,15 +315,14 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, co
             }
         }
     } else {
-        // ---- the cluster's CTAs exchange their rows: CTA c joins and stores rows [c * 128 / NC, (c + 1) * 128 / NC) of
-        // the tile.  Every CTA's K, V and P buffers are free once all CTAs are past this barrier; they receive the rows
+        // ---- the cluster's CTAs exchange their rows: CTA c joins and stores the rows r of the tile with r % NC == c.  Every CTA's K, V and P buffers are free once all CTAs are past this barrier; they receive the rows
         // as xch[source CTA][row][TA_RW].  (A CTA that gave up still takes part in the barriers; its rows are garbage,
         // the error word says so.)
-        constexpr int RPR = TA_BM / NC;                                 // rows joined per CTA
+        constexpr int RPR = (TA_BM + NC - 1) / NC;                      // rows joined per CTA: row r belongs to CTA r % NC
         asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
         {
-            const unsigned dest = (unsigned)(row / RPR);
-            const uint32_t local = ta_u32(sK) + (uint32_t)(((grp * RPR) + (row % RPR)) * TA_RW * 4);
+            const unsigned dest = (unsigned)(row % NC);
+            const uint32_t local = ta_u32(sK) + (uint32_t)(((grp * RPR) + (row / NC)) * TA_RW * 4);
             uint32_t remote;
             asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(dest));
 #pragma unroll
@@ -315,27 +332,27 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, co
             asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(remote + 4 * D), "f"(m), "f"(l), "f"(0.f), "f"(0.f) : "memory");
         }
         asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-        if (!*abort_p) {
-            constexpr int CPT = D / NC;                                 // columns per thread: NC threads share a row
-            const int r = tid / NC, c0 = (tid % NC) * CPT;
-            const int trow = grp * RPR + r;                             // the row's place in the tile
-            const float* xch = reinterpret_cast<const float*>(sK);
-            float M = -INFINITY;
+        {
+            constexpr int CPT = D / 2;                                  // two threads share a row, 32 columns each
+            const int r = tid >> 1, c0 = (tid & 1) * CPT;
+            const int trow = r * NC + grp;                              // the row's place in the tile
+            if (!*abort_p && r < RPR && trow < n_rows) {
+                const float* xch = reinterpret_cast<const float*>(sK);
+                float M = -INFINITY;
 #pragma unroll
-            for (int g = 0; g < NC; ++g) M = fmaxf(M, xch[(size_t)(g * RPR + r) * TA_RW + D]);
-            const float u = (M == -INFINITY) ? 0.f : M;
-            float acc[CPT], L = 0.f;
+                for (int g = 0; g < NC; ++g) M = fmaxf(M, xch[(size_t)(g * RPR + r) * TA_RW + D]);
+                const float u = (M == -INFINITY) ? 0.f : M;
+                float acc[CPT], L = 0.f;
 #pragma unroll
-            for (int d = 0; d < CPT; ++d) acc[d] = 0.f;
+                for (int d = 0; d < CPT; ++d) acc[d] = 0.f;
 #pragma unroll
-            for (int g = 0; g < NC; ++g) {
-                const float* src = xch + (size_t)(g * RPR + r) * TA_RW;
-                const float f = ta_exp2((src[D] - u) * scale_log2);
-                L += src[D + 1] * f;
+                for (int g = 0; g < NC; ++g) {
+                    const float* src = xch + (size_t)(g * RPR + r) * TA_RW;
+                    const float f = ta_exp2((src[D] - u) * scale_log2);
+                    L += src[D + 1] * f;
 #pragma unroll
-                for (int d = 0; d < CPT; ++d) acc[d] += src[c0 + d] * f;
-            }
-            if (trow < n_rows) {
+                    for (int d = 0; d < CPT; ++d) acc[d] += src[c0 + d] * f;
+                }
                 const float inv = 1.f / L;
                 __nv_bfloat16* orow = out + ((size_t)(t0 + trow) * H + h) * D + c0;
 #pragma unroll
@@ -383,7 +400,7 @@ int ta_launch(int n_tiles, int H, cudaStream_t stream, const __nv_bfloat16* q, i
 }  // namespace
 
 // n_tiles = sum over the step's sequences of ceil(new tokens / 128), computed by the host.  Head size 64 only;
-// out [T, H*64] must be 16-byte aligned, q rows too (q_row_stride % 8 == 0).  groups (1, 2 or 4): CTAs of a cluster
+// out [T, H*64] must be 16-byte aligned, q rows too (q_row_stride % 8 == 0).  groups (1 to 4): CTAs of a cluster
 // that take a tile's key blocks in turn; more for steps whose tiles see many keys.
 VM_API int vm_attention_prefill_tc_bf16(const void* q, int q_row_stride, const void* kpages, const void* vpages,
                                         const int* block_table, int max_blocks, const int* positions, const int* cu_tokens,
@@ -397,6 +414,9 @@ VM_API int vm_attention_prefill_tc_bf16(const void* q, int q_row_stride, const v
     const __nv_bfloat16 *qq = (const __nv_bfloat16*)q, *kk = (const __nv_bfloat16*)kpages, *vv = (const __nv_bfloat16*)vpages;
     if (groups >= 4)
         return ta_launch<4>(n_tiles, H, stream, qq, q_row_stride, kk, vv, block_table, max_blocks, positions, cu_tokens, B,
+                            (__nv_bfloat16*)out, Hkv, sl, window, n_pages, err);
+    if (groups == 3)
+        return ta_launch<3>(n_tiles, H, stream, qq, q_row_stride, kk, vv, block_table, max_blocks, positions, cu_tokens, B,
                             (__nv_bfloat16*)out, Hkv, sl, window, n_pages, err);
     if (groups >= 2)
         return ta_launch<2>(n_tiles, H, stream, qq, q_row_stride, kk, vv, block_table, max_blocks, positions, cu_tokens, B,

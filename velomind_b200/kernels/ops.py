@@ -21,6 +21,7 @@ _c_int, _c_ll, _c_f, _c_p = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, cty
 
 launch_count = 0          # this library's own kernels launched through this module (the bench reports it)
 library_calls = 0         # library matrix products (cuBLAS through torch.mm)
+tc_attention_calls = 0    # launches of the tcgen05 prefill attention (tests check that long prompts take it)
 
 
 class KernelError(RuntimeError):
@@ -153,6 +154,8 @@ def attention_prefill_tc_bf16(q: torch.Tensor, q_row_stride: int, k_pages: torch
     """The same attention on tcgen05 (tensor-memory accumulators), head size 64 only: a CTA per 128 new tokens and
     head.  n_tiles = sum of ceil(new tokens / 128); groups (1, 2, 4): groups of 128 threads that take a tile's key
     blocks in turn."""
+    global tc_attention_calls
+    tc_attention_calls += 1
     B = cu_tokens.shape[0] - 1
     _check(library().vm_attention_prefill_tc_bf16(_ptr(q), _c_int(q_row_stride), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
                                                   _c_int(block_table.shape[1]), _ptr(positions), _ptr(cu_tokens), _c_int(B),
@@ -161,7 +164,9 @@ def attention_prefill_tc_bf16(q: torch.Tensor, q_row_stride: int, k_pages: torch
            "attention_prefill_tc_bf16")
 
 
-TC_ATTENTION = True            # head size 64: prefill attention on tcgen05 instead of mma.sync
+TC_ATTENTION = True            # head size 64: prefill attention of long prompts on tcgen05 instead of mma.sync
+TC_ATTENTION_MIN_BLOCKS = 20   # ... when a tile sees at least this many key blocks of 64
+TC_ATTENTION_SLOTS = 444       # CTAs of that kernel the GPU holds at once (148 SMs x 3)
 
 _decode_counters = {}
 DECODE_COUNTERS = 1 << 16
@@ -222,10 +227,13 @@ def attention(ctx, q: torch.Tensor, q_row_stride: int, k_pages: torch.Tensor, v_
         lens = ctx.host_cu_tokens[1:] - ctx.host_cu_tokens[:-1]
         # the longest chain of key blocks a tile walks, and how many CTAs there are to hide it behind
         most_blocks = (min(ctx.max_ctx_len, window + 64) if window > 0 else ctx.max_ctx_len) // 64 + 1
-        if TC_ATTENTION and D == 64 and err_ok(ctx):
-            attention_prefill_tc_bf16(q, q_row_stride, k_pages, v_pages, block_table, ctx.positions, ctx.cu_tokens,
-                                      int(((lens + 127) // 128).sum()), out, H, Hkv, D, scale, window, ctx.err,
-                                      4 if most_blocks >= 16 else (2 if most_blocks >= 4 else 1))
+        if TC_ATTENTION and D == 64 and most_blocks >= TC_ATTENTION_MIN_BLOCKS and err_ok(ctx):
+            # long prompts: the tcgen05 kernel, a tile's key blocks dealt out to as many CTAs (2 to 4) as still fit the GPU at once
+            # (measured, 9 heads: 1,536 tokens 23.7 us against 32.2 us for the mma.sync kernel; 2,048: 33.6 / 39.4; 4,096: 89.9 / 123.8;
+            #  1,024: 17.6 / 16.6, hence the threshold)
+            n_tiles = int(((lens + 127) // 128).sum())
+            attention_prefill_tc_bf16(q, q_row_stride, k_pages, v_pages, block_table, ctx.positions, ctx.cu_tokens, n_tiles, out,
+                                      H, Hkv, D, scale, window, ctx.err, max(2, min(4, TC_ATTENTION_SLOTS // max(1, n_tiles * H))))
             return
         n_tiles = int(((lens + 63) // 64).sum())
         groups = 2 if most_blocks >= 8 else 1      # measured at 9 heads of 64: 2 groups 39 us, 1 group 43 us, 4 groups 46 us (2,048 tokens)
