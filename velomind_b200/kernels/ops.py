@@ -43,7 +43,13 @@ def _ptr(t: Optional[torch.Tensor]):
     return _c_p(t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream():
+    """The current CUDA stream's handle (the raw query is several times cheaper than building a Stream object)."""
+    if _raw_stream is not None:
+        return _c_p(_raw_stream(torch.cuda.current_device()))
     return _c_p(torch.cuda.current_stream().cuda_stream)
 
 
