@@ -47,7 +47,9 @@ def build_anchor(ref: str, work: str) -> str:
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: python tests/golden/make_golden.py <path of a checkout of the reference project>")
+    ref = sys.argv[1]
     with tempfile.TemporaryDirectory() as work:
         exe = build_anchor(ref, work)
         for name, (cfg, init, tokens) in CASES.items():
