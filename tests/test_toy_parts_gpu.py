@@ -1,7 +1,7 @@
 """Parts defined HERE, in the test, are registered, built from a config.json, loaded and stepped without any
 change to the package: a mixer with fixed-size state of its own (a decaying sum), a feed-forward with
-routing (top-1 of several experts), and an architecture whose layers mix them with the built-in attention
-and SwiGLU.  They are toys that exist to exercise the interfaces; they are nobody's model."""
+routing (top-1 of several experts), a position encoding with frequencies of its own, and an architecture whose
+layers mix them with the built-in attention and SwiGLU.  They are toys that exist to exercise the interfaces; they are nobody's model."""
 import numpy as np
 import pytest
 import torch
@@ -74,10 +74,24 @@ def _define():
                     y[rows] = hcur @ self.w[f"experts.{e}.down.weight"].t()
             out.copy_(y.to(out.dtype))
 
+    class EvenlySpacedRotary(Part):
+        """Rotary pairs whose frequencies are evenly spaced between 0 and `top` instead of geometric: a position part
+        owns constants only, so another table is all there is to it."""
+
+        graph_safe = True
+
+        def __init__(self, head_dim, top):
+            self.head_dim, self.top = head_dim, top
+
+        def tables(self, bc):
+            half = self.head_dim // 2
+            return (torch.arange(1, half + 1, dtype=torch.float32) * (self.top / half)).to(bc.device), self.head_dim
+
     def toy_config(data, where="config.json"):
         r = KeyReader(data, where)
         return {k: r.integer(k) for k in ("vocab", "width", "layers", "state", "heads", "experts", "limit")} | {
-            "decay": r.number("decay"), "eps": r.number("eps"), "theta": r.number("theta")}
+            "decay": r.number("decay"), "eps": r.number("eps"), "theta": r.number("theta"),
+            "even_rotary": r.integer("even_rotary", minimum=0)}
 
     def toy_plan(c):
         norm = PartSpec("rmsnorm", {"size": c["width"], "eps": c["eps"]})
@@ -86,10 +100,13 @@ def _define():
             if l % 2 == 0:      # state mixer + built-in SwiGLU
                 mixer = PartSpec("toy_decaying_sum", {"hidden": c["width"], "width": c["state"], "decay": c["decay"]})
                 ff = PartSpec("swiglu", {"hidden": c["width"], "intermediate": 2 * c["width"]})
-            else:               # built-in attention + routed feed-forward
+            else:               # built-in attention (the last one with the toy position encoding) + routed feed-forward
+                hd = c["width"] // c["heads"]
+                position = PartSpec("rotary_half_split", {"head_dim": hd, "theta": c["theta"]})
+                if c["even_rotary"] and l == c["layers"] - 1:
+                    position = PartSpec("toy_evenly_spaced_rotary", {"head_dim": hd, "top": 0.5})
                 mixer = PartSpec("grouped_query_attention", {
-                    "hidden": c["width"], "heads": c["heads"], "kv_heads": 1, "head_dim": c["width"] // c["heads"],
-                    "position": PartSpec("rotary_half_split", {"head_dim": c["width"] // c["heads"], "theta": c["theta"]})})
+                    "hidden": c["width"], "heads": c["heads"], "kv_heads": 1, "head_dim": hd, "position": position})
                 ff = PartSpec("toy_top_one_experts", {"hidden": c["width"], "inner": c["width"], "experts": c["experts"]})
             blocks.append(BlockSpec("prenorm", f"toy.layers.{l}.", mixer, ff, norm, norm))
         return ModelPlan(hidden_size=c["width"], vocab_size=c["vocab"],
@@ -101,11 +118,12 @@ def _define():
 
     register_part("mixer", "toy_decaying_sum", DecayingSumMixer)
     register_part("feed_forward", "toy_top_one_experts", TopOneExperts)
+    register_part("position", "toy_evenly_spaced_rotary", EvenlySpacedRotary)
     register_architecture("ToyForCausalLM", toy_config, toy_plan)
 
 
 TOY = {"architectures": ["ToyForCausalLM"], "vocab": 77, "width": 48, "layers": 4, "state": 20, "heads": 3, "experts": 3,
-       "limit": 512, "decay": 0.9, "eps": 1e-5, "theta": 1000.0}
+       "limit": 512, "decay": 0.9, "eps": 1e-5, "theta": 1000.0, "even_rotary": 1}
 
 
 @pytest.fixture
@@ -118,6 +136,24 @@ def toy_folder(tmp_path):
     unregister_architecture("ToyForCausalLM")
     unregister_part("mixer", "toy_decaying_sum")
     unregister_part("feed_forward", "toy_top_one_experts")
+    unregister_part("position", "toy_evenly_spaced_rotary")
+
+
+def test_toy_position_encoding_is_used(toy_folder, tmp_path):
+    """The same weights with and without the toy frequencies in the last layer: a sequence's first token is rotated by
+    angle 0 either way (equal logits), every later token is not (different logits)."""
+    import velomind_b200 as vm
+    plain_rotary = vm.write_random_model(str(tmp_path / "toy_geometric"), dict(TOY, even_rotary=0), seed=4, std=0.3, dtype="float32")
+    tokens = [5, 70, 3, 12, 44, 9]
+    rows = []
+    for folder in (toy_folder, plain_rotary):
+        model = vm.load_model(folder, torch.float32, "cuda:0")
+        assert type(model.layers[3].mixer.position).__name__ == ("EvenlySpacedRotary" if folder == toy_folder else "RotaryHalfSplit")
+        engine = vm.Engine(model, 64 * 4)
+        slot = engine.open()
+        rows.append(engine.step([vm.Entry(slot, tokens, list(range(len(tokens))))]).cpu().numpy().copy())
+    assert np.abs(rows[0][0] - rows[1][0]).max() < 1e-6
+    assert all(np.abs(rows[0][t] - rows[1][t]).max() > 1e-4 for t in range(1, len(tokens)))
 
 
 def test_toy_architecture_is_built_and_stepped(toy_folder):
