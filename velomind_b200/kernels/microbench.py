@@ -16,7 +16,43 @@ import torch
 from . import ops
 
 KERNELS = ["qkv_rope", "out_residual", "gate_up_swiglu", "down_residual", "head", "attn_decode", "attn_prefill", "attn_prefill_tc",
-           "add_rmsnorm", "sample", "tc_linear", "tc_residual", "tc_swiglu", "cublas_linear", "decode_cluster"]
+           "add_rmsnorm", "sample", "tc_linear", "tc_residual", "tc_swiglu", "cublas_linear", "decode_cluster", "prefill_step"]
+
+
+def _prefill_step(a) -> int:
+    """One whole prompt of --tokens tokens through a random model of the given sizes (--layers layers): the step's time
+    when replayed from its CUDA graph, and eagerly (the launches one by one, for a launch list under a profiler)."""
+    import tempfile
+
+    import numpy as np
+
+    from .. import Engine, Entry, load_model, write_random_model
+    cfg = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": a.layers,
+           "hidden_size": a.hidden, "num_attention_heads": a.heads, "num_key_value_heads": a.kv_heads,
+           "intermediate_size": a.intermediate, "vocab_size": a.vocab, "rope_theta": 100000.0, "rms_norm_eps": 1e-5,
+           "tie_word_embeddings": True, "max_position_embeddings": max(8192, a.tokens)}
+    T = a.tokens
+    with tempfile.TemporaryDirectory() as d:
+        write_random_model(d, cfg, seed=0)
+        model = load_model(d, torch.bfloat16, "cuda:0")
+        toks = np.random.default_rng(0).integers(0, a.vocab, size=T).tolist()
+        out = {"kernel": "prefill_step", "tokens": T, "layers": a.layers}
+        for name, graphs in (("graph", True), ("eager", False)):
+            eng = Engine(model, T + 64, use_graphs=graphs)
+            times = []
+            for _ in range(4 if graphs else 2):
+                slot = eng.open()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                eng.step([Entry(slot, toks, [T - 1])])
+                e1.record()
+                torch.cuda.synchronize()
+                times.append(e0.elapsed_time(e1))
+                eng.close(slot)
+            out[name + "_ms"] = round(min(times), 4)
+        print(json.dumps(out))
+    return 0
 
 
 def _decode_cluster(a) -> int:
@@ -135,7 +171,7 @@ def main(argv=None) -> int:
     ap.add_argument("--k", type=int, default=0, help="tc_*/cublas_linear: inner size (default hidden)")
     ap.add_argument("--splits", type=int, default=0, help="attn_decode: key splits (0: the engine's choice)")
     ap.add_argument("--groups", type=int, default=4, help="attn_prefill: warp groups sharing a tile's key blocks")
-    ap.add_argument("--layers", type=int, default=6, help="decode_cluster: layers of the random model")
+    ap.add_argument("--layers", type=int, default=6, help="decode_cluster, prefill_step: layers of the random model")
     ap.add_argument("--clusters", type=int, default=0, help="decode_cluster: deal the batch out to at most this many clusters")
     ap.add_argument("--temp", type=float, default=0.0, help="sample: temperature (0: greedy)")
     ap.add_argument("--top-p", type=float, default=0.9, help="sample: nucleus mass, with --temp")
@@ -145,6 +181,8 @@ def main(argv=None) -> int:
     dev = ops.require_cuda("cuda:0")
     if a.kernel == "decode_cluster":
         return _decode_cluster(a)
+    if a.kernel == "prefill_step":
+        return _prefill_step(a)
     M, hid, H, Hkv, D, I, V = a.batch, a.hidden, a.heads, a.kv_heads, a.head_dim, a.intermediate, a.vocab
     bf = torch.bfloat16
     copies = 40
