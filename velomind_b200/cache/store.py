@@ -52,6 +52,7 @@ class CacheGroup:
         self.pages = FreeList(n_pages, "cache page")
         self.block_table = np.full((max_slots, max_blocks), -1, dtype=np.int32)
         self.blocks_end = [0] * max_slots      # logical blocks [blocks_begin, blocks_end) hold a page
+        self.version = 0                       # grows whenever an entry of the block table changes
         self.blocks_begin = [0] * max_slots
         shape = (n_layers, n_pages, need.kv_heads, PAGE_TOKENS, need.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
@@ -72,6 +73,7 @@ class CacheGroup:
         for j, pg in enumerate(ids):
             self.block_table[slot, self.blocks_end[slot] + j] = pg
         self.blocks_end[slot] = want
+        self.version += 1
 
     def trim(self, slot: int, length: int) -> None:
         """After a step: a window group gives back the pages no later query can reach."""
@@ -84,6 +86,7 @@ class CacheGroup:
             self.pages.give(int(self.block_table[slot, b]))
             self.block_table[slot, b] = -1
             b += 1
+            self.version += 1
         self.blocks_begin[slot] = b
 
     def release(self, slot: int) -> None:
@@ -92,6 +95,7 @@ class CacheGroup:
             self.block_table[slot, b] = -1
         self.blocks_begin[slot] = 0
         self.blocks_end[slot] = 0
+        self.version += 1
 
     def layer(self, i: int):
         return self.k[i], self.v[i]

@@ -85,6 +85,8 @@ class Descriptors:
         self.dev = torch.zeros(off, dtype=torch.int32, device=device)
         self.copied = _new_event()
         self.used = False
+        self.decode_slots = None           # the slots whose plain decode step the buffer describes (Engine._step_decode) ...
+        self.decode_versions = None        # ... and the block tables' versions it was filled at
 
     def h(self, name: str) -> np.ndarray:
         off, n = self.offsets[name]
@@ -230,6 +232,9 @@ class Engine:
         """Run the entries' tokens as one batch from the cache; return float32 logits [wanted, vocab] on the
         device, in the order of the entries and of each entry's `want`.  The tensor is valid until the next step."""
         entries = list(entries)
+        if entries and len(entries) <= self.max_step_tokens and all(
+                len(e.tokens) == 1 and len(e.want) == 1 and e.want[0] == 0 for e in entries):
+            return self._step_decode(entries)
         self._validate(entries)
         n_rows = sum(len(e.want) for e in entries)
         logits = self._logits_buffer(n_rows)
@@ -505,6 +510,7 @@ class Engine:
         R = len(wanted_here)
         desc = self._descriptors(T, B, R, widths)
         desc.wait_reusable()
+        desc.decode_slots = None
         tok, pos, sot = desc.h("tokens"), desc.h("positions"), desc.h("seq_of_token")
         cu, slots, ctx_len, lrows = desc.h("cu_tokens"), desc.h("slots"), desc.h("ctx_len"), desc.h("logit_rows")
         if T == B:
@@ -567,10 +573,73 @@ class Engine:
             ctx.refresh()
         return ctx
 
+    def _step_decode(self, entries: List[Entry]) -> torch.Tensor:
+        """The common decode step (one new token per sequence, its logits wanted) with the host work of `step` cut to what
+        this shape needs: the same checks, the same descriptors, no general bookkeeping."""
+        cache, B = self.cache, len(entries)
+        lengths, held = cache.length, cache.slots.is_held
+        slot_list = [e.slot for e in entries]
+        toks = [int(e.tokens[0]) for e in entries]
+        if len(set(slot_list)) != B:
+            raise ValueError("a slot appears twice in one step")
+        grows = False
+        for slot, t in zip(slot_list, toks):
+            if not held(slot):
+                raise CacheError(f"slot {slot} is not open")
+            if not 0 <= t < self.vocab:
+                raise ValueError(f"slot {slot}: token id {t} outside the vocabulary of {self.vocab}")
+            if lengths[slot] + 1 > cache.max_positions:
+                raise CacheError(f"slot {slot} would reach {lengths[slot] + 1} tokens; the model's limit is {cache.max_positions}")
+            grows = grows or lengths[slot] % PAGE_TOKENS == 0
+        if grows:            # some sequence begins a new page: the general check and reservation
+            if not cache.can_hold({slot: lengths[slot] + 1 for slot in slot_list}):
+                raise CacheError("out of cache pages for this step: the live sequences and the new tokens exceed max_tokens")
+            for slot in slot_list:
+                cache.reserve(slot, lengths[slot] + 1)
+        widths = []
+        for g in cache.groups:
+            need = max(1, max(g.blocks_end[slot] for slot in slot_list))
+            w = 1
+            while w < need:
+                w *= 2
+            widths.append(min(w, g.max_blocks))
+        desc = self._descriptors(B, B, B, widths)
+        desc.wait_reusable()
+        base = np.array([lengths[slot] for slot in slot_list], dtype=np.int32)
+        desc.h("tokens")[:B] = toks
+        desc.h("positions")[:B] = base
+        desc.h("ctx_len")[:B] = base + 1
+        versions = [g.version for g in cache.groups]
+        if desc.decode_slots != slot_list or desc.decode_versions != versions:   # else the buffer still holds these rows and tables
+            slot_ids = np.array(slot_list, dtype=np.int64)
+            rows = np.arange(B + 1, dtype=np.int32)
+            desc.h("seq_of_token")[:B] = rows[:B]
+            desc.h("cu_tokens")[:B + 1] = rows
+            desc.h("slots")[:B] = slot_ids
+            desc.h("logit_rows")[:B] = rows[:B]
+            for g, group in enumerate(cache.groups):
+                w = widths[g]
+                desc.h(f"table{g}").reshape(desc.caps[1], w)[:B] = group.block_table[slot_ids, :w]
+            desc.decode_slots, desc.decode_versions = slot_list, versions
+        desc.upload()
+        logits = self._logits_buffer(B)
+        self._execute(desc, B, B, B, widths, logits, 0)
+        for slot in slot_list:
+            cache.commit(slot, lengths[slot] + 1)
+        self.steps_run += 1
+        return logits[:B]
+
     def _run_chunk(self, entries, chunk, logits, row0, produced) -> int:
         cache = self.cache
         desc, T, B, R, widths, new_len, wanted_here = self._describe(entries, chunk)
+        self._execute(desc, T, B, R, widths, logits, row0)
+        for s, (i, a, b) in enumerate(chunk):
+            cache.commit(entries[i].slot, new_len[s])
+        produced.extend(wanted_here)
+        return R
 
+    def _execute(self, desc, T: int, B: int, R: int, widths, logits, row0: int) -> None:
+        """Run the model on a described step: from its CUDA graph where there is one, else part by part."""
         ctx = self._context(desc, T, B, R, widths)
         ctx.logits = logits[row0: row0 + R]
         bucket = self._bucket_of(ctx, (desc.caps[0], desc.caps[1], desc.caps[2], ctx.one_token_each, self.fused_prefill_rows))   # decode steps take other scratch
@@ -588,7 +657,3 @@ class Engine:
             self._replay_graph(ctx, bucket, shape_key)
         else:
             self._run_eager(ctx, bucket)
-        for s, (i, a, b) in enumerate(chunk):
-            cache.commit(entries[i].slot, new_len[s])
-        produced.extend(wanted_here)
-        return R
