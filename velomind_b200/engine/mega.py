@@ -101,7 +101,7 @@ class MegaPlan:
     def splits(self, B: int, table_width: int) -> int:
         G = self.H // self.Hkv
         groups = B * self.Hkv * (-(-G // 16))
-        return max(1, min(148 // groups if groups <= 148 else 1, ops.MAX_DECODE_SPLITS, max(1, table_width // 2)))
+        return max(1, min(ops.B200_SMS // groups if groups <= ops.B200_SMS else 1, ops.MAX_DECODE_SPLITS, max(1, table_width // 2)))
 
     def run(self, ctx) -> None:
         """The step of `ctx` (one token per sequence, at most 16 sequences): logits into ctx.logits."""

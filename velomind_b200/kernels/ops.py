@@ -172,7 +172,7 @@ def attention_prefill_tc_bf16(q: torch.Tensor, q_row_stride: int, k_pages: torch
 
 TC_ATTENTION = True            # head size 64: prefill attention of long prompts on tcgen05 instead of mma.sync
 TC_ATTENTION_MIN_BLOCKS = 20   # ... when a tile sees at least this many key blocks of 64
-TC_ATTENTION_SLOTS = 444       # CTAs of that kernel the GPU holds at once (148 SMs x 3)
+TC_ATTENTION_CTAS_PER_SM = 3   # CTAs of that kernel an SM holds at once (registers and shared memory)
 
 _decode_counters = {}
 DECODE_COUNTERS = 1 << 16
@@ -187,6 +187,7 @@ def decode_counters(device) -> torch.Tensor:
     return _decode_counters[key]
 
 
+B200_SMS = 148                 # streaming multiprocessors of the GPU this library is written for
 DECODE_ONE_CTA_BLOCKS = 16     # block tables up to this wide (1,024 tokens): at most two rounds of pages for ten warps
 
 
@@ -194,9 +195,9 @@ def decode_splits(B: int, Hkv: int, G: int, table_width: int) -> int:
     """How many CTAs share the keys of one (sequence, kv head): enough to fill the GPU, a function of the
     step's SHAPE only (so that a captured launch stays valid as sequences grow)."""
     groups = B * Hkv * (-(-G // 16))          # a CTA serves up to 16 query heads of one kv head
-    if groups <= 148 and table_width <= DECODE_ONE_CTA_BLOCKS:
+    if groups <= B200_SMS and table_width <= DECODE_ONE_CTA_BLOCKS:
         return 1                              # short sequences: one CTA of ten warps holds all pages, nothing is merged across CTAs
-    want = -(-148 // groups)                  # about one CTA per SM ...
+    want = -(-B200_SMS // groups)             # about one CTA per SM ...
     table_width = max(1, table_width // 4)    # ... and at least a page per warp of a CTA (the width bounds the pages)
     return max(1, min(want, MAX_DECODE_SPLITS, table_width))
 
@@ -239,7 +240,7 @@ def attention(ctx, q: torch.Tensor, q_row_stride: int, k_pages: torch.Tensor, v_
             #  1,024: 17.6 / 16.6, hence the threshold)
             n_tiles = int(((lens + 127) // 128).sum())
             attention_prefill_tc_bf16(q, q_row_stride, k_pages, v_pages, block_table, ctx.positions, ctx.cu_tokens, n_tiles, out,
-                                      H, Hkv, D, scale, window, ctx.err, max(2, min(4, TC_ATTENTION_SLOTS // max(1, n_tiles * H))))
+                                      H, Hkv, D, scale, window, ctx.err, max(2, min(4, _tc_attention_slots(out.device) // max(1, n_tiles * H))))
             return
         n_tiles = int(((lens + 63) // 64).sum())
         groups = 2 if most_blocks >= 8 else 1      # measured at 9 heads of 64: 2 groups 39 us, 1 group 43 us, 4 groups 46 us (2,048 tokens)
@@ -248,6 +249,17 @@ def attention(ctx, q: torch.Tensor, q_row_stride: int, k_pages: torch.Tensor, v_
     else:
         attention_generic(q, q_row_stride, k_pages, v_pages, block_table, ctx.positions, ctx.seq_of_token, out,
                           H, Hkv, D, scale, window, ctx.err)
+
+
+_sm_counts = {}
+
+
+def _tc_attention_slots(device) -> int:
+    """CTAs of the tcgen05 attention kernel the GPU holds at once."""
+    key = str(device)
+    if key not in _sm_counts:
+        _sm_counts[key] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _sm_counts[key] * TC_ATTENTION_CTAS_PER_SM
 
 
 def err_ok(ctx) -> bool:
