@@ -265,30 +265,32 @@ def test_attention_reports_a_missing_page():
     assert int(err.item()) == 3
 
 
-@pytest.mark.parametrize("V", [1000, 49152 + 7, 60011])     # the largest does not fit the kernel's shared-memory cache of a row
-def test_sampling(V):
+# (vocabulary, rows): one CTA per row with the row's probabilities in shared memory; a cluster of eight CTAs per row
+# (large vocabulary, few rows), once with a vocabulary that is no multiple of its slices; one CTA per row without the
+# shared-memory copy (many rows of a vocabulary too large for it)
+@pytest.mark.parametrize("V,R", [(1000, 6), (49152 + 7, 6), (60011, 6), (60011, 70)])
+def test_sampling(V, R):
     o = ops()
-    R = 6
     rng = np.random.default_rng(V)
     logits = (rng.standard_normal((R, V)) * 2).astype(np.float32)
     logits[0, 17] = logits[0, 400] = logits[0].max() + 1          # a tie: the lower index wins
     logits[1, :5] = np.nan
     logits[2, :] = np.nan                                         # nothing to choose from
     logits[3, 10] = np.inf
-    temperature = np.array([0.0, 0.0, 0.0, 0.0, 0.8, 1.3], dtype=np.float32)
-    top_p = np.array([0.9, 0.9, 0.9, 0.9, 1.0, 0.6], dtype=np.float32)
-    seed = np.array([1, 2, 3, 4, 1234, 99], dtype=np.int64)
-    stream = np.array([0, 1, 2, 3, 4, 5], dtype=np.int64)
+    temperature = np.concatenate([[0.0, 0.0, 0.0, 0.0, 0.8, 1.3], rng.uniform(0.5, 1.5, R - 6)]).astype(np.float32)
+    top_p = np.concatenate([[0.9, 0.9, 0.9, 0.9, 1.0, 0.6], rng.uniform(0.3, 1.0, R - 6)]).astype(np.float32)
+    seed = np.concatenate([[1, 2, 3, 4, 1234, 99], rng.integers(0, 1000, R - 6)]).astype(np.int64)
+    stream = np.arange(R, dtype=np.int64)
     dl = torch.from_numpy(logits).to(DEV)
     out = torch.empty(R, dtype=torch.int32, device=DEV)
     mism = 0
-    for step in range(40):
+    for step in range(40 if R == 6 else 3):
         steps = np.full(R, step, dtype=np.int64)
         o.sample(dl, torch.from_numpy(temperature).to(DEV), torch.from_numpy(top_p).to(DEV), torch.from_numpy(seed).to(DEV),
                  torch.from_numpy(stream).to(DEV), torch.from_numpy(steps).to(DEV), out)
         got = out.cpu().numpy()
         assert got[0] == 17 and got[1] == int(np.nanargmax(logits[1])) and got[2] == -1 and got[3] == 10
-        for r in (4, 5):
+        for r in range(4, R):
             want = P.sample_top_p(logits[r], float(temperature[r]), float(top_p[r]), P.uniform01(int(seed[r]), int(stream[r]), step))
             mism += int(got[r] != want)
     assert mism == 0

@@ -260,7 +260,269 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int V, con
     }
 }
 
+// ---------------------------------------------------------------- the same sampler, a cluster of eight CTAs per row
+// A decode batch has few rows and one CTA per row leaves the GPU idle while it walks a vocabulary of tens of thousands
+// several times.  Here eight CTAs (a thread-block cluster) share a row: each keeps an eighth of the row's probabilities
+// in shared memory, every pass sums its own eighth, and the eight partial results meet through distributed shared
+// memory (every CTA writes its number into every CTA's table, one hardware cluster barrier, every CTA adds the eight
+// numbers in rank order: the same sum everywhere, so all eight take the same decisions).  Same rules, same results.
+constexpr int SC_CTAS = 8, SC_THREADS = 256, SC_WARPS = SC_THREADS / 32, SC_WAYS = 7, SC_VALS = 8;   // SC_VALS >= SC_WAYS: numbers per exchange
+
+__device__ __forceinline__ void sc_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void sc_put(double* slot_local, unsigned to_rank, double v) {
+    unsigned remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((unsigned)__cvta_generic_to_shared(slot_local)), "r"(to_rank));
+    asm volatile("st.shared::cluster.f64 [%0], %1;" ::"r"(remote), "d"(v) : "memory");
+}
+
+struct ScShared {
+    double gather[2][SC_CTAS][SC_VALS];       // [exchange parity][source CTA][value]
+    double warp_d[SC_WARPS][SC_VALS];
+    float warp_v[SC_WARPS];
+    int warp_i[SC_WARPS];
+    double prefix[SC_THREADS];
+    int choice;
+};
+
+// Every CTA contributes up to SC_VALS numbers; the caller reads sh.gather[parity][source][k] after the call.
+__device__ __forceinline__ void sc_all_gather(ScShared& sh, int parity, unsigned rank, const double (&mine)[SC_VALS], int n) {
+    if (threadIdx.x < SC_CTAS * SC_VALS) {
+        const unsigned to = threadIdx.x / SC_VALS;
+        const int k = threadIdx.x % SC_VALS;
+        double v = 0.0;
+#pragma unroll
+        for (int j = 0; j < SC_VALS; ++j) if (j == k) v = mine[j];      // (no dynamic indexing of registers)
+        if (k < n) sc_put(&sh.gather[parity][rank][k], to, v);
+    }
+    sc_cluster_sync();
+}
+
+// Sum of n (<= SC_VALS) per-thread doubles over the CTA; every thread gets the sums (warps joined in warp order).
+__device__ __forceinline__ void sc_block_sum(ScShared& sh, double (&v)[SC_VALS], int n) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int k = 0; k < SC_VALS; ++k) if (k < n) v[k] = warp_sum_d(v[k]);
+    __syncthreads();
+    if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < SC_VALS; ++k) if (k < n) sh.warp_d[warp][k] = v[k];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < SC_VALS; ++k) {
+        if (k < n) {
+            double t = 0.0;
+#pragma unroll
+            for (int w = 0; w < SC_WARPS; ++w) t += sh.warp_d[w][k];
+            v[k] = t;
+        }
+    }
+}
+
+__global__ void __cluster_dims__(SC_CTAS, 1, 1) __launch_bounds__(SC_THREADS)
+sample_cluster_kernel(const float* __restrict__ logits, long long row_stride, int V, int slice,
+                      const float* __restrict__ temperature, const float* __restrict__ top_p,
+                      const long long* __restrict__ seed, const long long* __restrict__ stream_id,
+                      const long long* __restrict__ step, int* __restrict__ out) {
+    extern __shared__ __align__(16) float sraw[];                   // this CTA's slice of unnormalised probabilities
+    __shared__ ScShared sh;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    unsigned rank;
+    asm("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const int row = blockIdx.x / SC_CTAS;
+    const float* x = logits + (size_t)row * row_stride;
+    const int i0 = min(V, (int)rank * slice), i1 = min(V, i0 + slice), n = i1 - i0;       // this CTA's tokens [i0, i1)
+    const float temp = temperature ? temperature[row] : 0.f;
+    const float tp = top_p ? top_p[row] : 1.f;
+    int parity = 0;
+    double mine[SC_VALS];
+
+    // ---- maximum (NaN skipped) with its first index
+    ArgBest best{-INFINITY, -1};
+    for (int i = i0 + tid; i < i1; i += SC_THREADS) {
+        const float v = x[i];
+        if (v == v) best = better(best, ArgBest{v, i});
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        ArgBest other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+        best = better(best, other);
+    }
+    if (lane == 0) { sh.warp_v[warp] = best.v; sh.warp_i[warp] = best.i; }
+    __syncthreads();
+    best = ArgBest{-INFINITY, -1};
+    for (int k = 0; k < SC_WARPS; ++k) best = better(best, ArgBest{sh.warp_v[k], sh.warp_i[k]});
+    mine[0] = (double)best.v; mine[1] = (double)best.i;
+    sc_all_gather(sh, parity, rank, mine, 2);
+    best = ArgBest{-INFINITY, -1};
+    for (int c = 0; c < SC_CTAS; ++c) best = better(best, ArgBest{(float)sh.gather[parity][c][0], (int)sh.gather[parity][c][1]});
+    parity ^= 1;
+    if (!(temp > 0.f) || !(tp > 0.f) || best.i < 0) {
+        if (rank == 0 && tid == 0) out[row] = best.i;
+        return;                                    // (uniform over the cluster; nobody writes into a peer after the barrier above)
+    }
+    // the reference takes the max over FINITE values only (an all -inf/+inf row gives -1)
+    float max_v = best.v;
+    if (isinf(max_v)) {                            // (uniform over the cluster)
+        float fm = -INFINITY; int any = 0;
+        for (int i = i0 + tid; i < i1; i += SC_THREADS) { const float v = x[i]; if (isfinite(v)) { fm = fmaxf(fm, v); any = 1; } }
+        fm = vm_warp_max(fm); any = __any_sync(0xffffffffu, any);
+        __syncthreads();
+        if (lane == 0) { sh.warp_v[warp] = fm; sh.warp_i[warp] = any; }
+        __syncthreads();
+        fm = -INFINITY; any = 0;
+        for (int k = 0; k < SC_WARPS; ++k) { fm = fmaxf(fm, sh.warp_v[k]); any |= sh.warp_i[k]; }
+        mine[0] = (double)fm; mine[1] = (double)any;
+        sc_all_gather(sh, parity, rank, mine, 2);
+        fm = -INFINITY; any = 0;
+        for (int c = 0; c < SC_CTAS; ++c) { fm = fmaxf(fm, (float)sh.gather[parity][c][0]); any |= (int)sh.gather[parity][c][1]; }
+        parity ^= 1;
+        if (!any) { if (rank == 0 && tid == 0) out[row] = -1; return; }
+        max_v = fm;
+    }
+    // ---- unnormalised probabilities of this slice (negative for a NaN logit) and their sum
+    const float inv_t = 1.0f / temp;
+    double part = 0.0;
+    for (int j = tid; j < n; j += SC_THREADS) {
+        const float v = x[i0 + j];
+        const float r = (v != v) ? -1.f : expf((v - max_v) * inv_t);
+        sraw[j] = r;
+        part += (double)(r < 0.f ? 0.f : r);
+    }
+    mine[0] = part;
+    sc_block_sum(sh, mine, 1);
+    sc_all_gather(sh, parity, rank, mine, 1);
+    double total = 0.0;
+    for (int c = 0; c < SC_CTAS; ++c) total += sh.gather[parity][c][0];
+    parity ^= 1;
+    const float inv_sum = (float)(1.0 / total);
+    auto prob = [&](int j) -> float { const float r = sraw[j]; return r < 0.f ? -1.f : r * inv_sum; };
+
+    // ---- nucleus threshold: the largest tau with sum{p_i >= tau} >= top_p (eight-way search on the float bits: what a
+    //      pass costs here is its cluster barrier, so few passes with several thresholds each)
+    float tau = 0.f;
+    if (tp < 1.0f) {
+        float pmax = 0.f;
+        for (int j = tid; j < n; j += SC_THREADS) pmax = fmaxf(pmax, prob(j));
+        pmax = vm_warp_max(pmax);
+        __syncthreads();
+        if (lane == 0) sh.warp_v[warp] = pmax;
+        __syncthreads();
+        pmax = 0.f;
+        for (int k = 0; k < SC_WARPS; ++k) pmax = fmaxf(pmax, sh.warp_v[k]);
+        mine[0] = (double)pmax;
+        sc_all_gather(sh, parity, rank, mine, 1);
+        pmax = 0.f;
+        for (int c = 0; c < SC_CTAS; ++c) pmax = fmaxf(pmax, (float)sh.gather[parity][c][0]);
+        parity ^= 1;
+        uint32_t lo = 0u, hi = __float_as_uint(pmax) + 1u;   // cond(lo) holds or tau stays 0; cond(hi) fails
+        double above = 0.0;                                   // the mass of p >= hi: known from the pass that lowered hi
+        while (hi - lo > 1u) {                                // (the same trip count in every CTA: the sums are the same)
+            const uint32_t stepw = (hi - lo + SC_WAYS) / (SC_WAYS + 1);
+            float th[SC_WAYS];
+            double sj[SC_VALS];
+#pragma unroll
+            for (int k = 0; k < SC_VALS; ++k) sj[k] = 0.0;
+#pragma unroll
+            for (int k = 0; k < SC_WAYS; ++k) {
+                const unsigned long long t = (unsigned long long)lo + (unsigned long long)(k + 1) * stepw;
+                th[k] = (t < (unsigned long long)hi) ? __uint_as_float((uint32_t)t) : INFINITY;
+            }
+            const float f_lo = __uint_as_float(lo + stepw), f_hi = __uint_as_float(hi);
+            for (int j = tid; j < n; j += SC_THREADS) {
+                const float p = prob(j);
+                if (p >= f_lo && p < f_hi) {                 // only what lies between the thresholds is summed again
+                    const double pd = (double)p;
+#pragma unroll
+                    for (int k = 0; k < SC_WAYS; ++k) if (p >= th[k]) sj[k] += pd;
+                }
+            }
+            sc_block_sum(sh, sj, SC_WAYS);
+            sc_all_gather(sh, parity, rank, sj, SC_WAYS);
+            uint32_t new_lo = lo, new_hi = hi;
+            double new_above = above;
+#pragma unroll
+            for (int k = 0; k < SC_WAYS; ++k) {
+                const unsigned long long t = (unsigned long long)lo + (unsigned long long)(k + 1) * stepw;
+                if (t < (unsigned long long)new_hi) {
+                    double sum = above;                       // mass of p >= t: what lies above hi, plus [t, hi)
+                    for (int c = 0; c < SC_CTAS; ++c) sum += sh.gather[parity][c][k];
+                    if (sum >= (double)tp) new_lo = (uint32_t)t; else { new_hi = (uint32_t)t; new_above = sum; }
+                }
+            }
+            parity ^= 1;
+            lo = new_lo; hi = new_hi; above = new_above;
+        }
+        tau = __uint_as_float(lo);
+    }
+
+    // ---- mass of the nucleus and the walk in index order: running sums over the threads' chunks, the CTAs in rank order
+    const int chunk = (n + SC_THREADS - 1) / SC_THREADS;
+    const int j0 = min(n, tid * chunk), j1 = min(n, j0 + chunk);
+    double my_mass = 0.0;
+    for (int j = j0; j < j1; ++j) { const float p = prob(j); if (p >= 0.f && p >= tau) my_mass += (double)p; }
+    double incl = my_mass;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const double up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+    }
+    __syncthreads();
+    if (lane == 31) sh.warp_d[warp][0] = incl;
+    if (tid == 0) sh.choice = 0x7fffffff;
+    __syncthreads();
+    double offset = 0.0, cta_mass = 0.0;
+    for (int k = 0; k < SC_WARPS; ++k) { const double t = sh.warp_d[k][0]; if (k < warp) offset += t; cta_mass += t; }
+    mine[0] = cta_mass;
+    sc_all_gather(sh, parity, rank, mine, 1);
+    double mass = 0.0, cta_before = 0.0;
+    for (int c = 0; c < SC_CTAS; ++c) { const double t = sh.gather[parity][c][0]; if (c < (int)rank) cta_before += t; mass += t; }
+    parity ^= 1;
+    uint32_t c4[4];
+    const unsigned long long st = (unsigned long long)(step ? step[row] : 0), sid = (unsigned long long)(stream_id ? stream_id[row] : 0);
+    const unsigned long long sd = (unsigned long long)(seed ? seed[row] : 0);
+    c4[0] = (uint32_t)st; c4[1] = (uint32_t)(st >> 32); c4[2] = (uint32_t)sid; c4[3] = (uint32_t)(sid >> 32);
+    philox4x32_10(c4, (uint32_t)sd, (uint32_t)(sd >> 32));
+    const float u = (float)(c4[0] >> 8) * (1.0f / 16777216.0f);
+    const double r = (double)u * mass;
+    // the chunk in which the running sum first reaches r walks its members; the last member overall is kept as well
+    const double before = cta_before + offset + incl - my_mass;
+    int last_member = -1;
+    for (int j = j1 - 1; j >= j0; --j) { const float p = prob(j); if (p >= 0.f && p >= tau) { last_member = i0 + j; break; } }
+    if (before <= r) {
+        double acc = before;
+        for (int j = j0; j < j1; ++j) {
+            const float p = prob(j);
+            if (p >= 0.f && p >= tau) {
+                acc += (double)p;
+                if (acc >= r) { atomicMin(&sh.choice, i0 + j); break; }
+            }
+        }
+    }
+    last_member = max(last_member, __shfl_xor_sync(0xffffffffu, last_member, 16));
+    last_member = max(last_member, __shfl_xor_sync(0xffffffffu, last_member, 8));
+    last_member = max(last_member, __shfl_xor_sync(0xffffffffu, last_member, 4));
+    last_member = max(last_member, __shfl_xor_sync(0xffffffffu, last_member, 2));
+    last_member = max(last_member, __shfl_xor_sync(0xffffffffu, last_member, 1));
+    __syncthreads();
+    if (lane == 0) sh.warp_i[warp] = last_member;
+    __syncthreads();
+    last_member = -1;
+    for (int k = 0; k < SC_WARPS; ++k) last_member = max(last_member, sh.warp_i[k]);
+    mine[0] = (double)sh.choice; mine[1] = (double)last_member;
+    sc_all_gather(sh, parity, rank, mine, 2);
+    if (rank == 0 && tid == 0) {
+        int choice = 0x7fffffff, last = -1;
+        for (int c = 0; c < SC_CTAS; ++c) { choice = min(choice, (int)sh.gather[parity][c][0]); last = max(last, (int)sh.gather[parity][c][1]); }
+        out[row] = (choice == 0x7fffffff) ? last : choice;    // rounding left the running sum short of r: the last member
+    }
+}
+
 constexpr int SAMPLE_CACHE_LIMIT = 200 * 1024;      // bytes of dynamic shared memory for a row's probabilities
+constexpr int SC_CLUSTER_MIN_VOCAB = 8192;        // from this many tokens on, and ...
+constexpr int SC_CLUSTER_MAX_ROWS = 64;           // ... up to this many rows, a cluster of CTAs samples a row
 
 VM_API int vm_sample(const float* logits, long long row_stride, int R, int V, const float* temperature,
                      const float* top_p, const long long* seed, const long long* stream_id, const long long* step,
@@ -268,6 +530,22 @@ VM_API int vm_sample(const float* logits, long long row_stride, int R, int V, co
     if (R <= 0) return 0;
     if (V <= 0) return VM_ERR_BAD_ARG;
     const size_t cache = (size_t)V * sizeof(float);
+    if (V >= SC_CLUSTER_MIN_VOCAB && R <= SC_CLUSTER_MAX_ROWS) {
+        // large vocabulary, few rows: eight CTAs per row
+        const int slice = ((V + SC_CTAS - 1) / SC_CTAS + 3) / 4 * 4;
+        const size_t smem = (size_t)slice * sizeof(float);
+        if (smem <= SAMPLE_CACHE_LIMIT) {
+            static bool configured_c = false;
+            if (!configured_c) {
+                cudaError_t e = cudaFuncSetAttribute(sample_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SAMPLE_CACHE_LIMIT);
+                if (e != cudaSuccess) return (int)e;
+                configured_c = true;
+            }
+            sample_cluster_kernel<<<R * SC_CTAS, SC_THREADS, smem, stream>>>(logits, row_stride, V, slice, temperature, top_p, seed,
+                                                                           stream_id, step, out);
+            return vm_launch_status();
+        }
+    }
     if (cache <= SAMPLE_CACHE_LIMIT) {
         static bool configured = false;
         if (!configured) {
