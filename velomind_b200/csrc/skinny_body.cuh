@@ -33,7 +33,8 @@ struct SkinnyParams {
 
 // `item` is the work item (what item_index is for the stand-alone kernel); `smem` the CTA's dynamic shared memory.
 // PDL: launched with programmatic dependent launch (weights may be fetched before the predecessor has finished).
-template <int MT, bool PDL>
+// PF: k blocks of 32 that a warp keeps in flight (8 warps x PF x 32 values of K per round).
+template <int MT, bool PDL, int PF = 8>
 __device__ __forceinline__ void skinny_body(const SkinnyParams& p, const int item_index, unsigned char* smem) {
     constexpr int ROWS = 16 * MT;
     unsigned char* sA = smem;                                              // ROWS x row_bytes
@@ -60,7 +61,6 @@ __device__ __forceinline__ void skinny_body(const SkinnyParams& p, const int ite
 
     // ---- weight fragments do not depend on A: the first group of this warp's k blocks is requested before
     //      anything else, so that its DRAM latency overlaps the staging of A
-    constexpr int PF = 8;                                   // k blocks in flight per warp
     uint4 wa[PF], wb[PF];
     auto issue = [&](int kc0, int blocks, int group) {
 #pragma unroll
@@ -74,7 +74,25 @@ __device__ __forceinline__ void skinny_body(const SkinnyParams& p, const int ite
         }
     };
     issue(0, min(p.kc, p.K) / 32, 0);
+    // the rotary frequencies of this thread's output column are constants of the model too
+    float freq = 0.f;
+    if (p.epi == EPI_ROPE_KV && head < p.H + p.Hkv && p.rot_dim > 0) freq = p.inv_freq[(nA - head * p.D) + (tid & 7)];
     if (PDL) vm_pdl_wait();                                 // from here on: data written by earlier kernels
+    // the residual values this thread will add to are requested now: their latency passes under the product
+    float res_a[MT], res_b[MT];
+    if (p.epi == EPI_RESIDUAL) {
+#pragma unroll
+        for (int i = 0; i < MT; ++i) {
+            const int item = tid + SK_THREADS * i;
+            const int row = item >> 3, c = item & 7;
+            res_a[i] = res_b[i] = 0.f;
+            if (item < ROWS * 8 && row < p.M) {
+                const float* o = p.h + (size_t)row * p.N;      // from L2: another SM wrote it
+                res_a[i] = __ldcg(o + nA + c);
+                if (two) res_b[i] = __ldcg(o + nB + c);
+            }
+        }
+    }
     // the epilogue's per-row facts (position, cache page) are fetched now, long before they are needed
     int row_pos[MT], row_page[MT];
     if (p.epi == EPI_ROPE_KV) {
@@ -104,13 +122,13 @@ __device__ __forceinline__ void skinny_body(const SkinnyParams& p, const int ite
         if (kc0 > 0) __syncthreads();                       // the previous chunk has been consumed
         // ---- stage A[:, kc0 : kc0+kc] as bf16
         if (p.pro == PRO_NONE) {
+            // (rows past M are never read: their fragments are zeros in registers)
             const __nv_bfloat16* A = static_cast<const __nv_bfloat16*>(p.A);
             const int chunks = kc / 8;
-            for (int c = tid; c < ROWS * chunks; c += SK_THREADS) {
-                const int r = c / chunks, ch = c - r * chunks;
-                unsigned char* dst = sA + (size_t)r * p.row_bytes + ch * 16;
-                if (r < p.M) vm_cp_async16(dst, A + (size_t)r * p.K + kc0 + ch * 8);
-                else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+            for (int r = warp; r < p.M; r += SK_WARPS) {
+                unsigned char* dst = sA + (size_t)r * p.row_bytes;
+                const __nv_bfloat16* src = A + (size_t)r * p.K + kc0;
+                for (int ch = lane; ch < chunks; ch += 32) vm_cp_async16(dst + ch * 16, src + ch * 8);
             }
             vm_cp_async_commit();
             vm_cp_async_wait_all();
@@ -119,24 +137,21 @@ __device__ __forceinline__ void skinny_body(const SkinnyParams& p, const int ite
             // commutes with the product); a warp owns whole rows and sums their squares on the way
             const float* h = static_cast<const float*>(p.A);
             const int quads = kc / 4;
-            for (int r = warp; r < ROWS; r += SK_WARPS) {
+            for (int r = warp; r < p.M; r += SK_WARPS) {
                 unsigned char* dst = sA + (size_t)r * p.row_bytes;
-                if (r >= p.M) {
-                    for (int qd = lane; qd < quads; qd += 32) *reinterpret_cast<uint2*>(dst + qd * 8) = make_uint2(0u, 0u);
-                    continue;
-                }
                 const float4* hrow = reinterpret_cast<const float4*>(h + (size_t)r * p.K + kc0);
                 const float4* wrow = reinterpret_cast<const float4*>(p.norm_w + kc0);
                 float ss = 0.f;
-                for (int q0 = lane; q0 < quads; q0 += 32 * 4) {
-                    float4 x[4], w[4];
+                constexpr int NU = PF <= 4 ? 5 : 4;        // loads in flight per lane (5: a row of up to 640 values in one round)
+                for (int q0 = lane; q0 < quads; q0 += 32 * NU) {
+                    float4 x[NU], w[NU];
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
+                    for (int u = 0; u < NU; ++u) {
                         const int qd = q0 + 32 * u;
                         if (qd < quads) { x[u] = __ldcg(hrow + qd); w[u] = wrow[qd]; }     // h: from L2, another SM may have written it
                     }
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
+                    for (int u = 0; u < NU; ++u) {
                         const int qd = q0 + 32 * u;
                         if (qd < quads) {
                             ss += x[u].x * x[u].x + x[u].y * x[u].y + x[u].z * x[u].z + x[u].w * x[u].w;
@@ -162,8 +177,9 @@ __device__ __forceinline__ void skinny_body(const SkinnyParams& p, const int ite
                 if (b < blocks) {
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) {
-                        const uint4 a_lo = *reinterpret_cast<const uint4*>(sA + (size_t)(mt * 16 + g) * p.row_bytes + (32 * b + 8 * t4) * 2);
-                        const uint4 a_hi = *reinterpret_cast<const uint4*>(sA + (size_t)(mt * 16 + g + 8) * p.row_bytes + (32 * b + 8 * t4) * 2);
+                        uint4 a_lo = make_uint4(0u, 0u, 0u, 0u), a_hi = a_lo;
+                        if (mt * 16 + g < p.M) a_lo = *reinterpret_cast<const uint4*>(sA + (size_t)(mt * 16 + g) * p.row_bytes + (32 * b + 8 * t4) * 2);
+                        if (mt * 16 + g + 8 < p.M) a_hi = *reinterpret_cast<const uint4*>(sA + (size_t)(mt * 16 + g + 8) * p.row_bytes + (32 * b + 8 * t4) * 2);
                         vm_mma_bf16_16816(acc[mt][0], a_lo.x, a_hi.x, a_lo.y, a_hi.y, wa[u].x, wa[u].y);
                         vm_mma_bf16_16816(acc[mt][0], a_lo.z, a_hi.z, a_lo.w, a_hi.w, wa[u].z, wa[u].w);
                         if (two) {
@@ -181,9 +197,11 @@ __device__ __forceinline__ void skinny_body(const SkinnyParams& p, const int ite
 #pragma unroll
         for (int t = 0; t < 2; ++t)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int row = mt * 16 + g + 8 * (e >> 1), col = t * 8 + 2 * t4 + (e & 1);
-                red[((size_t)warp * ROWS + row) * 16 + col] = acc[mt][t][e];
+            for (int half = 0; half < 2; ++half) {
+                const int row = mt * 16 + g + 8 * half;
+                if (row < p.M && (t == 0 || two))
+                    *reinterpret_cast<float2*>(&red[((size_t)warp * ROWS + row) * 16 + t * 8 + 2 * t4]) =
+                        make_float2(acc[mt][t][2 * half], acc[mt][t][2 * half + 1]);
             }
     __syncthreads();
 #pragma unroll
@@ -196,7 +214,7 @@ __device__ __forceinline__ void skinny_body(const SkinnyParams& p, const int ite
 #pragma unroll
         for (int w = 0; w < SK_WARPS; ++w) {
             vA += red[((size_t)w * ROWS + row) * 16 + c];
-            vB += red[((size_t)w * ROWS + row) * 16 + 8 + c];
+            if (two) vB += red[((size_t)w * ROWS + row) * 16 + 8 + c];
         }
         if (p.pro == PRO_RMSNORM) {
             const float rs = 1.0f / sqrtf(inv[row] / (float)p.K + p.eps);       // inv[] holds the row's sum of squares
@@ -214,9 +232,9 @@ __device__ __forceinline__ void skinny_body(const SkinnyParams& p, const int ite
                 if (two) o[nB + c] = vB;
             } break;
             case EPI_RESIDUAL: {
-                float* o = p.h + (size_t)row * p.N;          // read from L2: another SM may have written h earlier in a persistent kernel
-                o[nA + c] = __ldcg(o + nA + c) + vA;
-                if (two) o[nB + c] = __ldcg(o + nB + c) + vB;
+                float* o = p.h + (size_t)row * p.N;
+                o[nA + c] = res_a[it] + vA;
+                if (two) o[nB + c] = res_b[it] + vB;
             } break;
             case EPI_SWIGLU: {
                 const float sig = 1.0f / (1.0f + expf(-vA));
@@ -229,7 +247,7 @@ __device__ __forceinline__ void skinny_body(const SkinnyParams& p, const int ite
                 if (head < p.H + p.Hkv && p.rot_dim > 0) {
                     da = (nA - head * p.D) + c; db = da + p.D / 2;
                     float s, co;
-                    sincosf((float)pos * p.inv_freq[da], &s, &co);
+                    sincosf((float)pos * freq, &s, &co);
                     ya = vA * co - vB * s;
                     yb = vB * co + vA * s;
                 } else { da = (nA - head * p.D) + c; db = da + 8; }
@@ -281,11 +299,10 @@ __device__ __forceinline__ void skinny_wide_body(const SkinnyParams& p, const in
     {
         const __nv_bfloat16* A = static_cast<const __nv_bfloat16*>(p.A);
         const int chunks = p.K / 8;
-        for (int c = tid; c < ROWS * chunks; c += SK_THREADS) {
-            const int r = c / chunks, ch = c - r * chunks;
-            unsigned char* dst = sA + (size_t)r * p.row_bytes + ch * 16;
-            if (r < p.M) vm_cp_async16(dst, A + (size_t)r * p.K + ch * 8);
-            else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+        for (int r = warp; r < p.M; r += SK_WARPS) {         // rows past M are never read
+            unsigned char* dst = sA + (size_t)r * p.row_bytes;
+            const __nv_bfloat16* src = A + (size_t)r * p.K;
+            for (int ch = lane; ch < chunks; ch += 32) vm_cp_async16(dst + ch * 16, src + ch * 8);
         }
         vm_cp_async_commit();
         vm_cp_async_wait_all();
@@ -299,8 +316,9 @@ __device__ __forceinline__ void skinny_wide_body(const SkinnyParams& p, const in
             if (live && b < blocks) {
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
-                    const uint4 a_lo = *reinterpret_cast<const uint4*>(sA + (size_t)(mt * 16 + g) * p.row_bytes + (32 * b + 8 * t4) * 2);
-                    const uint4 a_hi = *reinterpret_cast<const uint4*>(sA + (size_t)(mt * 16 + g + 8) * p.row_bytes + (32 * b + 8 * t4) * 2);
+                    uint4 a_lo = make_uint4(0u, 0u, 0u, 0u), a_hi = a_lo;
+                    if (mt * 16 + g < p.M) a_lo = *reinterpret_cast<const uint4*>(sA + (size_t)(mt * 16 + g) * p.row_bytes + (32 * b + 8 * t4) * 2);
+                    if (mt * 16 + g + 8 < p.M) a_hi = *reinterpret_cast<const uint4*>(sA + (size_t)(mt * 16 + g + 8) * p.row_bytes + (32 * b + 8 * t4) * 2);
                     vm_mma_bf16_16816(acc[mt], a_lo.x, a_hi.x, a_lo.y, a_hi.y, wa[u].x, wa[u].y);
                     vm_mma_bf16_16816(acc[mt], a_lo.z, a_hi.z, a_lo.w, a_hi.w, wa[u].z, wa[u].w);
                 }

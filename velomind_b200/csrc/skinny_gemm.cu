@@ -26,11 +26,12 @@ namespace {
 using namespace vmsk;
 
 // (two CTAs per SM for up to 16 rows: 192 gate/up items then fit the GPU at once)
-template <int MT>
+// (PF: weight blocks a warp keeps in flight; 4 cover K <= 1,024 in one round and leave registers to the prologue)
+template <int MT, int PF>
 __global__ void __launch_bounds__(SK_THREADS, MT == 1 ? 2 : 1)
 skinny_gemm_kernel(const SkinnyParams p) {
     extern __shared__ __align__(16) unsigned char smem[];
-    skinny_body<MT, true>(p, blockIdx.x, smem);
+    skinny_body<MT, true, PF>(p, blockIdx.x, smem);
 }
 
 template <int MT>
@@ -82,17 +83,22 @@ int skinny_launch(SkinnyParams p, int grid, cudaStream_t stream) {
     pitch += ((64 - pitch % 128) + 128) % 128;
     p.row_bytes = pitch;
     const size_t smem = (size_t)rows * pitch + (size_t)SK_WARPS * rows * 16 * sizeof(float) + rows * sizeof(float);
-#define VM_SK_CASE(X)                                                                                                 \
-    case X: {                                                                                                         \
+    const bool few = kc <= SK_WARPS * 32 * 4;
+#define VM_SK_CASE(X, P)                                                                                              \
+    {                                                                                                                 \
         static size_t configured = 0;                                                                                 \
         if (smem > 48 * 1024 && smem > configured) {                                                                  \
-            cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<X>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); \
+            cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<X, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); \
             if (e != cudaSuccess) return (int)e;                                                                      \
             configured = 160 * 1024;                                                                                  \
         }                                                                                                             \
-        vm_launch_pdl(skinny_gemm_kernel<X>, dim3(grid), dim3(SK_THREADS), smem, stream, p);                          \
-    } break;
-    switch (MT) { VM_SK_CASE(1) VM_SK_CASE(2) VM_SK_CASE(4) }
+        vm_launch_pdl(skinny_gemm_kernel<X, P>, dim3(grid), dim3(SK_THREADS), smem, stream, p);                       \
+    }
+    switch (MT) {
+        case 1: if (few) VM_SK_CASE(1, 4) else VM_SK_CASE(1, 8) break;
+        case 2: if (few) VM_SK_CASE(2, 4) else VM_SK_CASE(2, 8) break;
+        case 4: if (few) VM_SK_CASE(4, 4) else VM_SK_CASE(4, 8) break;
+    }
 #undef VM_SK_CASE
     return vm_launch_status();
 }
