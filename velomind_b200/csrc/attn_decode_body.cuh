@@ -27,7 +27,11 @@ attn_decode_body(const __nv_bfloat16* __restrict__ q, int q_row_stride, const __
     __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);                    // [16][DP]
     __nv_bfloat16* sKV = sQ + DEC_ROWS * DP;                                            // [warps][K,V][64][DP]
     float* res = reinterpret_cast<float*>(sKV + DEC_WARPS * 2 * BN * DP);               // [warps][16][RW]
-    if (PDL) { vm_pdl_launch_dependents(); vm_pdl_wait(); }
+    if (PDL) vm_pdl_launch_dependents();
+    // Before the wait this kernel reads what OLDER steps and kernels wrote: positions, the block table and the cache
+    // rows of earlier tokens.  That is sound because the kernel launched directly before it (the one that writes the
+    // new token's row) lets its dependents start only after its own wait, when everything older is complete.  The
+    // new row and the queries, which that kernel writes, are fetched after the wait.
     const int G = H / Hkv;
     const int groups_per_kv = (G + DEC_ROWS - 1) / DEC_ROWS;
     const int hk = group_y / groups_per_kv, gg = group_y - hk * groups_per_kv;
@@ -44,14 +48,10 @@ attn_decode_body(const __nv_bfloat16* __restrict__ q, int q_row_stride, const __
     const int* table = block_table + (size_t)b * max_blocks;
     __nv_bfloat16* ks = sKV + (size_t)warp * 2 * BN * DP;
     __nv_bfloat16* vs = ks + BN * DP;
+    const int new_row = pos - last_page * BN;              // the row of the last page that this step's token takes
 
-    // ---- the queries of this CTA's heads (rows past the last head are zero)
-    for (int c = tid; c < DEC_ROWS * CH; c += DEC_WARPS * 32) {
-        const int r = c / CH, ch = c - r * CH;
-        if (r < ng) vm_cp_async16(sQ + r * DP + ch * 8, q + (size_t)b * q_row_stride + (size_t)(h0 + r) * D + ch * 8);
-        else *reinterpret_cast<uint4*>(sQ + r * DP + ch * 8) = make_uint4(0u, 0u, 0u, 0u);
-    }
-    auto load_page = [&](int blk) -> bool {                // the calling warp fetches K and V of one page
+    // the calling warp fetches K and V of one page; skip >= 0: all rows but that one
+    auto load_page = [&](int blk, int skip) -> bool {
         const int page = (blk < max_blocks) ? table[blk] : -1;
         if (page < 0 || page >= n_pages) { if (lane == 0 && err) atomicExch(err, 3); return false; }
         const __nv_bfloat16* kg = kpages + (size_t)page * page_stride + (size_t)hk * BN * D;
@@ -59,13 +59,31 @@ attn_decode_body(const __nv_bfloat16* __restrict__ q, int q_row_stride, const __
 #pragma unroll 4
         for (int c = lane; c < BN * CH; c += 32) {
             const int r = c / CH, ch = c - r * CH;
-            vm_cp_async16(ks + r * DP + ch * 8, kg + r * D + ch * 8);
-            vm_cp_async16(vs + r * DP + ch * 8, vg + r * D + ch * 8);
+            if (r != skip) {
+                vm_cp_async16(ks + r * DP + ch * 8, kg + r * D + ch * 8);
+                vm_cp_async16(vs + r * DP + ch * 8, vg + r * D + ch * 8);
+            }
         }
         return true;
     };
     int blk = page_a + warp;
-    bool have = (blk < page_b) && load_page(blk);
+    bool have = (blk < page_b) && load_page(blk, PDL && blk == last_page ? new_row : -1);
+    vm_cp_async_commit();
+    if (PDL) {
+        vm_pdl_wait();
+        if (have && blk == last_page && lane < 2 * CH) {   // the new token's key and value
+            const int page = table[blk];
+            const size_t at = (size_t)page * page_stride + ((size_t)hk * BN + new_row) * D + (lane % CH) * 8;
+            if (lane < CH) vm_cp_async16(ks + new_row * DP + lane * 8, kpages + at);
+            else vm_cp_async16(vs + new_row * DP + (lane - CH) * 8, vpages + at);
+        }
+    }
+    // ---- the queries of this CTA's heads (rows past the last head are zero)
+    for (int c = tid; c < DEC_ROWS * CH; c += DEC_WARPS * 32) {
+        const int r = c / CH, ch = c - r * CH;
+        if (r < ng) vm_cp_async16(sQ + r * DP + ch * 8, q + (size_t)b * q_row_stride + (size_t)(h0 + r) * D + ch * 8);
+        else *reinterpret_cast<uint4*>(sQ + r * DP + ch * 8) = make_uint4(0u, 0u, 0u, 0u);
+    }
     vm_cp_async_commit();
     vm_cp_async_wait_all();
     __syncthreads();                                       // the queries (fetched by all threads) are in place
@@ -143,7 +161,7 @@ attn_decode_body(const __nv_bfloat16* __restrict__ q, int q_row_stride, const __
         blk += DEC_WARPS;
         if (blk < page_b) {
             __syncwarp();                                  // every lane is done with the page before it is overwritten
-            have = load_page(blk);
+            have = load_page(blk, -1);
             vm_cp_async_commit();
             vm_cp_async_wait_all();
             __syncwarp();

@@ -41,7 +41,8 @@ __device__ __forceinline__ void skinny_body(const SkinnyParams& p, const int ite
     float* red = reinterpret_cast<float*>(smem + (size_t)ROWS * p.row_bytes);   // [SK_WARPS][ROWS][16]
     float* inv = red + SK_WARPS * ROWS * 16;                               // [ROWS]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
-    if (PDL) vm_pdl_launch_dependents();
+    // (the kernel that writes the cache lets its successor, the attention, start only after its own wait: see there)
+    if (PDL && p.epi != EPI_ROPE_KV) vm_pdl_launch_dependents();
 
     // ---- which output columns
     int nA, nB, head = 0;
@@ -78,6 +79,7 @@ __device__ __forceinline__ void skinny_body(const SkinnyParams& p, const int ite
     float freq = 0.f;
     if (p.epi == EPI_ROPE_KV && head < p.H + p.Hkv && p.rot_dim > 0) freq = p.inv_freq[(nA - head * p.D) + (tid & 7)];
     if (PDL) vm_pdl_wait();                                 // from here on: data written by earlier kernels
+    if (PDL && p.epi == EPI_ROPE_KV) vm_pdl_launch_dependents();
     // the residual values this thread will add to are requested now: their latency passes under the product
     float res_a[MT], res_b[MT];
     if (p.epi == EPI_RESIDUAL) {
