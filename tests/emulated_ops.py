@@ -104,9 +104,9 @@ def linear(x, weight, out):
     out.copy_((x.float() @ weight.float().t()).to(out.dtype))
 
 
-def sample(logits, temperature, top_p, seed, stream_id, step, out):
+def sample(logits, temperature, top_p, seed, stream_id, step, out, step_add=0):
     for r in range(logits.shape[0]):
-        u = P.uniform01(int(seed[r]), int(stream_id[r]), int(step[r]))
+        u = P.uniform01(int(seed[r]), int(stream_id[r]), int(step[r]) + int(step_add))
         out[r] = P.sample_top_p(logits[r].numpy(), float(temperature[r]), float(top_p[r]), u)
 
 
@@ -149,6 +149,7 @@ def install(monkeypatch):
     monkeypatch.setattr(step, "CLUSTER_DEFAULT", False)
     monkeypatch.setattr(step, "_host_buffer", lambda n, dtype: torch.empty(n, dtype=dtype))
     monkeypatch.setattr(step, "_new_event", lambda: _Event())
+    monkeypatch.setattr(step, "_upload", lambda dev, host, event: dev.copy_(host))
     monkeypatch.setattr(step, "_sync_stream", lambda: None)
     monkeypatch.setattr(sampler, "_host_buffer", lambda shape, dtype: torch.empty(shape, dtype=dtype))
     monkeypatch.setattr(sampler, "_sync", lambda: None)

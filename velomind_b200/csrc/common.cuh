@@ -48,6 +48,12 @@ __device__ __forceinline__ float vm_block_sum(float v, float* red) {
 // vm_pdl_wait() before it reads anything an earlier kernel wrote and before its first global write.
 // vm_pdl_launch_dependents() lets the successor start its own preamble.  Without the launch attribute both
 // are no-ops.
+// One kernel reads more than constants in its preamble: the decode attention fetches positions, the block table
+// and the cache rows of EARLIER tokens there.  The rule that makes this sound: the kernel launched directly
+// before it (the one that writes the new token's key and value) calls vm_pdl_launch_dependents() only AFTER its
+// own vm_pdl_wait(), so when the attention's preamble runs, everything older than that kernel is complete and
+// visible; what that kernel itself writes (the new row, the queries) is read after the attention's wait.
+// Kernels launched without the attribute (and library kernels) never release their successor early.
 __device__ __forceinline__ void vm_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void vm_pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

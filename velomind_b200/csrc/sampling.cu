@@ -57,7 +57,7 @@ template <bool CACHED>
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, long long row_stride, int V, const float* __restrict__ temperature,
               const float* __restrict__ top_p, const long long* __restrict__ seed, const long long* __restrict__ stream_id,
-              const long long* __restrict__ step, int* __restrict__ out) {
+              const long long* __restrict__ step, long long step_add, int* __restrict__ out) {
     extern __shared__ __align__(16) float sraw[];
     __shared__ double redd[32];
     __shared__ float redv[32];
@@ -231,7 +231,7 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int V, con
     sums[tid] = offset + incl - mine;
     __syncthreads();
     uint32_t c[4];
-    const unsigned long long st = (unsigned long long)(step ? step[row] : 0), sid = (unsigned long long)(stream_id ? stream_id[row] : 0);
+    const unsigned long long st = (unsigned long long)((step ? step[row] : 0) + step_add), sid = (unsigned long long)(stream_id ? stream_id[row] : 0);
     const unsigned long long sd = (unsigned long long)(seed ? seed[row] : 0);
     c[0] = (uint32_t)st; c[1] = (uint32_t)(st >> 32); c[2] = (uint32_t)sid; c[3] = (uint32_t)(sid >> 32);
     philox4x32_10(c, (uint32_t)sd, (uint32_t)(sd >> 32));
@@ -325,7 +325,7 @@ __global__ void __cluster_dims__(SC_CTAS, 1, 1) __launch_bounds__(SC_THREADS)
 sample_cluster_kernel(const float* __restrict__ logits, long long row_stride, int V, int slice,
                       const float* __restrict__ temperature, const float* __restrict__ top_p,
                       const long long* __restrict__ seed, const long long* __restrict__ stream_id,
-                      const long long* __restrict__ step, int* __restrict__ out) {
+                      const long long* __restrict__ step, long long step_add, int* __restrict__ out) {
     extern __shared__ __align__(16) float sraw[];                   // this CTA's slice of unnormalised probabilities
     __shared__ ScShared sh;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -481,7 +481,7 @@ sample_cluster_kernel(const float* __restrict__ logits, long long row_stride, in
     for (int c = 0; c < SC_CTAS; ++c) { const double t = sh.gather[parity][c][0]; if (c < (int)rank) cta_before += t; mass += t; }
     parity ^= 1;
     uint32_t c4[4];
-    const unsigned long long st = (unsigned long long)(step ? step[row] : 0), sid = (unsigned long long)(stream_id ? stream_id[row] : 0);
+    const unsigned long long st = (unsigned long long)((step ? step[row] : 0) + step_add), sid = (unsigned long long)(stream_id ? stream_id[row] : 0);
     const unsigned long long sd = (unsigned long long)(seed ? seed[row] : 0);
     c4[0] = (uint32_t)st; c4[1] = (uint32_t)(st >> 32); c4[2] = (uint32_t)sid; c4[3] = (uint32_t)(sid >> 32);
     philox4x32_10(c4, (uint32_t)sd, (uint32_t)(sd >> 32));
@@ -524,9 +524,11 @@ constexpr int SAMPLE_CACHE_LIMIT = 200 * 1024;      // bytes of dynamic shared m
 constexpr int SC_CLUSTER_MIN_VOCAB = 8192;        // from this many tokens on, and ...
 constexpr int SC_CLUSTER_MAX_ROWS = 64;           // ... up to this many rows, a cluster of CTAs samples a row
 
+// The Philox counter of row r is step[r] + step_add: a caller whose rows all move on by the same number of draws
+// leaves its parameter block on the device untouched.
 VM_API int vm_sample(const float* logits, long long row_stride, int R, int V, const float* temperature,
                      const float* top_p, const long long* seed, const long long* stream_id, const long long* step,
-                     int* out, cudaStream_t stream) {
+                     long long step_add, int* out, cudaStream_t stream) {
     if (R <= 0) return 0;
     if (V <= 0) return VM_ERR_BAD_ARG;
     const size_t cache = (size_t)V * sizeof(float);
@@ -542,7 +544,7 @@ VM_API int vm_sample(const float* logits, long long row_stride, int R, int V, co
                 configured_c = true;
             }
             sample_cluster_kernel<<<R * SC_CTAS, SC_THREADS, smem, stream>>>(logits, row_stride, V, slice, temperature, top_p, seed,
-                                                                           stream_id, step, out);
+                                                                           stream_id, step, step_add, out);
             return vm_launch_status();
         }
     }
@@ -553,9 +555,9 @@ VM_API int vm_sample(const float* logits, long long row_stride, int R, int V, co
             if (e != cudaSuccess) return (int)e;
             configured = true;
         }
-        sample_kernel<true><<<R, SAMPLE_THREADS, cache, stream>>>(logits, row_stride, V, temperature, top_p, seed, stream_id, step, out);
+        sample_kernel<true><<<R, SAMPLE_THREADS, cache, stream>>>(logits, row_stride, V, temperature, top_p, seed, stream_id, step, step_add, out);
     } else {
-        sample_kernel<false><<<R, SAMPLE_THREADS, 0, stream>>>(logits, row_stride, V, temperature, top_p, seed, stream_id, step, out);
+        sample_kernel<false><<<R, SAMPLE_THREADS, 0, stream>>>(logits, row_stride, V, temperature, top_p, seed, stream_id, step, step_add, out);
     }
     return vm_launch_status();
 }

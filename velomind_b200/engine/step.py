@@ -57,7 +57,11 @@ def _host_buffer(n: int, dtype: torch.dtype) -> torch.Tensor:
 
 
 def _new_event():
-    return torch.cuda.Event()
+    return ops.CopyEvent()
+
+
+def _upload(dev: torch.Tensor, host: torch.Tensor, event) -> None:
+    ops.upload(dev, host, event)
 
 
 def _sync_stream() -> None:
@@ -85,6 +89,7 @@ class Descriptors:
         self.dev = torch.zeros(off, dtype=torch.int32, device=device)
         self.copied = _new_event()
         self.used = False
+        self.next_decode = None            # what a decode step described ahead of its tokens rests on (Engine._describe_next_decode)
         self.decode_slots = None           # the slots whose plain decode step the buffer describes (Engine._step_decode) ...
         self.decode_versions = None        # ... and the block tables' versions it was filled at
 
@@ -97,8 +102,7 @@ class Descriptors:
         return self.dev[off: off + n]
 
     def upload(self) -> None:
-        self.dev.copy_(self.host, non_blocking=True)
-        self.copied.record()
+        _upload(self.dev, self.host, self.copied)
         self.used = True
 
     def wait_reusable(self) -> None:
@@ -203,6 +207,8 @@ class Engine:
         self._desc: Dict[Tuple, Descriptors] = {}
         self._logits: Optional[torch.Tensor] = None
         self._graphs: Dict[Tuple, "torch.cuda.CUDAGraph"] = {}
+        self._next_decode: Optional[Descriptors] = None     # the buffer that holds a decode step described ahead
+        self._last_decode_desc, self._last_decode_widths = None, None
         self.use_graphs = (GRAPHS_DEFAULT if use_graphs is None else bool(use_graphs)) and model.graph_safe
         self.graphs_captured = 0
         self._shape_seen: Dict[Tuple, int] = {}
@@ -469,7 +475,7 @@ class Engine:
         self.graphs_captured += 1
         return graph
 
-    def _replay_graph(self, ctx: StepContext, bucket, shape_key) -> None:
+    def _replay_graph(self, ctx: StepContext, bucket, shape_key) -> "torch.cuda.CUDAGraph":
         """Steps are launch-bound (hundreds of small kernels): the kernels of a step are captured once per
         step shape into a CUDA graph and replayed.  Everything that changes from step to step (tokens,
         positions, lengths, block tables) lies in the descriptor buffer, which the graph reads.  A decode
@@ -482,6 +488,7 @@ class Engine:
         graph.replay()
         ops.launch_count += graph.launches[0]
         ops.library_calls += graph.launches[1]
+        return graph
 
     def _describe(self, entries, chunk, reserve_extra: int = 0):
         """Reserve cache room for a chunk of a step and write its descriptors; returns (desc, T, B, R, widths,
@@ -511,6 +518,7 @@ class Engine:
         desc = self._descriptors(T, B, R, widths)
         desc.wait_reusable()
         desc.decode_slots = None
+        desc.next_decode = None
         tok, pos, sot = desc.h("tokens"), desc.h("positions"), desc.h("seq_of_token")
         cu, slots, ctx_len, lrows = desc.h("cu_tokens"), desc.h("slots"), desc.h("ctx_len"), desc.h("logit_rows")
         if T == B:
@@ -575,23 +583,66 @@ class Engine:
 
     def _step_decode(self, entries: List[Entry]) -> torch.Tensor:
         """The common decode step (one new token per sequence, its logits wanted) with the host work of `step` cut to what
-        this shape needs: the same checks, the same descriptors, no general bookkeeping."""
+        this shape needs: the same checks, the same descriptors, no general bookkeeping.  Everything of the descriptors
+        but the tokens is known before the tokens are: it is written for the NEXT step while the GPU runs this one
+        (`_describe_next_decode`), and used if the same sequences then come again."""
         cache, B = self.cache, len(entries)
-        lengths, held = cache.length, cache.slots.is_held
+        lengths = cache.length
         slot_list = [e.slot for e in entries]
         toks = [int(e.tokens[0]) for e in entries]
         if len(set(slot_list)) != B:
             raise ValueError("a slot appears twice in one step")
-        grows = False
         for slot, t in zip(slot_list, toks):
-            if not held(slot):
-                raise CacheError(f"slot {slot} is not open")
             if not 0 <= t < self.vocab:
                 raise ValueError(f"slot {slot}: token id {t} outside the vocabulary of {self.vocab}")
+        desc, self._next_decode = self._next_decode, None
+        ahead = desc.next_decode if desc is not None else None
+        graph = None
+        if (ahead is not None and ahead[0] == slot_list and ahead[1] == [lengths[slot] for slot in slot_list]
+                and ahead[2] == [g.version for g in cache.groups]):
+            widths, graph = ahead[3], ahead[4]      # described ahead: nothing has touched these sequences or the pages since
+        else:
+            desc, widths = self._describe_decode(slot_list, True)
+        desc.next_decode = None
+        self._last_decode_desc, self._last_decode_widths = desc, widths
+        desc.h("tokens")[:B] = toks
+        desc.upload()
+        logits = self._logits_buffer(B)
+        made_for = (logits.data_ptr(), self.ws.generation, self.use_graphs, self.fused_prefill_rows, id(self.mega), id(self.cluster))
+        if graph is not None and graph[1] == made_for:
+            # the graph that ran these sequences' last step: same shape, same buffers
+            graph[0].replay()
+            ops.launch_count += graph[0].launches[0]
+            ops.library_calls += graph[0].launches[1]
+        else:
+            made = self._execute(desc, B, B, B, widths, logits, 0)
+            graph = (made, made_for) if made is not None else None
+        for slot in slot_list:
+            cache.commit(slot, lengths[slot] + 1)
+        self.steps_run += 1
+        self._describe_next_decode(slot_list, graph)
+        return logits[:B]
+
+    def _describe_decode(self, slot_list: List[int], may_grow: bool):
+        """Checks, cache room and descriptors (all but the tokens) of a decode step of the sequences in `slot_list`:
+        (descriptors, table widths).  With `may_grow` False nothing is reserved and nothing raised: None comes back
+        where the step needs a new page or is not allowed."""
+        cache, B = self.cache, len(slot_list)
+        lengths, held = cache.length, cache.slots.is_held
+        grows = False
+        for slot in slot_list:
+            if not held(slot):
+                if not may_grow:
+                    return None
+                raise CacheError(f"slot {slot} is not open")
             if lengths[slot] + 1 > cache.max_positions:
+                if not may_grow:
+                    return None
                 raise CacheError(f"slot {slot} would reach {lengths[slot] + 1} tokens; the model's limit is {cache.max_positions}")
             grows = grows or lengths[slot] % PAGE_TOKENS == 0
         if grows:            # some sequence begins a new page: the general check and reservation
+            if not may_grow:
+                return None
             if not cache.can_hold({slot: lengths[slot] + 1 for slot in slot_list}):
                 raise CacheError("out of cache pages for this step: the live sequences and the new tokens exceed max_tokens")
             for slot in slot_list:
@@ -605,8 +656,8 @@ class Engine:
             widths.append(min(w, g.max_blocks))
         desc = self._descriptors(B, B, B, widths)
         desc.wait_reusable()
+        desc.next_decode = None
         base = np.array([lengths[slot] for slot in slot_list], dtype=np.int32)
-        desc.h("tokens")[:B] = toks
         desc.h("positions")[:B] = base
         desc.h("ctx_len")[:B] = base + 1
         versions = [g.version for g in cache.groups]
@@ -621,13 +672,21 @@ class Engine:
                 w = widths[g]
                 desc.h(f"table{g}").reshape(desc.caps[1], w)[:B] = group.block_table[slot_ids, :w]
             desc.decode_slots, desc.decode_versions = slot_list, versions
-        desc.upload()
-        logits = self._logits_buffer(B)
-        self._execute(desc, B, B, B, widths, logits, 0)
-        for slot in slot_list:
-            cache.commit(slot, lengths[slot] + 1)
-        self.steps_run += 1
-        return logits[:B]
+        return desc, widths
+
+    def _describe_next_decode(self, slot_list: List[int], graph) -> None:
+        """Called right after a decode step's launches, while the GPU works on them: the descriptors of the step that
+        follows if the same sequences go on (all but its tokens).  Kept only with what it rests on (the slots, their
+        lengths, the block tables' versions), so that any other use of the cache or of the buffer in between voids it."""
+        described = self._describe_decode(slot_list, False)
+        if described is None:
+            return
+        desc, widths = described
+        lengths = self.cache.length
+        if graph is not None and (desc is not self._last_decode_desc or widths != self._last_decode_widths):
+            graph = None                   # the next step has another shape (a wider block table): another graph
+        desc.next_decode = (slot_list, [lengths[slot] for slot in slot_list], [g.version for g in self.cache.groups], widths, graph)
+        self._next_decode = desc
 
     def _run_chunk(self, entries, chunk, logits, row0, produced) -> int:
         cache = self.cache
@@ -638,8 +697,9 @@ class Engine:
         produced.extend(wanted_here)
         return R
 
-    def _execute(self, desc, T: int, B: int, R: int, widths, logits, row0: int) -> None:
-        """Run the model on a described step: from its CUDA graph where there is one, else part by part."""
+    def _execute(self, desc, T: int, B: int, R: int, widths, logits, row0: int):
+        """Run the model on a described step: from its CUDA graph where there is one (which is returned), else part by
+        part (None)."""
         ctx = self._context(desc, T, B, R, widths)
         ctx.logits = logits[row0: row0 + R]
         bucket = self._bucket_of(ctx, (desc.caps[0], desc.caps[1], desc.caps[2], ctx.one_token_each, self.fused_prefill_rows))   # decode steps take other scratch
@@ -654,6 +714,6 @@ class Engine:
             self._shape_seen[shape_key] = seen
             use_graph = seen >= 2
         if use_graph:
-            self._replay_graph(ctx, bucket, shape_key)
-        else:
-            self._run_eager(ctx, bucket)
+            return self._replay_graph(ctx, bucket, shape_key)
+        self._run_eager(ctx, bucket)
+        return None

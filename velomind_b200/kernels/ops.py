@@ -386,14 +386,53 @@ def tc_qkv_rope(x: torch.Tensor, weight: torch.Tensor, q_out: torch.Tensor, posi
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor, seed: torch.Tensor,
-           stream_id: torch.Tensor, step: torch.Tensor, out: torch.Tensor) -> None:
+           stream_id: torch.Tensor, step: torch.Tensor, out, step_add: int = 0) -> None:
     """One token per row of logits float32 [R, V]: greedy where temperature <= 0 or top_p <= 0, else
-    temperature / nucleus sampling with a Philox draw keyed by (seed; stream_id, step) (all int64 [R])."""
+    temperature / nucleus sampling with a Philox draw keyed by (seed; stream_id, step + step_add) (all int64 [R]).
+    `out`: an int32 device tensor, or an address from `host_device_pointer` (tokens written straight to the host)."""
     R, V = logits.shape
     if logits.dtype != torch.float32 or logits.stride(1) != 1:
         raise KernelError("sample: logits are float32 rows")
+    dst = _c_p(out) if isinstance(out, int) else _ptr(out)
     _check(library().vm_sample(_ptr(logits), _c_ll(logits.stride(0)), _c_int(R), _c_int(V), _ptr(temperature), _ptr(top_p),
-                               _ptr(seed), _ptr(stream_id), _ptr(step), _ptr(out), _stream()), "sample")
+                               _ptr(seed), _ptr(stream_id), _ptr(step), _c_ll(int(step_add)), dst, _stream()), "sample")
+
+
+def host_device_pointer(pinned: torch.Tensor) -> int:
+    """The address under which kernels reach the pinned host tensor `pinned`, or 0 if they cannot."""
+    fn = library().vm_host_device_pointer
+    fn.restype = ctypes.c_void_p
+    return int(fn(_c_p(pinned.data_ptr())) or 0)
+
+
+class CopyEvent:
+    """An event that `upload` records behind a copy: `synchronize` returns when the copy has left the host buffer."""
+
+    def __init__(self):
+        lib = library()
+        lib.vm_event_create.restype = ctypes.c_void_p
+        self._destroy = lib.vm_event_destroy
+        self._synchronize = lib.vm_event_synchronize
+        self.handle = _c_p(lib.vm_event_create())
+        if not self.handle.value:
+            raise KernelError("could not create a CUDA event")
+
+    def synchronize(self) -> None:
+        _check(self._synchronize(self.handle), "event synchronize")
+
+    def __del__(self):
+        try:
+            if self.handle.value:
+                self._destroy(self.handle)
+        except Exception:
+            pass
+
+
+def upload(dev: torch.Tensor, pinned: torch.Tensor, event: Optional[CopyEvent]) -> None:
+    """dev <- pinned (the same number of bytes) on the current stream, `event` recorded behind the copy: one call into
+    the runtime instead of a tensor copy and an event record."""
+    _check(library().vm_upload_record(_c_p(dev.data_ptr()), _c_p(pinned.data_ptr()), _c_ll(dev.numel() * dev.element_size()),
+                                      event.handle if event is not None else _c_p(0), _stream()), "upload")
 
 
 def decode_advance(sampled: torch.Tensor, tokens: torch.Tensor, positions: torch.Tensor, ctx_len: torch.Tensor,

@@ -60,6 +60,9 @@ class DeviceSampler:
         self.dev_f = self.dev[split:].view(torch.float32).view(2, rows)
         self.out = torch.empty(rows, dtype=torch.int32, device=self.device)
         self.out_host = _host_buffer((rows,), torch.int32)
+        # where the kernel can write into pinned host memory itself, no copy follows it
+        self.out_direct = ops.host_device_pointer(self.out_host) if self.device.type == "cuda" else 0
+        self._uploaded = None          # (params, streams, steps) that the device's parameter block holds
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], streams: Sequence[int],
                steps: Sequence[int]) -> np.ndarray:
@@ -70,12 +73,28 @@ class DeviceSampler:
             return np.zeros(0, dtype=np.int32)
         if R > self.rows:
             self._alloc(max(R, 2 * self.rows))
-        hf, hi = self.host_f.numpy(), self.host_i.numpy()
-        for r, p in enumerate(params):
-            hf[0, r], hf[1, r] = p.temperature, p.top_p
-            hi[0, r], hi[1, r], hi[2, r] = p.seed, streams[r], steps[r]
-        self.dev.copy_(self.host, non_blocking=True)
-        ops.sample(logits, self.dev_f[0, :R], self.dev_f[1, :R], self.dev_i[0, :R], self.dev_i[1, :R], self.dev_i[2, :R], self.out)
-        self.out_host.copy_(self.out, non_blocking=True)
+        params, streams, steps = list(params), list(streams), list(steps)
+        step_add = None
+        up = self._uploaded
+        if up is not None and up[0] == params and up[1] == streams:
+            # the same requests as at the last upload: if all of them have moved on by the same number of draws,
+            # the block on the device still serves, and that number goes to the kernel as an argument
+            step_add = steps[0] - up[2][0]
+            if any(s - b != step_add for s, b in zip(steps, up[2])):
+                step_add = None
+        if step_add is None:
+            hf, hi = self.host_f.numpy(), self.host_i.numpy()
+            for r, p in enumerate(params):
+                hf[0, r], hf[1, r] = p.temperature, p.top_p
+                hi[0, r], hi[1, r], hi[2, r] = p.seed, streams[r], steps[r]
+            self.dev.copy_(self.host, non_blocking=True)
+            self._uploaded = (params, streams, steps)
+            step_add = 0
+        args = (logits, self.dev_f[0, :R], self.dev_f[1, :R], self.dev_i[0, :R], self.dev_i[1, :R], self.dev_i[2, :R])
+        if self.out_direct:
+            ops.sample(*args, self.out_direct, step_add)
+        else:
+            ops.sample(*args, self.out, step_add)
+            self.out_host.copy_(self.out, non_blocking=True)
         _sync()
         return self.out_host.numpy()[:R].copy()
