@@ -68,6 +68,21 @@ def steps_unequal_batches(requests, batch=3, tails=(3, 11, 6, 1, 8, 2)):
     return steps
 
 
+def steps_sparse_wants(requests, batch=3, tails=(3, 11, 6, 1, 8, 2)):
+    """The batches of steps_unequal_batches, asking for few logits: none at all from the prompts' step, and from the
+    decode steps only every other request's, so that some steps want nothing and others mix entries that do and do not."""
+    steps = steps_unequal_batches(requests, batch, tails)
+    first_of = {}
+    for st in steps:
+        for i, e in enumerate(st["entries"]):
+            if e["id"] not in first_of:
+                first_of[e["id"]] = st["step"]
+                e["want"] = []                                    # the prompt
+            elif (st["step"] + i) % 2:
+                e["want"] = []
+    return steps
+
+
 def expected_rows(steps, requests, plain):
     """For every step with wanted places: the plain logits rows in the order trace replay writes them."""
     fed = {rid: 0 for rid in requests}

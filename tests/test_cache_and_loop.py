@@ -144,7 +144,7 @@ def test_step_function_with_stand_in_kernels(emulated, model_folders, name, cfg)
     requests = S.make_requests(cfg["vocab_size"], (5, 70, 2, 130, 65, 1), seed=2)
     plain = S.plain_logits(folder, requests)
     model = vm.load_model(folder, torch.float32, "cpu")
-    for cut in (S.steps_whole, S.steps_tail_one_by_one, S.steps_unequal_batches):
+    for cut in (S.steps_whole, S.steps_tail_one_by_one, S.steps_unequal_batches, S.steps_sparse_wants):
         engine = vm.Engine(model, 64 * 6, max_slots=3, max_step_tokens=100)    # 130-token prompts are cut in two
         steps = cut(requests) if cut is not S.steps_tail_one_by_one else cut(requests, tail=4)
         got = S.run_steps_in_process(engine, steps)
@@ -152,6 +152,31 @@ def test_step_function_with_stand_in_kernels(emulated, model_folders, name, cfg)
         assert set(got) == set(want)
         assert max(float(np.abs(got[k] - want[k]).max()) for k in want) < 5e-6
         assert engine.cache.slots.held_count == 0 and engine.cache.tokens_held() == 0
+
+
+def test_steps_that_want_no_logits(emulated, model_folders):
+    """A prompt cut by the caller into steps of which only the last wants logits: the earlier steps return no rows (in
+    whichever order steps with and without wanted rows first meet a capacity bucket) and leave the cache as a whole
+    prompt does."""
+    import velomind_b200 as vm
+    folder = model_folders["tiny_a"]
+    tokens = [int(t) for t in np.random.default_rng(4).integers(0, TINY_A["vocab_size"], 23)]
+    ref = P.forward_logits(*P.read_model(folder), tokens)
+    model = vm.load_model(folder, torch.float32, "cpu")
+    for first_wants in (False, True):
+        engine = vm.Engine(model, 64 * 2, max_slots=2)
+        s = engine.open()
+        if first_wants:                                            # a step of the same bucket that does want rows comes first
+            w = engine.open()
+            engine.step([vm.Entry(w, tokens[:9], [8])])
+            engine.close(w)
+        none = engine.step([vm.Entry(s, tokens[:9], [])])
+        assert tuple(none.shape) == (0, TINY_A["vocab_size"])
+        assert tuple(engine.step([vm.Entry(s, tokens[9:17], [])]).shape) == (0, TINY_A["vocab_size"])
+        assert tuple(engine.step([vm.Entry(s, tokens[17:18], [])]).shape) == (0, TINY_A["vocab_size"])     # one token, nothing wanted
+        out = engine.step([vm.Entry(s, tokens[18:], [0, 4])])
+        assert np.abs(out.numpy() - ref[[18, 22]]).max() < 5e-6
+        engine.close(s)
 
 
 def test_step_refusals(emulated, model_folders):

@@ -38,12 +38,13 @@ def _compare(got, want, tol):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c"])
-@pytest.mark.parametrize("cut", ["whole", "tail", "batches"])
+@pytest.mark.parametrize("cut", ["whole", "tail", "batches", "sparse"])
 def test_cuts_match_plain(model_folders, name, dtype, cut):
     folder = model_folders[name]
     requests = S.make_requests(CONFIGS[name]["vocab_size"], LENGTHS, seed=3)
     plain = S.plain_logits(folder, requests)
-    steps = {"whole": S.steps_whole, "tail": S.steps_tail_one_by_one, "batches": S.steps_unequal_batches}[cut](requests)
+    steps = {"whole": S.steps_whole, "tail": S.steps_tail_one_by_one, "batches": S.steps_unequal_batches,
+             "sparse": S.steps_sparse_wants}[cut](requests)
     # a cache just large enough for one batch, so that pages and slots are used again and again
     engine = _engine(folder, dtype, max_tokens=64 * 8, max_slots=3)
     got = S.run_steps_in_process(engine, steps)

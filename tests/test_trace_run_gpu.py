@@ -28,8 +28,9 @@ def test_replay_three_cuts(model_folders, tmp_path, name, cfg, dtype):
     folder = model_folders[name]
     requests = S.make_requests(cfg["vocab_size"], (40, 7, 100, 66, 35, 129), seed=13)
     plain = S.plain_logits(folder, requests)
-    cuts = {"whole": S.steps_whole, "tail": S.steps_tail_one_by_one, "batches": S.steps_unequal_batches}
-    # one process replays all three cuts, one after another, with a cache of 8 pages: pages and slots are used again
+    cuts = {"whole": S.steps_whole, "tail": S.steps_tail_one_by_one, "batches": S.steps_unequal_batches,
+            "sparse": S.steps_sparse_wants}
+    # one process replays all the cuts, one after another, with a cache of 8 pages: pages and slots are used again
     steps, owner, all_requests, all_plain = [], {}, {}, {}
     for cut, make in cuts.items():
         renamed = {f"{cut}:{rid}": toks for rid, toks in requests.items()}

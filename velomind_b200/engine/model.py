@@ -104,11 +104,14 @@ class DecoderModel:
         to it); gives `h` and `pending` back to the workspace."""
         hid = self.plan.hidden_size
         logits = ctx.logits
-        x = ctx.take_rows(hid, ctx.act_dtype)
+        # (the buffer is taken whatever R is, so that every step of a capacity bucket asks for the same buffers; it is
+        # given back by its whole extent: with R = 0, a prompt cut into several steps, the view of its rows is empty)
+        rows = ctx.take((ctx.R_cap, hid), ctx.act_dtype)
         if ctx.R > 0:
+            x = rows[: ctx.R]
             self.final_norm.forward(ctx, h, pending, x, ctx.logit_rows)
             self.head.forward(ctx, x, logits)
-        ctx.ws.give(x)
+        ctx.ws.give(rows)
         ctx.ws.give(pending)
         ctx.ws.give(h)
         return logits

@@ -160,9 +160,6 @@ class StepContext:
         """A [T, cols] buffer (backed by capacity rows, so that the plan of the bucket fits every step in it)."""
         return self.ws.take((self.T_cap, cols), dtype)[: self.T]
 
-    def take_rows(self, cols: int, dtype: torch.dtype) -> torch.Tensor:
-        return self.ws.take((self.R_cap, cols), dtype)[: self.R]
-
     def take(self, shape, dtype: torch.dtype) -> torch.Tensor:
         return self.ws.take(shape, dtype)
 
