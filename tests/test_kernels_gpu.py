@@ -328,7 +328,7 @@ def _rms_ref(h, w, eps):
 
 
 @pytest.mark.parametrize("M", [1, 8, 17, 64])
-@pytest.mark.parametrize("N,K", [(72, 64), (576, 576), (200, 160), (576, 1536), (4752, 96)])
+@pytest.mark.parametrize("N,K", [(72, 64), (576, 576), (200, 160), (576, 1536), (4752, 96), (3000, 1056)])   # (the last two: CTAs take several column tiles)
 def test_skinny_linear(M, N, K):
     o = ops()
     x = _bf(torch.randn(M, K, generator=_gen(M + N)))
@@ -355,7 +355,7 @@ def test_skinny_linear(M, N, K):
     assert (out.float().cpu() - want_n).abs().max() <= 2e-2 * float(want_n.abs().max())
 
 
-@pytest.mark.parametrize("M,I,K", [(3, 192, 64), (8, 1536, 576), (33, 160, 96), (64, 1000, 1536)])
+@pytest.mark.parametrize("M,I,K", [(3, 192, 64), (8, 1536, 576), (33, 160, 96), (64, 1000, 1536), (5, 5000, 96), (20, 2000, 1088)])
 def test_skinny_swiglu(M, I, K):
     o = ops()
     hres = torch.randn(M, K, generator=_gen(M)) * 2
@@ -371,7 +371,8 @@ def test_skinny_swiglu(M, I, K):
     assert (out.float().cpu() - want).abs().max() <= 2e-2 * float(want.abs().max())
 
 
-@pytest.mark.parametrize("H,Hkv,D,K,rot", [(4, 2, 16, 64, 16), (3, 1, 32, 96, 32), (9, 3, 64, 576, 64), (5, 5, 48, 160, 0), (2, 1, 128, 256, 128)])
+@pytest.mark.parametrize("H,Hkv,D,K,rot", [(4, 2, 16, 64, 16), (3, 1, 32, 96, 32), (9, 3, 64, 576, 64), (5, 5, 48, 160, 0), (2, 1, 128, 256, 128),
+                                           (40, 8, 64, 96, 64)])                # (the last: CTAs take several column tiles)
 def test_skinny_qkv_rope(H, Hkv, D, K, rot):
     o = ops()
     lens_before, new = [3, 70, 0], [5, 1, 20]

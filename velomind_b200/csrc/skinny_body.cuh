@@ -27,15 +27,38 @@ struct SkinnyParams {
     const int* positions; const int* seq_of_token; const int* block_table; int max_blocks;
     const float* inv_freq; int rot_dim;
     __nv_bfloat16* kpages; __nv_bfloat16* vpages; int H, Hkv, D, n_pages; int* err;
+    int n_items;                 // work items of the launch (a CTA takes items blockIdx.x, + gridDim.x, ...)
     int kc;                      // k chunk staged in shared memory at a time (multiple of 32)
     int row_bytes;               // shared-memory row pitch of the A tile, == 64 mod 128
 };
 
 // `item` is the work item (what item_index is for the stand-alone kernel); `smem` the CTA's dynamic shared memory.
 // PDL: launched with programmatic dependent launch (weights may be fetched before the predecessor has finished).
+// The output columns of a work item: tile A's first column, tile B's, and (rope_kv) the head they lie in.
+struct SkinnyCols { int nA, nB, head; };
+__device__ __forceinline__ SkinnyCols skinny_cols(const SkinnyParams& p, int item_index) {
+    SkinnyCols c{0, 0, 0};
+    if (p.epi == EPI_SWIGLU) { c.nA = 8 * item_index; c.nB = p.I + c.nA; }
+    else if (p.epi == EPI_ROPE_KV) {
+        const int per_head = p.D / 16;
+        c.head = item_index / per_head;
+        const int sub = item_index - c.head * per_head;
+        if (c.head < p.H + p.Hkv && p.rot_dim > 0) { c.nA = c.head * p.D + 8 * sub; c.nB = c.nA + p.D / 2; }   // rotary pair (j, j + D/2)
+        else { c.nA = c.head * p.D + 16 * sub; c.nB = c.nA + 8; }
+    }
+    else if (p.tiles == 2) { c.nA = 16 * item_index; c.nB = c.nA + 8; }
+    else { c.nA = 8 * item_index; c.nB = c.nA; }
+    return c;
+}
+
+// Work items first_item, first_item + item_stride, ... below n_items.  When all of K fits into the shared-memory tile
+// (K <= p.kc), A is staged (and normalised) ONCE for all items of the CTA, and an item's first weight blocks are
+// requested before the previous item's sums are joined and stored.
 // PF: k blocks of 32 that a warp keeps in flight (8 warps x PF x 32 values of K per round).
-template <int MT, bool PDL, int PF = 8>
-__device__ __forceinline__ void skinny_body(const SkinnyParams& p, const int item_index, unsigned char* smem) {
+// LOOP false: the CTA has the one item first_item (the code that looks ahead to a next item is left out).
+template <int MT, bool PDL, int PF = 8, bool LOOP = true>
+__device__ __forceinline__ void skinny_run(const SkinnyParams& p, const int first_item, const int item_stride, const int n_items,
+                                           unsigned char* smem) {
     constexpr int ROWS = 16 * MT;
     unsigned char* sA = smem;                                              // ROWS x row_bytes
     float* red = reinterpret_cast<float*>(smem + (size_t)ROWS * p.row_bytes);   // [SK_WARPS][ROWS][16]
@@ -44,21 +67,13 @@ __device__ __forceinline__ void skinny_body(const SkinnyParams& p, const int ite
     // (the kernel that writes the cache lets its successor, the attention, start only after its own wait: see there)
     if (PDL && p.epi != EPI_ROPE_KV) vm_pdl_launch_dependents();
 
+    if (first_item >= n_items) return;
     // ---- which output columns
-    int nA, nB, head = 0;
-    if (p.epi == EPI_SWIGLU) { nA = 8 * item_index; nB = p.I + nA; }
-    else if (p.epi == EPI_ROPE_KV) {
-        const int per_head = p.D / 16;
-        head = item_index / per_head;
-        const int sub = item_index - head * per_head;
-        if (head < p.H + p.Hkv && p.rot_dim > 0) { nA = head * p.D + 8 * sub; nB = nA + p.D / 2; }   // rotary pair (j, j + D/2)
-        else { nA = head * p.D + 16 * sub; nB = nA + 8; }
-    }
-    else if (p.tiles == 2) { nA = 16 * item_index; nB = nA + 8; }
-    else { nA = 8 * item_index; nB = nA; }
-    const __nv_bfloat16* wA = p.W + (size_t)(nA + g) * p.K;
-    const __nv_bfloat16* wB = p.W + (size_t)(nB + g) * p.K;
+    SkinnyCols cols = skinny_cols(p, first_item);
+    const __nv_bfloat16* wA = p.W + (size_t)(cols.nA + g) * p.K;
+    const __nv_bfloat16* wB = p.W + (size_t)(cols.nB + g) * p.K;
     const bool two = (p.tiles == 2);
+    const bool whole_k = p.K <= p.kc;                       // A is staged once for all items
 
     // ---- weight fragments do not depend on A: the first group of this warp's k blocks is requested before
     //      anything else, so that its DRAM latency overlaps the staging of A
@@ -77,9 +92,31 @@ __device__ __forceinline__ void skinny_body(const SkinnyParams& p, const int ite
     issue(0, min(p.kc, p.K) / 32, 0);
     // the rotary frequencies of this thread's output column are constants of the model too
     float freq = 0.f;
-    if (p.epi == EPI_ROPE_KV && head < p.H + p.Hkv && p.rot_dim > 0) freq = p.inv_freq[(nA - head * p.D) + (tid & 7)];
+    if (p.epi == EPI_ROPE_KV && cols.head < p.H + p.Hkv && p.rot_dim > 0) freq = p.inv_freq[(cols.nA - cols.head * p.D) + (tid & 7)];
     if (PDL) vm_pdl_wait();                                 // from here on: data written by earlier kernels
     if (PDL && p.epi == EPI_ROPE_KV) vm_pdl_launch_dependents();
+    // the epilogue's per-row facts (position, cache page) are fetched now, long before they are needed
+    int row_pos[MT], row_page[MT];
+    if (p.epi == EPI_ROPE_KV) {
+#pragma unroll
+        for (int i = 0; i < MT; ++i) {
+            const int item = tid + SK_THREADS * i;
+            const int row = item >> 3;
+            row_pos[i] = 0; row_page[i] = -1;
+            if (item < ROWS * 8 && row < p.M) {
+                row_pos[i] = p.positions[row];
+                if (p.kpages != nullptr && (LOOP || cols.head >= p.H)) {      // (a CTA with one item of a query head needs no page)
+                    const int blk = row_pos[i] / VM_PAGE_TOKENS;
+                    row_page[i] = (blk < p.max_blocks) ? p.block_table[(size_t)p.seq_of_token[row] * p.max_blocks + blk] : -1;
+                }
+            }
+        }
+    }
+
+    int item_index = first_item;
+    do {
+    const int nA = cols.nA, nB = cols.nB, head = cols.head;
+    const bool first = !LOOP || item_index == first_item;
     // the residual values this thread will add to are requested now: their latency passes under the product
     float res_a[MT], res_b[MT];
     if (p.epi == EPI_RESIDUAL) {
@@ -95,24 +132,6 @@ __device__ __forceinline__ void skinny_body(const SkinnyParams& p, const int ite
             }
         }
     }
-    // the epilogue's per-row facts (position, cache page) are fetched now, long before they are needed
-    int row_pos[MT], row_page[MT];
-    if (p.epi == EPI_ROPE_KV) {
-#pragma unroll
-        for (int i = 0; i < MT; ++i) {
-            const int item = tid + SK_THREADS * i;
-            const int row = item >> 3;
-            row_pos[i] = 0; row_page[i] = -1;
-            if (item < ROWS * 8 && row < p.M) {
-                row_pos[i] = p.positions[row];
-                if (head >= p.H && p.kpages != nullptr) {
-                    const int blk = row_pos[i] / VM_PAGE_TOKENS;
-                    row_page[i] = (blk < p.max_blocks) ? p.block_table[(size_t)p.seq_of_token[row] * p.max_blocks + blk] : -1;
-                }
-            }
-        }
-    }
-
     float acc[MT][2][4];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
@@ -122,8 +141,9 @@ __device__ __forceinline__ void skinny_body(const SkinnyParams& p, const int ite
     for (int kc0 = 0; kc0 < p.K; kc0 += p.kc) {
         const int kc = min(p.kc, p.K - kc0);
         if (kc0 > 0) __syncthreads();                       // the previous chunk has been consumed
-        // ---- stage A[:, kc0 : kc0+kc] as bf16
-        if (p.pro == PRO_NONE) {
+        // ---- stage A[:, kc0 : kc0+kc] as bf16 (once per CTA when all of K fits)
+        if (whole_k && !first) {
+        } else if (p.pro == PRO_NONE) {
             // (rows past M are never read: their fragments are zeros in registers)
             const __nv_bfloat16* A = static_cast<const __nv_bfloat16*>(p.A);
             const int chunks = kc / 8;
@@ -168,7 +188,7 @@ __device__ __forceinline__ void skinny_body(const SkinnyParams& p, const int ite
                 if (lane == 0) inv[r] = (kc0 == 0 ? 0.f : inv[r]) + ss;        // sum of squares so far
             }
         }
-        __syncthreads();
+        if (!(whole_k && !first)) __syncthreads();
         // ---- this warp's k blocks of the chunk: block b covers k = kc0 + 32 b .. + 31
         const int blocks = kc / 32;
         for (int group = 0; warp + SK_WARPS * group * PF < blocks; ++group) {
@@ -192,6 +212,15 @@ __device__ __forceinline__ void skinny_body(const SkinnyParams& p, const int ite
                 }
             }
         }
+    }
+    // ---- the next item's first weight blocks are on their way while this item's sums are joined and stored
+    float next_freq = 0.f;
+    if (LOOP && item_index + item_stride < n_items) {
+        cols = skinny_cols(p, item_index + item_stride);
+        wA = p.W + (size_t)(cols.nA + g) * p.K;
+        wB = p.W + (size_t)(cols.nB + g) * p.K;
+        issue(0, min(p.kc, p.K) / 32, 0);
+        if (p.epi == EPI_ROPE_KV && cols.head < p.H + p.Hkv && p.rot_dim > 0) next_freq = p.inv_freq[(cols.nA - cols.head * p.D) + (tid & 7)];
     }
     // ---- join the warps' partial sums: red[warp][row][col], col 0..7 = tile A, 8..15 = tile B
 #pragma unroll
@@ -268,7 +297,15 @@ __device__ __forceinline__ void skinny_body(const SkinnyParams& p, const int ite
             } break;
         }
     }
-    __syncthreads();                                        // the buffers may be reused for another item
+    if (LOOP) freq = next_freq;
+    __syncthreads();                                        // the sums' buffer is reused by the next item
+    } while (LOOP && (item_index += item_stride) < n_items);
+}
+
+// One work item (the persistent decode kernel deals items out itself).
+template <int MT, bool PDL, int PF = 8>
+__device__ __forceinline__ void skinny_body(const SkinnyParams& p, const int item_index, unsigned char* smem) {
+    skinny_run<MT, PDL, PF, false>(p, item_index, 1, item_index + 1, smem);
 }
 
 // The same product for MANY output columns (the vocabulary head): the warps of a CTA split N instead of K.

@@ -27,11 +27,12 @@ using namespace vmsk;
 
 // (two CTAs per SM for up to 16 rows: 192 gate/up items then fit the GPU at once)
 // (PF: weight blocks a warp keeps in flight; 4 cover K <= 1,024 in one round and leave registers to the prologue)
-template <int MT, int PF>
+// (LOOP: a CTA takes several work items one after another; without it the grid has a CTA per item)
+template <int MT, int PF, bool LOOP>
 __global__ void __launch_bounds__(SK_THREADS, MT == 1 ? 2 : 1)
 skinny_gemm_kernel(const SkinnyParams p) {
     extern __shared__ __align__(16) unsigned char smem[];
-    skinny_body<MT, true, PF>(p, blockIdx.x, smem);
+    skinny_run<MT, true, PF, LOOP>(p, blockIdx.x, gridDim.x, p.n_items, smem);
 }
 
 template <int MT>
@@ -83,22 +84,40 @@ int skinny_launch(SkinnyParams p, int grid, cudaStream_t stream) {
     pitch += ((64 - pitch % 128) + 128) % 128;
     p.row_bytes = pitch;
     const size_t smem = (size_t)rows * pitch + (size_t)SK_WARPS * rows * 16 * sizeof(float) + rows * sizeof(float);
+    // all of K in shared memory: as many CTAs as the GPU holds at once, each staging A once and taking its share of the
+    // items one after another; else one CTA per item
+    p.n_items = grid;
+    if (p.K <= kc) {
+        static int sms = 0;
+        if (sms == 0) {
+            int dev = 0;
+            if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 1;
+        }
+        const int resident = sms * ((MT == 1 && 2 * smem + 2048 <= 227 * 1024) ? 2 : 1);
+        const int per_cta = (grid + resident - 1) / resident;
+        grid = (grid + per_cta - 1) / per_cta;
+    }
+    const bool loop = grid < p.n_items;
     const bool few = kc <= SK_WARPS * 32 * 4;
-#define VM_SK_CASE(X, P)                                                                                              \
+#define VM_SK_CASE(X, P, L)                                                                                           \
     {                                                                                                                 \
         static size_t configured = 0;                                                                                 \
         if (smem > 48 * 1024 && smem > configured) {                                                                  \
-            cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<X, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); \
+            cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<X, P, L>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); \
             if (e != cudaSuccess) return (int)e;                                                                      \
             configured = 160 * 1024;                                                                                  \
         }                                                                                                             \
-        vm_launch_pdl(skinny_gemm_kernel<X, P>, dim3(grid), dim3(SK_THREADS), smem, stream, p);                       \
+        vm_launch_pdl(skinny_gemm_kernel<X, P, L>, dim3(grid), dim3(SK_THREADS), smem, stream, p);                    \
     }
+#define VM_SK_ROWS(X)                                                                                                 \
+    if (few) { if (loop) VM_SK_CASE(X, 4, true) else VM_SK_CASE(X, 4, false) }                                        \
+    else { if (loop) VM_SK_CASE(X, 8, true) else VM_SK_CASE(X, 8, false) }
     switch (MT) {
-        case 1: if (few) VM_SK_CASE(1, 4) else VM_SK_CASE(1, 8) break;
-        case 2: if (few) VM_SK_CASE(2, 4) else VM_SK_CASE(2, 8) break;
-        case 4: if (few) VM_SK_CASE(4, 4) else VM_SK_CASE(4, 8) break;
+        case 1: VM_SK_ROWS(1) break;
+        case 2: VM_SK_ROWS(2) break;
+        case 4: VM_SK_ROWS(4) break;
     }
+#undef VM_SK_ROWS
 #undef VM_SK_CASE
     return vm_launch_status();
 }
