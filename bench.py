@@ -237,12 +237,18 @@ def main() -> int:
         prompts = [rng.integers(0, vocab, prompt_len).tolist() for _ in range(B)]
         # the host reads every step's tokens and sends the next step's descriptors (steps_per_sync=1), as the contract asks
         te.generate(prompts, temperature=0.0, max_tokens=warmup + 1, stop_tokens=(), steps_per_sync=1)
+        from velomind_b200.kernels import ops as kernel_ops
+        # bytes are counted where they are copied (descriptors and sampler parameters up, sampled tokens down); what the
+        # prompt step alone moves is taken off, as the timed region is the decode steps
+        h2d0, d2h0 = kernel_ops.h2d_bytes, kernel_ops.d2h_bytes
+        te.generate(prompts, temperature=0.0, max_tokens=1, stop_tokens=(), steps_per_sync=1)
+        h2d_prompt, d2h_prompt = kernel_ops.h2d_bytes - h2d0, kernel_ops.d2h_bytes - d2h0
+        h2d0, d2h0 = kernel_ops.h2d_bytes, kernel_ops.d2h_bytes
         te.generate(prompts, temperature=0.0, max_tokens=args.steps + 1, stop_tokens=(), steps_per_sync=1)
         tm = te.last_timing
         e2e = {"value": B * tm.decode_steps / tm.decode_seconds, "unit": "tokens/s",
-               "h2d_bytes_per_step": 4 * min(d.total for k, d in te.engine._desc.items() if k[0] == 8 and k[1] == 8)
-               + te.sampler.rows * (2 * 4 + 3 * 8),
-               "d2h_bytes_per_step": 4 * B}
+               "h2d_bytes_per_step": round((kernel_ops.h2d_bytes - h2d0 - h2d_prompt) / max(tm.decode_steps, 1)),
+               "d2h_bytes_per_step": round((kernel_ops.d2h_bytes - d2h0 - d2h_prompt) / max(tm.decode_steps, 1))}
 
     if e2e is not None:
         # the same call with its default of 8 decode steps queued per host round trip

@@ -21,6 +21,8 @@ _c_int, _c_ll, _c_f, _c_p = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, cty
 
 launch_count = 0          # this library's own kernels launched through this module (the bench reports it)
 library_calls = 0         # library matrix products (cuBLAS through torch.mm)
+h2d_bytes = 0             # bytes of step inputs copied from pinned host memory (descriptors, sampler parameters)
+d2h_bytes = 0             # bytes of step results that reached the host (sampled tokens)
 tc_attention_calls = 0    # launches of the tcgen05 prefill attention (tests check that long prompts take it)
 
 
@@ -431,8 +433,11 @@ class CopyEvent:
 def upload(dev: torch.Tensor, pinned: torch.Tensor, event: Optional[CopyEvent]) -> None:
     """dev <- pinned (the same number of bytes) on the current stream, `event` recorded behind the copy: one call into
     the runtime instead of a tensor copy and an event record."""
-    _check(library().vm_upload_record(_c_p(dev.data_ptr()), _c_p(pinned.data_ptr()), _c_ll(dev.numel() * dev.element_size()),
+    global h2d_bytes
+    nbytes = dev.numel() * dev.element_size()
+    _check(library().vm_upload_record(_c_p(dev.data_ptr()), _c_p(pinned.data_ptr()), _c_ll(nbytes),
                                       event.handle if event is not None else _c_p(0), _stream()), "upload")
+    h2d_bytes += nbytes
 
 
 def decode_advance(sampled: torch.Tensor, tokens: torch.Tensor, positions: torch.Tensor, ctx_len: torch.Tensor,

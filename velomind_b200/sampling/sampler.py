@@ -88,6 +88,7 @@ class DeviceSampler:
                 hf[0, r], hf[1, r] = p.temperature, p.top_p
                 hi[0, r], hi[1, r], hi[2, r] = p.seed, streams[r], steps[r]
             self.dev.copy_(self.host, non_blocking=True)
+            ops.h2d_bytes += self.host.numel()
             self._uploaded = (params, streams, steps)
             step_add = 0
         args = (logits, self.dev_f[0, :R], self.dev_f[1, :R], self.dev_i[0, :R], self.dev_i[1, :R], self.dev_i[2, :R])
@@ -97,4 +98,5 @@ class DeviceSampler:
             ops.sample(*args, self.out, step_add)
             self.out_host.copy_(self.out, non_blocking=True)
         _sync()
+        ops.d2h_bytes += 4 * R
         return self.out_host.numpy()[:R].copy()
