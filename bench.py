@@ -251,8 +251,8 @@ def main() -> int:
                "d2h_bytes_per_step": round((kernel_ops.d2h_bytes - d2h0 - d2h_prompt) / max(tm.decode_steps, 1))}
 
     if e2e is not None:
-        # the same call with its default of 8 decode steps queued per host round trip
-        te.generate(prompts, temperature=0.0, max_tokens=args.steps + 1, stop_tokens=())
+        # the same call with 8 decode steps queued per host round trip
+        te.generate(prompts, temperature=0.0, max_tokens=args.steps + 1, stop_tokens=(), steps_per_sync=8)
         points["e2e_queued_8"] = B * te.last_timing.decode_steps / te.last_timing.decode_seconds
     line = {
         "metric": "decode tok/s at batch 8 (SmolLM2-135M shape, prompts of 512 tokens)",

@@ -111,10 +111,12 @@ class TextEngine:
 
     def generate(self, prompts: Sequence[Union[str, Sequence[int]]], temperature: float = 0.7, top_p: float = 0.9,
                  max_tokens: int = 32, seed: int = 42, stop_tokens: Optional[Sequence[int]] = None,
-                 on_token: Optional[Callable[[int, int, str], None]] = None, steps_per_sync: int = 8) -> List[Result]:
+                 on_token: Optional[Callable[[int, int, str], None]] = None, steps_per_sync: int = 1) -> List[Result]:
         """Generate for a batch of prompts (token id lists, or text if a tokenizer is loaded).
         `on_token(index, token, piece)` is called for every new token; `piece` is its text (or "[id]").
-        `steps_per_sync`: decode steps queued on the GPU before the host reads their tokens (1: every step)."""
+        `steps_per_sync`: decode steps queued on the GPU before the host reads their tokens.  1 (the default): every
+        step, each token reaches `on_token` as it is made, and on a host that keeps up this is also the faster way;
+        more: the host is out of the loop for that many steps, at the price of steps computed past a stop token."""
         engine = self._need()
         stops = tuple(stop_tokens) if stop_tokens is not None else self.default_stop_tokens()
         requests = [Request(self.encode(p), SamplingParams(temperature, top_p, max_tokens, seed, stops), stream=i)
