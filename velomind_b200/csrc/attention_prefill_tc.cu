@@ -133,9 +133,9 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, co
     const uint32_t t_s = tmem_base + ((uint32_t)(warp * 32) << 16);         // this warp's 32 lanes; scores in columns 0..63
     const uint32_t t_pv = t_s + 64;                                         // P V in columns 64..127
     float m = -INFINITY, l = 0.f;
-    float o[D];
+    float2 o[D / 2];                                        // the row's output sums, in pairs (packed float32 arithmetic)
 #pragma unroll
-    for (int d = 0; d < D; ++d) o[d] = 0.f;
+    for (int d = 0; d < D / 2; ++d) o[d] = make_float2(0.f, 0.f);
     uint32_t phase_s = 0, phase_pv = 0;
     bool ok = !*abort_p;
     const uint64_t dq = ta_desc(ta_u32(sQ)), dp = ta_desc(ta_u32(sP));
@@ -180,21 +180,23 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, co
             }
         }
 #pragma unroll
-        for (int j = 0; j < 64; ++j) mx = fmaxf(mx, __uint_as_float(sv[j >> 5][j & 31]));
+        for (int j = 0; j < 64; j += 2) mx = ta_max3(mx, __uint_as_float(sv[j >> 5][j & 31]), __uint_as_float(sv[(j + 1) >> 5][(j + 1) & 31]));
         const float mn = fmaxf(m, mx);
         const float use = (mn == -INFINITY) ? 0.f : mn;     // the row sees nothing yet
         const float alpha = ta_exp2((m - use) * scale_log2);
         const float off = -use * scale_log2;
-        float p_sum = 0.f;
+        float2 p_sum = make_float2(0.f, 0.f);              // (even and odd columns apart: two values per instruction)
+        const float2 scale2 = make_float2(scale_log2, scale_log2), off2 = make_float2(off, off);
         uint32_t pw[32];                                    // the probabilities, two bf16 per word
 #pragma unroll
         for (int j = 0; j < 64; j += 2) {
-            const float p0 = ta_exp2(fmaf(__uint_as_float(sv[j >> 5][j & 31]), scale_log2, off));
-            const float p1 = ta_exp2(fmaf(__uint_as_float(sv[(j + 1) >> 5][(j + 1) & 31]), scale_log2, off));
-            p_sum += p0 + p1;
-            pw[j >> 1] = vm_pack_bf16(p0, p1);
+            const float2 x = __ffma2_rn(make_float2(__uint_as_float(sv[j >> 5][j & 31]), __uint_as_float(sv[(j + 1) >> 5][(j + 1) & 31])),
+                                        scale2, off2);
+            const float2 p = make_float2(ta_exp2(x.x), ta_exp2(x.y));
+            p_sum = __fadd2_rn(p_sum, p);
+            pw[j >> 1] = vm_pack_bf16(p.x, p.y);
         }
-        l = l * alpha + p_sum;
+        l = l * alpha + (p_sum.x + p_sum.y);
         m = mn;
         // ---- the previous block's P V is done by now: add it, then rescale; its P tile and its V buffer are free
         if (step > 0) {
@@ -205,13 +207,15 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, co
             ta_ld32(t_pv + 32, sv[1]);
             ta_ld_wait();
 #pragma unroll
-            for (int d = 0; d < D; ++d) o[d] += __uint_as_float(sv[d >> 5][d & 31]);
+            for (int d = 0; d < D; d += 2)
+                o[d >> 1] = __fadd2_rn(o[d >> 1], make_float2(__uint_as_float(sv[d >> 5][d & 31]), __uint_as_float(sv[(d + 1) >> 5][(d + 1) & 31])));
         }
         load_page(step + 1, true);                          // V(step + 1) into the buffer V(step - 1) was in
         ta_commit_group();
         if (alpha != 1.f) {
+            const float2 alpha2 = make_float2(alpha, alpha);
 #pragma unroll
-            for (int d = 0; d < D; ++d) o[d] *= alpha;
+            for (int d = 0; d < D / 2; ++d) o[d] = __fmul2_rn(o[d], alpha2);
         }
         unsigned char* prow = sP + row * 128;
 #pragma unroll
@@ -238,7 +242,8 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, co
         ta_ld32(t_pv + 32, sv[1]);
         ta_ld_wait();
 #pragma unroll
-        for (int d = 0; d < D; ++d) o[d] += __uint_as_float(sv[d >> 5][d & 31]);
+        for (int d = 0; d < D; d += 2)
+            o[d >> 1] = __fadd2_rn(o[d >> 1], make_float2(__uint_as_float(sv[d >> 5][d & 31]), __uint_as_float(sv[(d + 1) >> 5][(d + 1) & 31])));
     }
     ta_wait_group<0>();
     ta_fence_before();
@@ -252,8 +257,8 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, co
 #pragma unroll
             for (int c = 0; c < D / 8; ++c) {
                 uint4 w;
-                w.x = vm_pack_bf16(o[8 * c] * inv, o[8 * c + 1] * inv); w.y = vm_pack_bf16(o[8 * c + 2] * inv, o[8 * c + 3] * inv);
-                w.z = vm_pack_bf16(o[8 * c + 4] * inv, o[8 * c + 5] * inv); w.w = vm_pack_bf16(o[8 * c + 6] * inv, o[8 * c + 7] * inv);
+                w.x = vm_pack_bf16(o[4 * c].x * inv, o[4 * c].y * inv); w.y = vm_pack_bf16(o[4 * c + 1].x * inv, o[4 * c + 1].y * inv);
+                w.z = vm_pack_bf16(o[4 * c + 2].x * inv, o[4 * c + 2].y * inv); w.w = vm_pack_bf16(o[4 * c + 3].x * inv, o[4 * c + 3].y * inv);
                 *reinterpret_cast<uint4*>(orow + 8 * c) = w;
             }
         }
@@ -270,8 +275,8 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, co
             asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(dest));
 #pragma unroll
             for (int c = 0; c < D / 4; ++c)
-                asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(remote + 16 * c), "f"(o[4 * c]), "f"(o[4 * c + 1]),
-                             "f"(o[4 * c + 2]), "f"(o[4 * c + 3]) : "memory");
+                asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(remote + 16 * c), "f"(o[2 * c].x), "f"(o[2 * c].y),
+                             "f"(o[2 * c + 1].x), "f"(o[2 * c + 1].y) : "memory");
             asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(remote + 4 * D), "f"(m), "f"(l), "f"(0.f), "f"(0.f) : "memory");
         }
         asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");

@@ -42,6 +42,12 @@ __device__ __forceinline__ float ta_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// max(a, b, c) in one instruction
+__device__ __forceinline__ float ta_max3(float a, float b, float c) {
+    float y;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+    return y;
+}
 // Shared-memory matrix descriptor for 128-byte rows with 128-byte swizzle, eight-row groups 1024 bytes apart: start
 // address >> 4 in bits 0-13, leading byte offset (unused here; 1) in bits 16-29, stride byte offset 1024 >> 4 in bits
 // 32-45, descriptor version 1 in bits 46-47, layout 2 (128-byte swizzle) in bits 61-63.  The same bits describe a
