@@ -86,21 +86,30 @@ rope_kv_write_bf16_vec_kernel(__nv_bfloat16* __restrict__ qkv, const int* __rest
         return;
     }
     const int half = D / 2;
+    __nv_bfloat16* row = qkv + (size_t)t * (H + 2 * Hkv) * D;
+    const size_t page_stride = (size_t)Hkv * VM_PAGE_TOKENS * D;
+    const int in_page = pos % VM_PAGE_TOKENS;
+    const int g8 = half / 8;                            // groups of eight pairs per head
+    const int n_items = (write_kv ? H + Hkv : H) * g8;
+    // each thread's first item is requested before the angles are computed: its latency passes under them
+    const int it0 = threadIdx.x;
+    uint4 first_a = make_uint4(0u, 0u, 0u, 0u), first_b = first_a;
+    if (it0 < n_items) {
+        const int head = it0 / g8, j0 = (it0 - head * g8) * 8;
+        const __nv_bfloat16* x = row + (size_t)head * D;
+        first_a = *reinterpret_cast<const uint4*>(x + j0); first_b = *reinterpret_cast<const uint4*>(x + half + j0);
+    }
     for (int j = threadIdx.x; j < half; j += blockDim.x) {
         float s, c;
         sincosf((float)pos * inv_freq[j], &s, &c);
         cs[j] = c; cs[half + j] = s;
     }
     __syncthreads();
-    __nv_bfloat16* row = qkv + (size_t)t * (H + 2 * Hkv) * D;
-    const size_t page_stride = (size_t)Hkv * VM_PAGE_TOKENS * D;
-    const int in_page = pos % VM_PAGE_TOKENS;
-    const int g8 = half / 8;                            // groups of eight pairs per head
-    const int n_items = (write_kv ? H + Hkv : H) * g8;
     for (int it = threadIdx.x; it < n_items; it += blockDim.x) {
         const int head = it / g8, j0 = (it - head * g8) * 8;
         __nv_bfloat16* x = row + (size_t)head * D;
-        const uint4 a4 = *reinterpret_cast<const uint4*>(x + j0), b4 = *reinterpret_cast<const uint4*>(x + half + j0);
+        uint4 a4 = first_a, b4 = first_b;
+        if (it != it0) { a4 = *reinterpret_cast<const uint4*>(x + j0); b4 = *reinterpret_cast<const uint4*>(x + half + j0); }
         const unsigned aw[4] = {a4.x, a4.y, a4.z, a4.w}, bw[4] = {b4.x, b4.y, b4.z, b4.w};
         unsigned ya[4], yb[4];
 #pragma unroll
@@ -133,7 +142,9 @@ VM_API int vm_rope_kv_write(void* qkv, const int* positions, const int* seq_of_t
     if (rot_dim < 0 || rot_dim > D || (rot_dim & 1) || (rot_dim > 0 && inv_freq == nullptr)) return VM_ERR_BAD_ARG;
     if (act_dtype == VM_BF16 && rot_dim == D && D % 16 == 0 && (reinterpret_cast<uintptr_t>(qkv) & 15) == 0 &&
         ((reinterpret_cast<uintptr_t>(kpages) | reinterpret_cast<uintptr_t>(vpages)) & 15) == 0) {
-        rope_kv_write_bf16_vec_kernel<<<T, 128, (size_t)D * sizeof(float), stream>>>(
+        // (a thread takes eight pairs of a head: 64 threads cover this model's 9 + 3 heads of 64 in one round)
+        const int threads = (H + Hkv) * (D / 16) <= 64 ? 64 : 128;
+        rope_kv_write_bf16_vec_kernel<<<T, threads, (size_t)D * sizeof(float), stream>>>(
             (__nv_bfloat16*)qkv, positions, seq_of_token, block_table, max_blocks, inv_freq, (__nv_bfloat16*)kpages,
             (__nv_bfloat16*)vpages, H, Hkv, D, n_pages, err);
         return vm_launch_status();
