@@ -36,7 +36,7 @@ def test_embed_gather(table_dtype):
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-6), (torch.bfloat16, 2e-2)])
-@pytest.mark.parametrize("hid", [200, 576, 4100])
+@pytest.mark.parametrize("hid", [200, 576, 1600, 4100])      # (1600: a row no longer fits a warp's registers)
 @pytest.mark.parametrize("T", [19, 131])          # few rows: a block per row; many rows (bfloat16): a warp per row, four values per load
 def test_add_rmsnorm(dtype, tol, hid, T):
     eps = 3e-6

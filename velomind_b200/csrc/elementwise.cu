@@ -86,6 +86,47 @@ add_rmsnorm_bf16_vec_kernel(float* __restrict__ h, const __nv_bfloat16* __restri
     const uint2* drow = delta ? reinterpret_cast<const uint2*>(delta + (size_t)src * hid) : nullptr;
     float4* mine = reinterpret_cast<float4*>(vrow + (size_t)warp * hid);
     const int n4 = hid >> 2;
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+    uint2* orow = reinterpret_cast<uint2*>(out + (size_t)r * hid);
+    constexpr int NV = 8;                                // rows of up to 1,024 values: a lane's share stays in registers
+    if (n4 <= 32 * NV) {
+        // all loads of the row first (they do not depend on one another), then the arithmetic: one memory latency
+        float4 v[NV];
+        uint2 d[NV];
+#pragma unroll
+        for (int u = 0; u < NV; ++u) {
+            const int i = lane + 32 * u;
+            if (i < n4) { v[u] = hrow[i]; if (drow) d[u] = drow[i]; }
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int u = 0; u < NV; ++u) {
+            const int i = lane + 32 * u;
+            if (i < n4) {
+                if (drow) {
+                    const __nv_bfloat162 d01 = *reinterpret_cast<const __nv_bfloat162*>(&d[u].x), d23 = *reinterpret_cast<const __nv_bfloat162*>(&d[u].y);
+                    v[u].x += __low2float(d01); v[u].y += __high2float(d01); v[u].z += __low2float(d23); v[u].w += __high2float(d23);
+                    if (!rows) hrow[i] = v[u];
+                }
+                ss += v[u].x * v[u].x + v[u].y * v[u].y + v[u].z * v[u].z + v[u].w * v[u].w;
+            }
+        }
+        ss = vm_warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)hid + eps);
+#pragma unroll
+        for (int u = 0; u < NV; ++u) {
+            const int i = lane + 32 * u;
+            if (i < n4) {
+                const float4 ww = w4[i];
+                const __nv_bfloat162 o01 = __floats2bfloat162_rn(v[u].x * inv * ww.x, v[u].y * inv * ww.y);
+                const __nv_bfloat162 o23 = __floats2bfloat162_rn(v[u].z * inv * ww.z, v[u].w * inv * ww.w);
+                uint2 o;
+                o.x = *reinterpret_cast<const unsigned*>(&o01); o.y = *reinterpret_cast<const unsigned*>(&o23);
+                orow[i] = o;
+            }
+        }
+        return;
+    }
     float ss = 0.f;
     for (int i = lane; i < n4; i += 32) {
         float4 v = hrow[i];
@@ -100,8 +141,6 @@ add_rmsnorm_bf16_vec_kernel(float* __restrict__ h, const __nv_bfloat16* __restri
     }
     ss = vm_warp_sum(ss);
     const float inv = 1.0f / sqrtf(ss / (float)hid + eps);
-    const float4* w4 = reinterpret_cast<const float4*>(w);
-    uint2* orow = reinterpret_cast<uint2*>(out + (size_t)r * hid);
     for (int i = lane; i < n4; i += 32) {
         const float4 v = mine[i], ww = w4[i];
         const __nv_bfloat162 o01 = __floats2bfloat162_rn(v.x * inv * ww.x, v.y * inv * ww.y);
