@@ -221,7 +221,9 @@ __global__ void swiglu_bf16_vec_kernel(const uint4* __restrict__ gu, uint4* __re
         for (int k = 0; k < 4; ++k) {
             const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(&gw[k]), u2 = *reinterpret_cast<const __nv_bfloat162*>(&uw[k]);
             const float ga = __low2float(g2), gb = __high2float(g2);
-            const float sa = 1.0f / (1.0f + expf(-ga)), sb = 1.0f / (1.0f + expf(-gb));
+            // (float32 throughout; the hardware exponential and reciprocal are exact to a few units in the last place,
+            //  far inside what the bfloat16 result keeps)
+            const float sa = __frcp_rn(1.0f + __expf(-ga)), sb = __frcp_rn(1.0f + __expf(-gb));
             const __nv_bfloat162 o2 = __floats2bfloat162_rn((sa * ga) * __low2float(u2), (sb * gb) * __high2float(u2));
             ow[k] = *reinterpret_cast<const unsigned*>(&o2);
         }
