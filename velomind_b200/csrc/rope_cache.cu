@@ -75,6 +75,11 @@ rope_kv_write_bf16_vec_kernel(__nv_bfloat16* __restrict__ qkv, const int* __rest
                               const float* __restrict__ inv_freq, __nv_bfloat16* __restrict__ kpages,
                               __nv_bfloat16* __restrict__ vpages, int H, int Hkv, int D, int n_pages, int* __restrict__ err) {
     extern __shared__ float cs[];                       // [D/2] cosines, [D/2] sines
+    // Launched with programmatic dependent launch: it reads nothing before its predecessor is complete, and lets its
+    // successor start only then.  The successor may be the decode attention, which fetches the cache rows of EARLIER
+    // tokens in its preamble and this kernel's new rows after its own wait (the rule is in common.cuh).
+    vm_pdl_wait();
+    vm_pdl_launch_dependents();
     const int t = blockIdx.x;
     const int pos = positions[t];
     const int seq = seq_of_token[t];
@@ -144,9 +149,9 @@ VM_API int vm_rope_kv_write(void* qkv, const int* positions, const int* seq_of_t
         ((reinterpret_cast<uintptr_t>(kpages) | reinterpret_cast<uintptr_t>(vpages)) & 15) == 0) {
         // (a thread takes eight pairs of a head: 64 threads cover this model's 9 + 3 heads of 64 in one round)
         const int threads = (H + Hkv) * (D / 16) <= 64 ? 64 : 128;
-        rope_kv_write_bf16_vec_kernel<<<T, threads, (size_t)D * sizeof(float), stream>>>(
-            (__nv_bfloat16*)qkv, positions, seq_of_token, block_table, max_blocks, inv_freq, (__nv_bfloat16*)kpages,
-            (__nv_bfloat16*)vpages, H, Hkv, D, n_pages, err);
+        vm_launch_pdl(rope_kv_write_bf16_vec_kernel, dim3(T), dim3(threads), (size_t)D * sizeof(float), stream,
+                      (__nv_bfloat16*)qkv, positions, seq_of_token, block_table, max_blocks, inv_freq, (__nv_bfloat16*)kpages,
+                      (__nv_bfloat16*)vpages, H, Hkv, D, n_pages, err);
         return vm_launch_status();
     }
     const int work = (H + Hkv) * (rot_dim / 2) + Hkv * D;
