@@ -29,7 +29,7 @@ using namespace vmsk;
 // (PF: weight blocks a warp keeps in flight; 4 cover K <= 1,024 in one round and leave registers to the prologue)
 // (LOOP: a CTA takes several work items one after another; without it the grid has a CTA per item)
 template <int MT, int PF, bool LOOP>
-__global__ void __launch_bounds__(SK_THREADS, MT == 1 ? 2 : 1)
+__global__ void __launch_bounds__(SK_THREADS, (MT == 1 || (MT == 2 && PF == 4)) ? 2 : 1)
 skinny_gemm_kernel(const SkinnyParams p) {
     extern __shared__ __align__(16) unsigned char smem[];
     skinny_run<MT, true, PF, LOOP>(p, blockIdx.x, gridDim.x, p.n_items, smem);
@@ -93,7 +93,7 @@ int skinny_launch(SkinnyParams p, int grid, cudaStream_t stream) {
             int dev = 0;
             if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 1;
         }
-        const int resident = sms * ((MT == 1 && 2 * smem + 2048 <= 227 * 1024) ? 2 : 1);
+        const int resident = sms * (((MT == 1 || (MT == 2 && kc <= SK_WARPS * 32 * 4)) && 2 * smem + 2048 <= 227 * 1024) ? 2 : 1);
         const int per_cta = (grid + resident - 1) / resident;
         grid = (grid + per_cta - 1) / per_cta;
     }
