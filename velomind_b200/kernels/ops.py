@@ -286,8 +286,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
 
 
 SKINNY_MAX_ROWS = 32       # beyond this the library product wins (the A tile is staged once per CTA; measured per decode
-#                            step at 17 / 32 / 64 rows: 1.07 / 1.21 / 1.73 ms fused against 1.14 / 1.22 / 1.33 ms with cuBLAS)
-SKINNY_NORM_ROWS = 16      # up to this many rows the norm is fused into the product that follows it
+#                            step at 33 / 48 / 64 rows: 1.07 / 1.20 / 1.25 ms fused against 1.02 / 1.07 / 1.05 ms with cuBLAS)
+SKINNY_NORM_ROWS = 32      # up to this many rows the norm is fused into the product that follows it (measured per decode
+#                            step at 17 / 24 / 32 rows: 0.70 / 0.72 / 0.86 ms against 0.82 / 0.84 / 0.92 ms with a norm kernel)
 
 
 def skinny_ok(M: int, K: int, weight: torch.Tensor) -> bool:
