@@ -15,7 +15,11 @@
 // each thread fetches 16 contiguous bytes of a weight row per 32-wide k block straight from global memory
 // into the B fragments of two mma.sync m16n8k16 (bf16 in, float32 accumulate).  The k indices inside a
 // block are permuted the same way for A and B, which leaves the dot product unchanged and makes the
-// 16-byte loads possible.  A (at most 64 rows) sits in shared memory.
+// 16-byte loads possible.  A (at most 64 rows) sits in shared memory; when a product has more column tiles than the
+// GPU holds CTAs and all of K fits the tile, a CTA takes several tiles one after another with A staged once.
+// Under programmatic dependent launch the kernel requests its first weight blocks (and the rotary frequencies) before
+// it waits for its predecessor; the rope_kv form lets ITS successor, the decode attention, start only after that wait
+// (common.cuh says why).
 //
 // Sizes: K % 32 == 0, N % 8 == 0 (16 for the two-tile forms), head size % 16 == 0, I % 8 == 0; M <= 64.
 // Anything else is refused with VM_ERR_UNSUPPORTED and the caller uses the library product.
@@ -25,7 +29,7 @@ namespace {
 
 using namespace vmsk;
 
-// (two CTAs per SM for up to 16 rows: 192 gate/up items then fit the GPU at once)
+// (two CTAs per SM for up to 16 rows, and for up to 32 rows when K is at most 1,024: 192 gate/up items then fit the GPU at once)
 // (PF: weight blocks a warp keeps in flight; 4 cover K <= 1,024 in one round and leave registers to the prologue)
 // (LOOP: a CTA takes several work items one after another; without it the grid has a CTA per item)
 template <int MT, int PF, bool LOOP>
