@@ -179,6 +179,38 @@ def test_steps_that_want_no_logits(emulated, model_folders):
         engine.close(s)
 
 
+def test_step_described_ahead_is_dropped_when_a_slot_changes_hands(emulated, model_folders):
+    """After a decode step the engine describes the next one ahead of its tokens.  If a sequence of the batch ends and
+    another takes its slot and reaches the very same length, what was described ahead is stale (other pages): it has to
+    be noticed, whatever the lengths say."""
+    import velomind_b200 as vm
+    folder = model_folders["tiny_b"]
+    V = TINY_B["vocab_size"]
+    rng = np.random.default_rng(9)
+    a, b, c = ([int(t) for t in rng.integers(0, V, n)] for n in (70, 12, 13))
+    weights = P.read_model(folder)
+    model = vm.load_model(folder, torch.float32, "cpu")
+    engine = vm.Engine(model, 64 * 6, max_slots=2)
+    sa, sb = engine.open(), engine.open()
+    engine.step([vm.Entry(sa, a[:68], []), vm.Entry(sb, b[:11], [])])
+    out = engine.step([vm.Entry(sa, [a[68]], [0]), vm.Entry(sb, [b[11]], [0])])           # lengths now 69 and 12
+    assert np.abs(out.numpy() - np.stack([P.forward_logits(*weights, a[:69])[-1], P.forward_logits(*weights, b[:12])[-1]])).max() < 5e-6
+    engine.close(sb)
+    sc = engine.open()
+    assert sc == sb                                                                       # the same slot, another sequence
+    engine.step([vm.Entry(sc, c[:12], [])])                                               # ... at the same length: 12
+    out = engine.step([vm.Entry(sa, [a[69]], [0]), vm.Entry(sc, [c[12]], [0])])
+    want = np.stack([P.forward_logits(*weights, a[:70])[-1], P.forward_logits(*weights, c[:13])[-1]])
+    assert np.abs(out.numpy() - want).max() < 5e-6
+    # and the plain case: the same two sequences go on, from what was described ahead
+    a2, c2 = int(rng.integers(0, V)), int(rng.integers(0, V))
+    out = engine.step([vm.Entry(sa, [a2], [0]), vm.Entry(sc, [c2], [0])])
+    want = np.stack([P.forward_logits(*weights, a[:70] + [a2])[-1], P.forward_logits(*weights, c[:13] + [c2])[-1]])
+    assert np.abs(out.numpy() - want).max() < 5e-6
+    engine.close(sa); engine.close(sc)
+    assert engine.cache.tokens_held() == 0
+
+
 def test_step_refusals(emulated, model_folders):
     import velomind_b200 as vm
     model = vm.load_model(model_folders["tiny_a"], torch.float32, "cpu")
