@@ -190,15 +190,18 @@ def test_step_described_ahead_is_dropped_when_a_slot_changes_hands(emulated, mod
     a, b, c = ([int(t) for t in rng.integers(0, V, n)] for n in (70, 12, 13))
     weights = P.read_model(folder)
     model = vm.load_model(folder, torch.float32, "cpu")
-    engine = vm.Engine(model, 64 * 6, max_slots=2)
-    sa, sb = engine.open(), engine.open()
+    engine = vm.Engine(model, 64 * 6, max_slots=3)
+    sa, sb, sd = engine.open(), engine.open(), engine.open()
     engine.step([vm.Entry(sa, a[:68], []), vm.Entry(sb, b[:11], [])])
     out = engine.step([vm.Entry(sa, [a[68]], [0]), vm.Entry(sb, [b[11]], [0])])           # lengths now 69 and 12
     assert np.abs(out.numpy() - np.stack([P.forward_logits(*weights, a[:69])[-1], P.forward_logits(*weights, b[:12])[-1]])).max() < 5e-6
+    page_of_b = int(engine.cache.groups[0].block_table[sb, 0])
     engine.close(sb)
+    engine.step([vm.Entry(sd, a[:5], [])])                                                # a third sequence takes the freed page
     sc = engine.open()
     assert sc == sb                                                                       # the same slot, another sequence
     engine.step([vm.Entry(sc, c[:12], [])])                                               # ... at the same length: 12
+    assert int(engine.cache.groups[0].block_table[sc, 0]) != page_of_b                    # ... in another page
     out = engine.step([vm.Entry(sa, [a[69]], [0]), vm.Entry(sc, [c[12]], [0])])
     want = np.stack([P.forward_logits(*weights, a[:70])[-1], P.forward_logits(*weights, c[:13])[-1]])
     assert np.abs(out.numpy() - want).max() < 5e-6
@@ -207,7 +210,7 @@ def test_step_described_ahead_is_dropped_when_a_slot_changes_hands(emulated, mod
     out = engine.step([vm.Entry(sa, [a2], [0]), vm.Entry(sc, [c2], [0])])
     want = np.stack([P.forward_logits(*weights, a[:70] + [a2])[-1], P.forward_logits(*weights, c[:13] + [c2])[-1]])
     assert np.abs(out.numpy() - want).max() < 5e-6
-    engine.close(sa); engine.close(sc)
+    engine.close(sa); engine.close(sc); engine.close(sd)
     assert engine.cache.tokens_held() == 0
 
 
