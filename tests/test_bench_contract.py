@@ -1,0 +1,44 @@
+"""bench.py's answers that need no GPU: the reference arm's `unavailable` line, the refusal of more than one GPU, and
+the roofline arithmetic (bytes of a decode step, FLOPs per token) for a known configuration."""
+import json
+import os
+import subprocess
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(*args):
+    return subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), *args], capture_output=True, text=True, timeout=300,
+                          env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
+
+
+def test_reference_arm_says_why_it_is_unavailable():
+    proc = _run("--impl", "reference", "--gpus", "1", "--steps", "2", "--warmup", "1")
+    assert proc.returncode == 0
+    line = json.loads(proc.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and isinstance(line["unavailable"], str) and "\n" not in line["unavailable"]
+
+
+def test_more_than_one_gpu_is_refused_with_one_line():
+    proc = _run("--gpus", "2", "--steps", "2", "--warmup", "1")
+    assert proc.returncode == 2
+    lines = [ln for ln in proc.stdout.strip().splitlines() if ln.strip()]
+    assert len(lines) == 1 and "--gpus 2" in lines[0]
+
+
+def test_step_bytes_and_flops_of_the_benchmark_shape():
+    sys.path.insert(0, ROOT)
+    import bench
+    import velomind_b200 as vm
+    cfg = dict(vm.SMOLLM2_135M)
+    per_layer, weight_bytes, kv_per_token, D = bench.model_bytes_and_flops(cfg, cfg["num_hidden_layers"])
+    hid, I, H, Hkv = 576, 1536, 9, 3
+    assert D == 64
+    assert per_layer == hid * (H + 2 * Hkv) * D + H * D * hid + 3 * hid * I          # weights of a layer = multiply-adds per token
+    # every weight a decode step uses once, in bfloat16: the layers, the two norms' vectors and the tied table as head
+    assert weight_bytes >= 2 * (30 * per_layer + cfg["vocab_size"] * hid)
+    assert weight_bytes <= 2 * (30 * per_layer + cfg["vocab_size"] * hid) + 4 * 61 * hid * 2
+    assert kv_per_token == 30 * 2 * Hkv * D * 2                                      # keys and values, bfloat16, per cached token
+    pk = bench.peaks()
+    assert pk["source"] in ("measured", "fallback") and pk["hbm_gbs"] > 0 and pk["bf16_tflops"] > 0
