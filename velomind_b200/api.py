@@ -132,6 +132,18 @@ class TextEngine:
         engine.raise_if_error()
         return results
 
+    def describe(self) -> Dict[str, Any]:
+        """What the reference console's /model prints (llama_interactive_console.cpp:145-158): device, mode and the
+        model's sizes, read from the plan's parts."""
+        plan = self.model.plan
+        first = plan.blocks[plan.schedule[0].layer] if plan.schedule else None
+        mixer = first.mixer.args if first is not None else {}
+        ff = first.feed_forward.args if first is not None else {}
+        return {"Backend": self.config.device, "Mode": "Synthetic" if self.config.use_synthetic else "Real model",
+                "Vocab": f"{plan.vocab_size} tokens", "Hidden": plan.hidden_size, "Layers": len(plan.schedule),
+                "Heads": f"{mixer.get('heads', '?')} (kv={mixer.get('kv_heads', '?')})", "HeadDim": mixer.get("head_dim", "?"),
+                "Intermed": ff.get("intermediate", "?"), "Dtype": self.config.dtype}
+
     def default_stop_tokens(self):
         if self.tokenizer is not None and self.tokenizer.eos_id is not None and self.tokenizer.eos_id >= 0:
             return (self.tokenizer.eos_id,)
