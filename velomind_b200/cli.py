@@ -11,8 +11,8 @@ the same option names and defaults where it has them.
     --prompt <string>     single non-interactive prompt; without it a `>>>` loop reads prompts and the
                           reference console's commands (examples/common/llama/llama_interactive_console.cpp:125-309):
                           /help /temp /top_p /max /system /clear /history /model /save /load /exit /quit
-Additions: --prompt-ids 1,2,3 (token ids, for models without a tokenizer), --seed (default 42, the
-reference's fixed seed), --dtype bfloat16|float32, --config <config.json> for --synthetic.
+Additions: --prompt-ids 1,2,3 (token ids, for models without a tokenizer), --prompt-file <path>, --seed (default 42,
+the reference's fixed seed), --dtype bfloat16|float32 (--fp32 for short), --config <config.json> for --synthetic.
 The reference's --download is not offered (no network).
 """
 from __future__ import annotations
@@ -37,8 +37,11 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--max-tokens", type=int, default=32, dest="max_tokens")
     ap.add_argument("--prompt", default="")
     ap.add_argument("--prompt-ids", default="", dest="prompt_ids")
+    ap.add_argument("--prompt-file", default="", dest="prompt_file",
+                    help="a file holding the prompt: text, or token ids when the model has no tokenizer")
     ap.add_argument("--seed", type=int, default=42)
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap.add_argument("--fp32", action="store_true", help="the true 32-bit path of the whole model (the same as --dtype float32)")
     return ap
 
 
@@ -203,6 +206,8 @@ class Console:
 
 def main(argv=None) -> int:
     args = build_parser().parse_args(argv)
+    if args.fp32:
+        args.dtype = "float32"
     model_config = None
     if args.config:
         with open(args.config) as f:
@@ -216,6 +221,13 @@ def main(argv=None) -> int:
         print(f"Initializing engine on device [{cfg.device}]...")
         engine = TextEngine(cfg).load()
         print("Engine ready.")
+        if args.prompt_file:
+            with open(args.prompt_file) as f:
+                text = f.read().strip()
+            if engine.tokenizer is None:
+                args.prompt_ids = text
+            else:
+                args.prompt = text
         if args.prompt_ids:
             _run_turn(engine, [int(t) for t in args.prompt_ids.replace(",", " ").split()], args)
             return 0
