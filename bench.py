@@ -28,6 +28,16 @@ sys.path.insert(0, ROOT)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
+# other shapes of the family (config.json keys that differ from the 135M sizes): the benchmark itself is the 135M shape
+SHAPES = {
+    "135m": {},
+    "360m": {"num_hidden_layers": 32, "hidden_size": 960, "num_attention_heads": 15, "num_key_value_heads": 5,
+             "intermediate_size": 2560},
+    "1.7b": {"num_hidden_layers": 24, "hidden_size": 2048, "num_attention_heads": 32, "num_key_value_heads": 32,
+             "intermediate_size": 8192, "rope_theta": 130000.0},
+}
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     out = dict(FALLBACK_PEAKS)
@@ -184,6 +194,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0: all); reported in config")
     ap.add_argument("--quick", action="store_true", help="skip the batch 1 / 64 points and the end-to-end run")
+    ap.add_argument("--shape", default="135m", choices=sorted(SHAPES),
+                    help="sizes of the random model: the benchmark's SmolLM2-135M (default), or the 360M / 1.7B shapes of the family")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -200,6 +212,7 @@ def main() -> int:
     from velomind_b200.kernels import ops
 
     cfg = dict(vm.SMOLLM2_135M)
+    cfg.update(SHAPES[args.shape])
     full_layers = cfg["num_hidden_layers"]
     layers = args.layers or full_layers
     cfg["num_hidden_layers"] = layers
@@ -255,10 +268,10 @@ def main() -> int:
         te.generate(prompts, temperature=0.0, max_tokens=args.steps + 1, stop_tokens=(), steps_per_sync=8)
         points["e2e_queued_8"] = B * te.last_timing.decode_steps / te.last_timing.decode_seconds
     line = {
-        "metric": "decode tok/s at batch 8 (SmolLM2-135M shape, prompts of 512 tokens)",
+        "metric": f"decode tok/s at batch 8 (SmolLM2-{args.shape.upper()} shape, prompts of 512 tokens)",
         "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"model": "SmolLM2-135M shape, random weights", "global_batch": B, "seq_len": prompt_len, "context": context,
+        "config": {"model": f"SmolLM2-{args.shape.upper()} shape, random weights", "global_batch": B, "seq_len": prompt_len, "context": context,
                    "parallelism": "single GPU", "layers": layers, "layers_of_config": full_layers,
                    "hidden": cfg["hidden_size"], "heads": H, "kv_heads": cfg["num_key_value_heads"], "head_dim": D,
                    "intermediate": cfg["intermediate_size"], "vocab": vocab, "rope_theta": cfg["rope_theta"],
