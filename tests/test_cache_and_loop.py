@@ -154,6 +154,30 @@ def test_step_function_with_stand_in_kernels(emulated, model_folders, name, cfg)
         assert engine.cache.slots.held_count == 0 and engine.cache.tokens_held() == 0
 
 
+def test_poisoned_scratch_changes_nothing(emulated, model_folders):
+    """With `poison_freed` every scratch buffer is filled with NaN the moment a part gives it back: a part that gave a
+    buffer back before its last reader ran, or read one it no longer holds, would show in the logits."""
+    import velomind_b200 as vm
+    folder = model_folders["tiny_b"]
+    requests = S.make_requests(TINY_B["vocab_size"], (5, 70, 2, 33), seed=8)
+    plain = S.plain_logits(folder, requests)
+    model = vm.load_model(folder, torch.float32, "cpu")
+    for cut in (S.steps_whole, S.steps_unequal_batches):
+        engine = vm.Engine(model, 64 * 6, max_slots=3, poison_freed=True)
+        steps = cut(requests)
+        got = S.run_steps_in_process(engine, steps)
+        want = S.expected_rows(steps, requests, plain)
+        assert max(float(np.abs(got[k] - want[k]).max()) for k in want) < 5e-6
+    # the poison itself: a buffer that was given back reads NaN
+    ws = engine.ws
+    ws.begin(("poison test",))
+    t = ws.take((4, 8), torch.float32)
+    t.zero_()
+    ws.give(t)
+    assert torch.isnan(t).all()
+    ws.end()
+
+
 def test_steps_that_want_no_logits(emulated, model_folders):
     """A prompt cut by the caller into steps of which only the last wants logits: the earlier steps return no rows (in
     whichever order steps with and without wanted rows first meet a capacity bucket) and leave the cache as a whole

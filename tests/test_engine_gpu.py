@@ -53,6 +53,19 @@ def test_cuts_match_plain(model_folders, name, dtype, cut):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_poisoned_scratch_changes_nothing(model_folders, dtype):
+    """`poison_freed`: every scratch buffer is filled with NaN the moment a part gives it back (in stream order, also
+    inside the recorded graphs).  A part that gave a buffer back before launching its last reader would show here."""
+    folder = model_folders["tiny_b"]
+    requests = S.make_requests(TINY_B["vocab_size"], LENGTHS, seed=4)
+    plain = S.plain_logits(folder, requests)
+    engine = _engine(folder, dtype, max_tokens=64 * 8, max_slots=3, poison_freed=True)
+    steps = S.steps_unequal_batches(requests)
+    got = S.run_steps_in_process(engine, steps)
+    _compare(got, S.expected_rows(steps, requests, plain), TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding(model_folders, dtype):
     """300 tokens one by one from a 3-token prompt: crosses several pages; compared at every position."""
     folder = model_folders["tiny_b"]

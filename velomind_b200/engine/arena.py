@@ -64,8 +64,9 @@ class Workspace:
     """Hands out step buffers.  `begin(key)` opens a step of capacity bucket `key`; `take`/`give` bracket each
     buffer's life; `end()` closes the step (and, the first time, turns the recording into a plan)."""
 
-    def __init__(self, device):
+    def __init__(self, device, poison: bool = False):
         self.device = device
+        self.poison = bool(poison)              # debugging aid: a buffer that is given back is filled with NaN (integers: -1)
         self.arena: Optional[torch.Tensor] = None
         self.generation = 0                     # bumped when the arena moves (captured graphs must be dropped)
         self.plans: Dict[object, ArenaPlan] = {}
@@ -118,6 +119,10 @@ class Workspace:
         self._clock += 1
         if self._recording:
             self._log[idx][2] = self._clock
+        if self.poison and t.numel():
+            # whoever reads the buffer after this point (a part that gave it back too early, a kernel still to run on
+            # it) now reads NaN, and the step's result shows it
+            t.fill_(float("nan") if t.dtype.is_floating_point else -1)
 
     def end(self) -> None:
         if self._live:

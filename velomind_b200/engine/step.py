@@ -186,7 +186,7 @@ class Engine:
     def __init__(self, model: DecoderModel, max_tokens: int, max_slots: Optional[int] = None,
                  max_step_tokens: int = 8192, use_graphs: Optional[bool] = None,
                  fused_prefill_rows: Optional[int] = None, persistent_decode: bool = False,
-                 cluster_decode: Optional[bool] = None):
+                 cluster_decode: Optional[bool] = None, poison_freed: bool = False):
         if model.device is None:
             raise RuntimeError("the model has no weights bound; use load_model()")
         self.model = model
@@ -199,7 +199,8 @@ class Engine:
         max_tokens = -(-int(max_tokens) // PAGE_TOKENS) * PAGE_TOKENS
         self.cache = SequenceCache(model.cache_needs(), model.cache_shares(), max_tokens, model.plan.max_positions,
                                    self.dtype, self.device, max_slots)
-        self.ws = Workspace(self.device)
+        # (poison_freed: a debugging aid; every scratch buffer is filled with NaN the moment it is given back)
+        self.ws = Workspace(self.device, poison=poison_freed)
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._desc: Dict[Tuple, Descriptors] = {}
         self._logits: Optional[torch.Tensor] = None
