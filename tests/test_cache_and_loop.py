@@ -154,6 +154,36 @@ def test_step_function_with_stand_in_kernels(emulated, model_folders, name, cfg)
         assert engine.cache.slots.held_count == 0 and engine.cache.tokens_held() == 0
 
 
+def test_sampler_keeps_its_parameter_block_while_requests_move_on_together(emulated):
+    """The device sampler uploads (temperature, top-p, seed, stream, step) per row; while the same requests all move on
+    by the same number of draws it leaves the block where it is and hands the kernel the offset.  The draws are the
+    same either way, and anything else (other parameters, rows that move on unevenly, other rows) uploads again."""
+    from velomind_b200.sampling.sampler import DeviceSampler, SamplingParams
+    rng = np.random.default_rng(0)
+    V = 50
+    params = [SamplingParams(temperature=0.8, top_p=0.9, seed=7), SamplingParams(temperature=1.3, top_p=1.0, seed=9)]
+    logits = [torch.from_numpy(rng.standard_normal((2, V)).astype(np.float32)) for _ in range(6)]
+
+    def expected(row, p, stream, step):
+        return P.sample_top_p(row.numpy(), p.temperature, p.top_p, P.uniform01(p.seed, stream, step))
+
+    kept = DeviceSampler("cpu")
+    for step, lg in enumerate(logits[:4]):                       # steps 0, 1, 2, 3: one upload, then offsets 1, 2, 3
+        got = kept.sample(lg, params, [0, 1], [step, step])
+        assert list(got) == [expected(lg[r], params[r], r, step) for r in range(2)]
+        if step == 0:
+            block = kept._uploaded
+        assert kept._uploaded is block
+    got = kept.sample(logits[4], params, [0, 1], [4, 6])          # the rows move on unevenly: a new upload
+    assert kept._uploaded is not block and list(got) == [expected(logits[4][0], params[0], 0, 4), expected(logits[4][1], params[1], 1, 6)]
+    block = kept._uploaded
+    other = [params[0], SamplingParams(temperature=0.0)]           # other parameters (greedy row): a new upload
+    got = kept.sample(logits[5], other, [0, 1], [5, 7])
+    assert kept._uploaded is not block and int(got[1]) == int(logits[5][1].argmax())
+    got = kept.sample(logits[5][:1], other[:1], [0], [6])          # fewer rows: a new upload
+    assert list(got) == [expected(logits[5][0], params[0], 0, 6)]
+
+
 def test_poisoned_scratch_changes_nothing(emulated, model_folders):
     """With `poison_freed` every scratch buffer is filled with NaN the moment a part gives it back: a part that gave a
     buffer back before its last reader ran, or read one it no longer holds, would show in the logits."""
