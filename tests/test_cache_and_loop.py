@@ -154,6 +154,76 @@ def test_step_function_with_stand_in_kernels(emulated, model_folders, name, cfg)
         assert engine.cache.slots.held_count == 0 and engine.cache.tokens_held() == 0
 
 
+def test_op_times_bracket_every_launch_and_restore_the_wrappers(emulated, model_folders):
+    """The switchable per-operation timer: inside the block every launching function of `ops` is bracketed by two events,
+    outside it the functions are the ones they were.  (Stand-in events with a counter as clock: no device here.)"""
+    import velomind_b200 as vm
+    from velomind_b200.kernels import ops
+    from velomind_b200.kernels.optimes import OpTimes
+
+    clock = [0.0]
+
+    class Event:
+        def record(self):
+            clock[0] += 1.0
+            self.at = clock[0]
+
+        def synchronize(self):
+            pass
+
+        def elapsed_time(self, other):
+            return other.at - self.at
+
+    model = vm.load_model(model_folders["tiny_a"], torch.float32, "cpu")
+    engine = vm.Engine(model, 64 * 2, max_slots=1)
+    s = engine.open()
+    before = {n: getattr(ops, n) for n in ("linear", "add_rmsnorm", "rope_kv_write", "swiglu")}
+    with OpTimes(event=Event) as times:
+        assert ops.linear is not before["linear"]
+        engine.step([vm.Entry(s, [1, 2, 3], [2])])
+    assert all(getattr(ops, n) is fn for n, fn in before.items())
+    layers = TINY_A["num_hidden_layers"]
+    assert times.calls["rope_kv_write"] == layers and times.calls["swiglu"] == layers
+    assert times.calls["add_rmsnorm"] == 2 * layers + 1 and times.calls["linear"] == 4 * layers + 1
+    assert all(ms > 0 for ms in times.ms.values()) and "operation" in times.table() and "linear" in times.table()
+    engine.close(s)
+
+
+def test_injected_failures_leave_the_engine_usable(emulated, model_folders, monkeypatch):
+    """Failures made on the host (never on the device): a step whose N-th scratch buffer is refused raises, holds no
+    workspace, and the same step run again gives the right logits; a kernel wrapper told to fail names its op."""
+    import velomind_b200 as vm
+    from velomind_b200.kernels import ops
+    folder = model_folders["tiny_a"]
+    tokens = [int(t) for t in np.random.default_rng(6).integers(0, TINY_A["vocab_size"], 40)]
+    ref = P.forward_logits(*P.read_model(folder), tokens)
+    model = vm.load_model(folder, torch.float32, "cpu")
+    engine = vm.Engine(model, 64 * 2, max_slots=2)
+    s = engine.open()
+    engine.ws.fail_after = 3
+    with pytest.raises(RuntimeError, match="injected failure: buffer 3"):
+        engine.step([vm.Entry(s, tokens[:30], [29])])
+    assert engine.length(s) == 0                                   # nothing was committed
+    engine.ws.fail_after = None
+    out = engine.step([vm.Entry(s, tokens[:30], [29])])            # the same step again
+    assert np.abs(out.numpy()[0] - ref[29]).max() < 5e-6
+    engine.ws.fail_after = 2                                       # ... and in a decode step
+    with pytest.raises(RuntimeError, match="injected failure"):
+        engine.step([vm.Entry(s, [tokens[30]], [0])])
+    assert engine.length(s) == 30
+    engine.ws.fail_after = None
+    out = engine.step([vm.Entry(s, [tokens[30]], [0])])
+    assert np.abs(out.numpy()[0] - ref[30]).max() < 5e-6
+    engine.close(s)
+    engine.cache.check()
+    assert engine.cache.tokens_held() == 0
+    # the kernel wrappers' own switch: the op of that name raises after its launch
+    monkeypatch.setattr(ops, "FAIL_OP", "rope_kv_write")
+    ops._check(0, "add_rmsnorm")
+    with pytest.raises(ops.KernelError, match="rope_kv_write: injected failure"):
+        ops._check(0, "rope_kv_write")
+
+
 def test_sampler_keeps_its_parameter_block_while_requests_move_on_together(emulated):
     """The device sampler uploads (temperature, top-p, seed, stream, step) per row; while the same requests all move on
     by the same number of draws it leaves the block where it is and hands the kernel the offset.  The draws are the

@@ -47,6 +47,7 @@ class EngineConfig:
     dtype: str = "bfloat16"
     max_tokens: int = 65536              # cached tokens of live sequences (whole pages of 64)
     max_batch: int = 64
+    use_graphs: Optional[bool] = None    # None: the engine's default (decode steps replayed from CUDA graphs)
 
 
 class TextEngine:
@@ -75,7 +76,7 @@ class TextEngine:
         if os.path.isfile(folder):               # the reference takes the path of model.safetensors itself
             folder = os.path.dirname(folder) or "."
         self.model = load_model(folder, DTYPES[cfg.dtype], cfg.device)
-        self.engine = Engine(self.model, cfg.max_tokens)
+        self.engine = Engine(self.model, cfg.max_tokens, use_graphs=cfg.use_graphs)
         self.sampler = DeviceSampler(self.engine.device, cfg.max_batch)
         tok_path = cfg.tokenizer_path or os.path.join(folder, "tokenizer.json")
         if os.path.isfile(tok_path):

@@ -12,7 +12,8 @@ the same option names and defaults where it has them.
                           reference console's commands (examples/common/llama/llama_interactive_console.cpp:125-309):
                           /help /temp /top_p /max /system /clear /history /model /save /load /exit /quit
 Additions: --prompt-ids 1,2,3 (token ids, for models without a tokenizer), --prompt-file <path>, --seed (default 42,
-the reference's fixed seed), --dtype bfloat16|float32 (--fp32 for short), --config <config.json> for --synthetic.
+the reference's fixed seed), --dtype bfloat16|float32 (--fp32 for short), --config <config.json> for --synthetic,
+--op-times (device time per kind of operation after each response).
 The reference's --download is not offered (no network).
 """
 from __future__ import annotations
@@ -42,6 +43,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--seed", type=int, default=42)
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--fp32", action="store_true", help="the true 32-bit path of the whole model (the same as --dtype float32)")
+    ap.add_argument("--op-times", action="store_true", dest="op_times",
+                    help="after each response, print the device time per kind of operation (kernels launched one by one, no CUDA graphs)")
     return ap
 
 
@@ -63,9 +66,17 @@ def _run_turn(engine: TextEngine, prompt, args):
         print(piece, end="", flush=True)
 
     t0 = time.perf_counter()
-    res = engine.generate([prompt], temperature=args.temp, top_p=args.top_p, max_tokens=args.max_tokens, seed=args.seed,
-                          on_token=show)[0]
-    dt = time.perf_counter() - t0
+    if getattr(args, "op_times", False):
+        from .kernels.optimes import OpTimes
+        with OpTimes() as times:
+            res = engine.generate([prompt], temperature=args.temp, top_p=args.top_p, max_tokens=args.max_tokens, seed=args.seed,
+                                  on_token=show)[0]
+        dt = time.perf_counter() - t0
+        print("\n\n" + times.table(), end="")
+    else:
+        res = engine.generate([prompt], temperature=args.temp, top_p=args.top_p, max_tokens=args.max_tokens, seed=args.seed,
+                              on_token=show)[0]
+        dt = time.perf_counter() - t0
     rate = len(res.tokens) / dt if dt > 0 else 0.0
     print(f"\n\n[{len(res.tokens)} tokens in {dt:.3f}s ({rate:.1f} tok/s)]")
     return res, dt, "".join(pieces)
@@ -217,7 +228,8 @@ def main(argv=None) -> int:
         return 1
     try:
         cfg = EngineConfig(model_path=args.model, tokenizer_path=args.tokenizer, device=_device(args.device),
-                           use_synthetic=args.synthetic, model_config=model_config, seed=args.seed, dtype=args.dtype)
+                           use_synthetic=args.synthetic, model_config=model_config, seed=args.seed, dtype=args.dtype,
+                           use_graphs=False if args.op_times else None)
         print(f"Initializing engine on device [{cfg.device}]...")
         engine = TextEngine(cfg).load()
         print("Engine ready.")

@@ -14,6 +14,7 @@ with no allocation.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -67,6 +68,10 @@ class Workspace:
     def __init__(self, device, poison: bool = False):
         self.device = device
         self.poison = bool(poison)              # debugging aid: a buffer that is given back is filled with NaN (integers: -1)
+        # host-side fault injection (the reference's VELOMIND_FAIL_GRAPH_BUILD_AFTER_ALLOCATIONS, graph_compiler.cpp:562-569):
+        # the N-th buffer a step asks for raises instead; the step is abandoned and can be run again
+        env = os.environ.get("VELOMIND_B200_FAIL_STEP_AFTER_BUFFERS", "")
+        self.fail_after: Optional[int] = int(env) if env.isdigit() else None
         self.arena: Optional[torch.Tensor] = None
         self.generation = 0                     # bumped when the arena moves (captured graphs must be dropped)
         self.plans: Dict[object, ArenaPlan] = {}
@@ -96,6 +101,8 @@ class Workspace:
             numel *= int(d)
         nbytes = numel * torch.empty((), dtype=dtype).element_size()
         idx = self._next
+        if self.fail_after is not None and idx >= self.fail_after:
+            raise RuntimeError(f"injected failure: buffer {idx} of the step was refused (fail_after = {self.fail_after})")
         self._next += 1
         self._clock += 1
         if self._recording:

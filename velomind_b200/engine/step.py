@@ -207,7 +207,8 @@ class Engine:
         self._graphs: Dict[Tuple, "torch.cuda.CUDAGraph"] = {}
         self._next_decode: Optional[Descriptors] = None     # the buffer that holds a decode step described ahead
         self._last_decode_desc, self._last_decode_widths = None, None
-        self.use_graphs = (GRAPHS_DEFAULT if use_graphs is None else bool(use_graphs)) and model.graph_safe
+        # (waiting for the device after every launch, a debugging switch of the kernel wrappers, cannot be recorded)
+        self.use_graphs = (GRAPHS_DEFAULT if use_graphs is None else bool(use_graphs)) and model.graph_safe and not ops.SYNC_EVERY_OP
         self.graphs_captured = 0
         self._shape_seen: Dict[Tuple, int] = {}
         self._run_state = None

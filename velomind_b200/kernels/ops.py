@@ -8,6 +8,7 @@ per engine); the residual stream is always float32.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -24,6 +25,12 @@ library_calls = 0         # library matrix products (cuBLAS through torch.mm)
 h2d_bytes = 0             # bytes of step inputs copied from pinned host memory (descriptors, sampler parameters)
 d2h_bytes = 0             # bytes of step results that reached the host (sampled tokens)
 tc_attention_calls = 0    # launches of the tcgen05 prefill attention (tests check that long prompts take it)
+
+
+# Debugging switches, read once from the environment (the reference has VELOMIND_CUDA_SYNC and VELOMIND_FAIL_BACKEND for
+# the same purposes: src/cuda/cuda_context.cu:115-118, src/cuda/ops/backend_error.h:31-51).  Both act on the host only.
+SYNC_EVERY_OP = os.environ.get("VELOMIND_B200_SYNC", "") == "1"    # wait for the device after every launch: an error names its op
+FAIL_OP = os.environ.get("VELOMIND_B200_FAIL_OP", "")              # the op of this name raises after its launch (fault injection)
 
 
 class KernelError(RuntimeError):
@@ -59,6 +66,13 @@ def _check(status: int, name: str) -> None:
     global launch_count
     launch_count += 1
     if status == 0:
+        if FAIL_OP and name == FAIL_OP:
+            raise KernelError(f"{name}: injected failure (VELOMIND_B200_FAIL_OP)")
+        if SYNC_EVERY_OP:
+            try:
+                torch.cuda.synchronize()
+            except RuntimeError as ex:
+                raise KernelError(f"{name}: {ex}") from None
         return
     if status == -1:
         raise KernelError(f"{name}: this size or dtype is not supported by the kernel")
