@@ -128,55 +128,62 @@ class GenerationLoop:
             t0 = time.perf_counter()
             feed = {i: list(requests[i].prompt) for i, _ in live}
             step_no = 0
+            timing, default_stop = self.timing, self.default_stop
+            # what the batch's live sequences bring to every step, kept while none of them ends
+            live_params = [requests[i].params for i, _ in live]
+            live_streams = [requests[i].stream for i, _ in live]
+            live_tokens = [results[i].tokens for i, _ in live]
             while live:
                 run = self._run_length(requests, results, live, step_no)
+                drawn = [len(t) for t in live_tokens]
                 if run > 1:
-                    rows = stepper.decode_many(
-                        [slot for _, slot in live], [feed[i][0] for i, _ in live], [requests[i].params for i, _ in live],
-                        [requests[i].stream for i, _ in live], [len(results[i].tokens) for i, _ in live], run)
+                    rows = stepper.decode_many([slot for _, slot in live], [feed[i][0] for i, _ in live], live_params,
+                                               live_streams, drawn, run)
                 else:
                     entries = [Entry(slot, feed[i], [len(feed[i]) - 1]) for i, slot in live]
                     logits = stepper.step(entries)
-                    rows = [self.sampler.sample(
-                        logits, [requests[i].params for i, _ in live],
-                        [requests[i].stream for i, _ in live],
-                        [len(results[i].tokens) for i, _ in live])]
+                    rows = [self.sampler.sample(logits, live_params, live_streams, drawn)]
                 now = time.perf_counter()
                 if step_no == 0:
-                    self.timing.prefill_seconds += now - t0
+                    timing.prefill_seconds += now - t0
                 else:
-                    self.timing.decode_seconds += now - t0
-                    self.timing.decode_steps += len(rows)
+                    timing.decode_seconds += now - t0
+                    timing.decode_steps += len(rows)
                 t0 = now
                 ended = set()
                 for tokens in rows:                      # one row of tokens per step of the run
-                    for (i, slot), tok in zip(live, tokens):
+                    tokens = tokens.tolist() if hasattr(tokens, "tolist") else tokens
+                    for (i, slot), par, out, tok in zip(live, live_params, live_tokens, tokens):
                         if i in ended:
                             continue                     # the sequence ended earlier in this run: the rest is not its output
                         tok = int(tok)
-                        res, par = results[i], requests[i].params
-                        res.tokens.append(tok)
-                        self.timing.generated_tokens += 1
+                        out.append(tok)
+                        timing.generated_tokens += 1
                         if on_token is not None:
                             on_token(i, tok)
-                        stops = par.stop_tokens if par.stop_tokens else self.default_stop
-                        if tok in stops:
-                            res.finish_reason = "stop"
-                        elif len(res.tokens) >= par.max_tokens:
-                            res.finish_reason = "length"
+                        reason = ""
+                        if tok in (par.stop_tokens or default_stop):
+                            reason = "stop"
+                        elif len(out) >= par.max_tokens:
+                            reason = "length"
                         elif tok < 0:
-                            res.finish_reason = "error"
-                        if res.finish_reason:
+                            reason = "error"
+                        if reason:
+                            results[i].finish_reason = reason
                             ended.add(i)
                         else:
                             feed[i] = [tok]
-                still = []
-                for (i, slot) in live:
-                    if i in ended:
-                        stepper.close(slot)              # the slot and its pages are free for the next batch at once
-                    else:
-                        still.append((i, slot))
-                live = still
+                if ended:
+                    still = []
+                    for (i, slot) in live:
+                        if i in ended:
+                            stepper.close(slot)          # the slot and its pages are free for the next batch at once
+                        else:
+                            still.append((i, slot))
+                    live = still
+                    live_params = [requests[i].params for i, _ in live]
+                    live_streams = [requests[i].stream for i, _ in live]
+                    live_tokens = [results[i].tokens for i, _ in live]
                 step_no += len(rows)
         except Exception:
             for _, slot in live:
