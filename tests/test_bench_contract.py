@@ -42,3 +42,20 @@ def test_step_bytes_and_flops_of_the_benchmark_shape():
     assert kv_per_token == 30 * 2 * Hkv * D * 2                                      # keys and values, bfloat16, per cached token
     pk = bench.peaks()
     assert pk["source"] in ("measured", "fallback") and pk["hbm_gbs"] > 0 and pk["bf16_tflops"] > 0
+
+
+def test_trace_run_without_a_gpu_says_so_in_one_line(tmp_path):
+    """No CPU fallback: with no CUDA device visible the replay program refuses with one clear line and exit code 1."""
+    sys.path.insert(0, ROOT)
+    import velomind_b200 as vm
+    from tiny_configs import TINY_A, TINY_A_INIT
+    folder = str(tmp_path / "model")
+    vm.write_random_model(folder, TINY_A, **TINY_A_INIT)
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", "float32",
+                           "--out", str(tmp_path / "out"), "--max-tokens", "64"],
+                          input='{"step": 0, "entries": [{"id": "a", "tokens": [1, 2], "want": [1]}], "end": ["a"]}\n',
+                          capture_output=True, text=True, timeout=300, env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
+    assert proc.returncode == 1
+    lines = [ln for ln in proc.stderr.strip().splitlines() if ln.strip()]
+    assert lines[-1].startswith("trace_run: error:") and "no CPU fallback" in lines[-1] and "Traceback" not in proc.stderr
+    assert "done" not in proc.stdout

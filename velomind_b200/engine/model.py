@@ -8,6 +8,8 @@ from typing import Dict, List, Optional
 
 import torch
 
+from ..kernels import ops
+
 from ..cache.store import CacheNeed
 from ..config.base import read_config_json
 from ..config.registry import resolve
@@ -63,6 +65,7 @@ class DecoderModel:
 
     def bind(self, tensors: Dict[str, torch.Tensor], dtype: torch.dtype, device) -> None:
         """Put the host tensors (names of `weight_table`) on `device` for compute dtype `dtype`."""
+        ops.require_cuda(device)                 # (one clear refusal before the first tensor moves: there is no CPU fallback)
         bc = BindContext(dtype, torch.device(device))
         for prefix, part in self.named_parts():
             part.bind({name: tensors[prefix + name] for name in part.weight_specs()}, bc)

@@ -66,5 +66,16 @@ def main(argv=None) -> int:
     return 0
 
 
+def run(argv=None) -> int:
+    """`main` for the command line: a failure is one line on stderr and exit code 1, not a traceback."""
+    try:
+        return main(argv)
+    except (KeyboardInterrupt, BrokenPipeError):
+        return 130
+    except Exception as ex:
+        print(f"trace_run: error: {type(ex).__name__}: {ex}", file=sys.stderr, flush=True)
+        return 1
+
+
 if __name__ == "__main__":
-    sys.exit(main())
+    sys.exit(run())
