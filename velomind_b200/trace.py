@@ -73,7 +73,9 @@ def run(argv=None) -> int:
     except (KeyboardInterrupt, BrokenPipeError):
         return 130
     except Exception as ex:
-        print(f"trace_run: error: {type(ex).__name__}: {ex}", file=sys.stderr, flush=True)
+        if os.environ.get("VELOMIND_B200_TRACEBACK", "") == "1":
+            raise
+        print(f"trace_run: error: {type(ex).__name__}: {ex}   (VELOMIND_B200_TRACEBACK=1 shows where)", file=sys.stderr, flush=True)
         return 1
 
 
