@@ -469,6 +469,26 @@ def test_generation_with_stand_in_kernels_matches_plain(emulated, model_folders)
     assert np.abs(te.forward_full_logits(prompts[0]).numpy() - ref).max() < 5e-6
     te.reset_session()
     assert te.session_length == 0 and te.engine.cache.slots.held_count == 0
+    # the reference's own way of sampling: a host function of one row of logits (llama_engine.h:106-121)
+    seen = []
+
+    def second_best(row):
+        seen.append(row.shape)
+        return int(np.argsort(row)[-2])
+
+    got = te.generate([prompts[1]], max_tokens=3, stop_tokens=(), sample_fn=second_best)[0].tokens
+    want, ctx = [], list(prompts[1])
+    for _ in range(3):
+        want.append(int(np.argsort(P.forward_logits(cfg, w, ctx)[-1])[-2]))
+        ctx.append(want[-1])
+    assert got == want and seen == [(cfg["vocab_size"],)] * 3
+    # forward_step with the reference's position argument: only the session's length is a valid place
+    te.prefill(prompts[0][:3])
+    with pytest.raises(ValueError, match="not the session's length 3"):
+        te.forward_step(prompts[0][3], pos=5)
+    step = te.forward_step(prompts[0][3], pos=3)
+    assert np.abs(step.numpy() - P.forward_logits(cfg, w, prompts[0][:4])[-1]).max() < 5e-6
+    te.reset_session()
 
 
 class FakeRunStepper(FakeStepper):

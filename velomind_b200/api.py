@@ -112,17 +112,24 @@ class TextEngine:
 
     def generate(self, prompts: Sequence[Union[str, Sequence[int]]], temperature: float = 0.7, top_p: float = 0.9,
                  max_tokens: int = 32, seed: int = 42, stop_tokens: Optional[Sequence[int]] = None,
-                 on_token: Optional[Callable[[int, int, str], None]] = None, steps_per_sync: int = 1) -> List[Result]:
+                 on_token: Optional[Callable[[int, int, str], None]] = None, steps_per_sync: int = 1,
+                 sample_fn: Optional[Callable[[Any], int]] = None) -> List[Result]:
         """Generate for a batch of prompts (token id lists, or text if a tokenizer is loaded).
         `on_token(index, token, piece)` is called for every new token; `piece` is its text (or "[id]").
         `steps_per_sync`: decode steps queued on the GPU before the host reads their tokens.  1 (the default): every
         step, each token reaches `on_token` as it is made, and on a host that keeps up this is also the faster way;
-        more: the host is out of the loop for that many steps, at the price of steps computed past a stop token."""
+        more: the host is out of the loop for that many steps, at the price of steps computed past a stop token.
+        `sample_fn(logits) -> token`: the reference's way of sampling (llama_engine.h:106-121): a function of one row of
+        float32 logits (a numpy array on the host) instead of temperature and top-p; every step's logits then come to
+        the host."""
         engine = self._need()
         stops = tuple(stop_tokens) if stop_tokens is not None else self.default_stop_tokens()
         requests = [Request(self.encode(p), SamplingParams(temperature, top_p, max_tokens, seed, stops), stream=i)
                     for i, p in enumerate(prompts)]
-        loop = GenerationLoop(engine, self.sampler, engine.cache.n_pages, self.config.max_batch, stops, steps_per_sync)
+        sampler = self.sampler if sample_fn is None else FunctionSampler(sample_fn)
+        if sample_fn is not None:
+            steps_per_sync = 1                   # (the function runs on the host after every step)
+        loop = GenerationLoop(engine, sampler, engine.cache.n_pages, self.config.max_batch, stops, steps_per_sync)
         streamers = [TextStreamer(self.tokenizer) for _ in requests]
         callback = None
         if on_token is not None:
@@ -167,10 +174,13 @@ class TextEngine:
         self._session_slot = engine.open()
         return engine.step([Entry(self._session_slot, list(tokens), [len(tokens) - 1])])[0].clone()
 
-    def forward_step(self, token: int) -> torch.Tensor:
-        """Feed one more token to the session; logits [vocab] (llama_engine.cpp:395-455)."""
+    def forward_step(self, token: int, pos: Optional[int] = None) -> torch.Tensor:
+        """Feed one more token to the session; logits [vocab] (llama_engine.cpp:395-455).  `pos`, the reference's second
+        argument, is the token's place in the session: it can only be the session's length, and is checked when given."""
         if self._session_slot is None:
             raise RuntimeError("forward_step needs a session: call prefill first")
+        if pos is not None and int(pos) != self.session_length:
+            raise ValueError(f"forward_step: pos {pos} is not the session's length {self.session_length}")
         return self._need().step([Entry(self._session_slot, [int(token)], [0])])[0].clone()
 
     def forward_full_logits(self, tokens: Sequence[int]) -> torch.Tensor:
@@ -190,6 +200,18 @@ class TextEngine:
             return engine.step([Entry(slot, list(tokens), [len(tokens) - 1])])[0].clone()
         finally:
             engine.close(slot)
+
+
+class FunctionSampler:
+    """A host function of one row of logits as the loop's sampler (the reference's `sample_fn`)."""
+
+    def __init__(self, fn: Callable[[Any], int]):
+        self.fn = fn
+
+    def sample(self, logits, params, streams, steps):
+        import numpy as np
+        rows = logits.float().cpu().numpy()
+        return np.array([int(self.fn(rows[r])) for r in range(rows.shape[0])], dtype=np.int32)
 
 
 class TextStreamer:
