@@ -457,6 +457,7 @@ def test_generation_with_stand_in_kernels_matches_plain(emulated, model_folders)
     got = te.generate(prompts, temperature=0.8, top_p=0.95, max_tokens=4, seed=5, stop_tokens=())
     want = [P.generate(cfg, w, p, 4, temperature=0.8, top_p=0.95, seed=5, stream=i) for i, p in enumerate(prompts)]
     assert [r.tokens for r in got] == want
+    assert got[0].text == "".join(f"[{t}]" for t in want[0]) and got[0].elapsed_seconds > 0 and got[0].tokens_per_second > 0
     pieces = []
     te.generate(prompts[:1], temperature=0.0, max_tokens=2, on_token=lambda i, t, piece: pieces.append(piece))
     assert all(p.startswith("[") for p in pieces)         # no tokenizer: ids in brackets

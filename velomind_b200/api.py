@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import os
 import tempfile
+import time
 from dataclasses import dataclass, field
 from typing import Any, Callable, Dict, List, Optional, Sequence, Union
 
@@ -135,9 +136,16 @@ class TextEngine:
         if on_token is not None:
             def callback(i, tok):
                 on_token(i, tok, streamers[i].put(tok))
+        t0 = time.perf_counter()
         results = loop.run(requests, callback)
+        elapsed = time.perf_counter() - t0
         self.last_timing = loop.timing
         engine.raise_if_error()
+        for res in results:                      # the reference's result fields (llama_engine.h:32-38)
+            res.text = (self.tokenizer.decode(res.tokens) if self.tokenizer is not None
+                        else "".join(f"[{t}]" for t in res.tokens))
+            res.elapsed_seconds = elapsed
+            res.tokens_per_second = len(res.tokens) / elapsed if elapsed > 0 else 0.0
         return results
 
     def describe(self) -> Dict[str, Any]:

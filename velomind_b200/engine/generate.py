@@ -35,6 +35,9 @@ class Result:
     tokens: List[int] = field(default_factory=list)
     finish_reason: str = ""              # "stop" (a stop token, kept in `tokens`), "length", "empty"
     prompt_tokens: int = 0
+    text: str = ""                       # the tokens as text (filled where a tokenizer is at hand; "[id]" pieces without one)
+    elapsed_seconds: float = 0.0         # of the whole call that produced it (prompts and decoding of every batch)
+    tokens_per_second: float = 0.0       # this sequence's tokens over that time
 
 
 @dataclass
