@@ -6,9 +6,6 @@ The product never imports this file.  `install(monkeypatch)` swaps them in.
 """
 from __future__ import annotations
 
-import math
-
-import numpy as np
 import torch
 
 import plain_llama as P

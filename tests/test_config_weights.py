@@ -1,5 +1,4 @@
 """Configuration, registry, safetensors and weight binding: what is accepted and how refusals read."""
-import copy
 import json
 import os
 import struct

@@ -1,7 +1,6 @@
 """Each CUDA kernel alone against a plain float32 reference, at sizes other than the engine tests use:
 head sizes in steps of 16, odd head counts and groups, widths and vocabularies that are no power of two."""
 import math
-import types
 
 import numpy as np
 import pytest

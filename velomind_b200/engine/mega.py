@@ -7,9 +7,7 @@ an architecture's name.  Where it does not apply, decode steps run part by part 
 """
 from __future__ import annotations
 
-import ctypes
 import struct
-from typing import Optional
 
 import torch
 
