@@ -489,6 +489,18 @@ class Engine:
         ops.library_calls += graph.launches[1]
         return graph
 
+    def _table_widths(self, slots: Sequence[int]) -> List[int]:
+        """Per cache group, how wide the block tables of a batch of these slots are: the most blocks any of them holds,
+        rounded up to a power of two (few distinct step shapes), at most the table's own width."""
+        widths = []
+        for g in self.cache.groups:
+            need = max(1, max(g.blocks_end[slot] for slot in slots))
+            w = 1
+            while w < need:
+                w *= 2
+            widths.append(min(w, g.max_blocks))
+        return widths
+
     def _describe(self, entries, chunk, reserve_extra: int = 0):
         """Reserve cache room for a chunk of a step and write its descriptors; returns (desc, T, B, R, widths,
         new lengths, wanted (entry, place) pairs).  `reserve_extra` tokens of room are reserved beyond the chunk's
@@ -500,14 +512,7 @@ class Engine:
         for (i, a, b) in chunk:
             e = entries[i]
             cache.reserve(e.slot, cache.length[e.slot] + (b - a) + reserve_extra)
-        # widths of the block tables of this batch, per group (power of two, at most the table's width)
-        widths = []
-        for g in cache.groups:
-            need = max(1, max(g.blocks_end[entries[i].slot] for i, _, _ in chunk))
-            w = 1
-            while w < need:
-                w *= 2
-            widths.append(min(w, g.max_blocks))
+        widths = self._table_widths([entries[i].slot for i, _, _ in chunk])
         wanted_here = []
         for (i, a, b) in chunk:
             for w in sorted(int(x) for x in entries[i].want):
@@ -646,13 +651,7 @@ class Engine:
                 raise CacheError("out of cache pages for this step: the live sequences and the new tokens exceed max_tokens")
             for slot in slot_list:
                 cache.reserve(slot, lengths[slot] + 1)
-        widths = []
-        for g in cache.groups:
-            need = max(1, max(g.blocks_end[slot] for slot in slot_list))
-            w = 1
-            while w < need:
-                w *= 2
-            widths.append(min(w, g.max_blocks))
+        widths = self._table_widths(slot_list)
         desc = self._descriptors(B, B, B, widths)
         desc.wait_reusable()
         desc.next_decode = None
