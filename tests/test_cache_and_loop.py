@@ -492,6 +492,27 @@ def test_generation_with_stand_in_kernels_matches_plain(emulated, model_folders)
     te.reset_session()
 
 
+def test_queued_decode_runs_with_stand_in_kernels_equal_single_steps(emulated, model_folders):
+    """`Engine.decode_many` (several decode steps without the host in between, the tokens fed back by the device-side
+    kernel's stand-in) against one step at a time and against the plain implementation, greedy and sampled, with a stop
+    token that ends one sequence inside a run."""
+    import velomind_b200 as vm
+    folder = model_folders["tiny_a"]
+    cfg, w = P.read_model(folder)
+    prompts = [[3, 1, 4, 1, 5, 9, 2, 6], [2, 7], [1] * 62]          # the last one crosses a page while decoding
+    te = vm.TextEngine(vm.EngineConfig(model_path=folder, dtype="float32", device="cpu", max_tokens=1024)).load()
+    for temperature, top_p in ((0.0, 1.0), (0.9, 0.8)):
+        one = te.generate(prompts, temperature=temperature, top_p=top_p, max_tokens=9, seed=3, stop_tokens=(), steps_per_sync=1)
+        want = [P.generate(cfg, w, p, 9, temperature=temperature, top_p=top_p, seed=3, stream=i) for i, p in enumerate(prompts)]
+        assert [r.tokens for r in one] == want
+        stop = want[1][4]                                             # ends the second sequence in the middle of a run
+        ref = te.generate(prompts, temperature=temperature, top_p=top_p, max_tokens=9, seed=3, stop_tokens=(stop,), steps_per_sync=1)
+        for k in (2, 4, 8):
+            got = te.generate(prompts, temperature=temperature, top_p=top_p, max_tokens=9, seed=3, stop_tokens=(stop,), steps_per_sync=k)
+            assert [(r.tokens, r.finish_reason) for r in got] == [(r.tokens, r.finish_reason) for r in ref]
+    assert te.engine.cache.slots.held_count == 0 and te.engine.cache.tokens_held() == 0
+
+
 class FakeRunStepper(FakeStepper):
     """FakeStepper that can also queue several decode steps (next token = last + 1, like its logits say)."""
     MAX_DECODE_RUN = 5
