@@ -143,7 +143,6 @@ def install(monkeypatch):
             pass
 
     monkeypatch.setattr(step, "GRAPHS_DEFAULT", False)
-    monkeypatch.setattr(step, "CLUSTER_DEFAULT", False)
     monkeypatch.setattr(step, "_host_buffer", lambda n, dtype: torch.empty(n, dtype=dtype))
     monkeypatch.setattr(step, "_new_event", lambda: _Event())
     monkeypatch.setattr(step, "_upload", lambda dev, host, event: dev.copy_(host))

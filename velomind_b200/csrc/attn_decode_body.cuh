@@ -1,5 +1,4 @@
-// Device body of the split-KV decode attention (see attention_decode.cu), shared by the stand-alone kernel and
-// by the persistent decode kernel of decode_mega.cu.
+// Device body of the split-KV decode attention (see attention_decode.cu).
 #pragma once
 #include "mma.cuh"
 

@@ -1,5 +1,4 @@
-// Device bodies of the weight-streaming products (see skinny_gemm.cu for what they compute and why).  They are
-// shared by the stand-alone kernels of skinny_gemm.cu and by the persistent decode kernel of decode_mega.cu.
+// Device bodies of the weight-streaming products (see skinny_gemm.cu for what they compute and why).
 #pragma once
 #include "mma.cuh"
 

@@ -22,8 +22,6 @@ from ..cache.pages import PAGE_TOKENS, CacheError
 from ..cache.store import SequenceCache
 from ..kernels import ops
 from .arena import Workspace
-from .cluster import ClusterPlan
-from .mega import MAX_ROWS as MEGA_MAX_ROWS, MegaPlan
 from .model import DecoderModel
 
 
@@ -48,7 +46,6 @@ def _bucket(n: int, fine_from: int = 512, fine_step: int = 512, floor: int = 8) 
 
 
 GRAPHS_DEFAULT = True     # decode steps are replayed from CUDA graphs unless an Engine is told otherwise
-CLUSTER_DEFAULT = False   # the cluster decode kernel (engine/cluster.py) is asked for per Engine: it is slower than the graph so far
 
 
 def _host_buffer(n: int, dtype: torch.dtype) -> torch.Tensor:
@@ -185,8 +182,7 @@ class Engine:
 
     def __init__(self, model: DecoderModel, max_tokens: int, max_slots: Optional[int] = None,
                  max_step_tokens: int = 8192, use_graphs: Optional[bool] = None,
-                 fused_prefill_rows: Optional[int] = None, persistent_decode: bool = False,
-                 cluster_decode: Optional[bool] = None, poison_freed: bool = False):
+                 fused_prefill_rows: Optional[int] = None, poison_freed: bool = False):
         if model.device is None:
             raise RuntimeError("the model has no weights bound; use load_model()")
         self.model = model
@@ -213,13 +209,6 @@ class Engine:
         self._shape_seen: Dict[Tuple, int] = {}
         self._run_state = None
         self._contexts: Dict[Tuple, StepContext] = {}
-        # one persistent kernel per decode step where the model allows it (engine/mega.py); measured slower than the graph of
-        # dependent launches so far (profiles/decode_persistent_kernel.md), hence off unless asked for
-        self.mega = MegaPlan(model, self.cache) if (persistent_decode and self.dtype == torch.bfloat16) else None
-        # all layers of a decode step in one launch of thread-block clusters, each taking a few sequences through every
-        # layer (engine/cluster.py); measured slower than the graph of dependent launches so far, hence off unless asked for
-        want_cluster = CLUSTER_DEFAULT if cluster_decode is None else bool(cluster_decode)
-        self.cluster = ClusterPlan(model, self.cache) if (want_cluster and self.dtype == torch.bfloat16) else None
         self.steps_run = 0
 
     # ---- slots
@@ -294,14 +283,8 @@ class Engine:
         ctx.logits = logits[:B]
         bucket = (desc.caps[0], desc.caps[1], desc.caps[2], True, self.fused_prefill_rows)
 
-        mega = self.mega is not None and self.mega.ok and B <= MEGA_MAX_ROWS
-        bucket = bucket + ("mega",) if mega else self._bucket_of(ctx, bucket)
-
         def one_step():
-            if mega:
-                self.mega.run(ctx)
-            else:
-                self._forward(ctx)
+            self._forward(ctx)
             ops.sample(ctx.logits, st["dev_f"][0, :B], st["dev_f"][1, :B], st["dev_i"][0, :B], st["dev_i"][1, :B],
                        st["dev_i"][2, :B], st["sampled"][:B])
             ops.decode_advance(st["sampled"][:B], ctx.tokens, ctx.positions, ctx.ctx_len, st["dev_i"][2, :B],
@@ -420,18 +403,8 @@ class Engine:
             self._desc[key] = d
         return d
 
-    def _clustered(self, ctx: StepContext) -> bool:
-        return self.cluster is not None and self.cluster.takes(ctx)
-
-    def _bucket_of(self, ctx: StepContext, bucket):
-        """The workspace bucket of a step: steps that run the cluster kernel take other scratch."""
-        return bucket + ("cluster",) if self._clustered(ctx) else bucket
-
     def _forward(self, ctx: StepContext) -> None:
-        if self._clustered(ctx):
-            self.cluster.run(ctx)
-        else:
-            self.model.forward(ctx)
+        self.model.forward(ctx)
 
     def _run_eager(self, ctx: StepContext, bucket) -> None:
         ops.TC_FUSED_MIN_ROWS = self.fused_prefill_rows
@@ -612,7 +585,7 @@ class Engine:
         desc.h("tokens")[:B] = toks
         desc.upload()
         logits = self._logits_buffer(B)
-        made_for = (logits.data_ptr(), self.ws.generation, self.use_graphs, self.fused_prefill_rows, id(self.mega), id(self.cluster))
+        made_for = (logits.data_ptr(), self.ws.generation, self.use_graphs, self.fused_prefill_rows)
         if graph is not None and graph[1] == made_for:
             # the graph that ran these sequences' last step: same shape, same buffers
             graph[0].replay()
@@ -700,7 +673,7 @@ class Engine:
         part (None)."""
         ctx = self._context(desc, T, B, R, widths)
         ctx.logits = logits[row0: row0 + R]
-        bucket = self._bucket_of(ctx, (desc.caps[0], desc.caps[1], desc.caps[2], ctx.one_token_each, self.fused_prefill_rows))   # decode steps take other scratch
+        bucket = (desc.caps[0], desc.caps[1], desc.caps[2], ctx.one_token_each, self.fused_prefill_rows)   # decode steps take other scratch
         lens = tuple(int(x) for x in np.diff(ctx.host_cu_tokens)) if not ctx.one_token_each else ()
         shape_key = (T, B, R, tuple(widths), ctx.logits.data_ptr(), lens)
         use_graph = self.use_graphs and self.ws.planned(bucket)

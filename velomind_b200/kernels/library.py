@@ -29,7 +29,7 @@ ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC"]
 LIB_NAME = "libvelomind_b200_kernels.so"
 # optional kernels, each a library of its own (group name -> source files); everything else is the "core" library
-OPTIONAL = {"decode_cluster": ["decode_cluster.cu"], "decode_mega": ["decode_mega.cu"]}
+OPTIONAL = {}
 
 
 class KernelLibraryError(RuntimeError):

@@ -16,7 +16,7 @@ import torch
 from . import ops
 
 KERNELS = ["qkv_rope", "out_residual", "gate_up_swiglu", "down_residual", "head", "attn_decode", "attn_prefill", "attn_prefill_tc",
-           "add_rmsnorm", "sample", "tc_linear", "tc_residual", "tc_swiglu", "cublas_linear", "decode_cluster", "prefill_step"]
+           "add_rmsnorm", "sample", "tc_linear", "tc_residual", "tc_swiglu", "cublas_linear", "prefill_step"]
 
 
 def _prefill_step(a) -> int:
@@ -51,80 +51,6 @@ def _prefill_step(a) -> int:
                 times.append(e0.elapsed_time(e1))
                 eng.close(slot)
             out[name + "_ms"] = round(min(times), 4)
-        print(json.dumps(out))
-    return 0
-
-
-def _decode_cluster(a) -> int:
-    """All layers of a decode step in the cluster kernel (csrc/decode_cluster.cu) on a random model of the given
-    sizes: the step's time against the graph of dependent launches, and where the cluster kernel's time goes, from its
-    own trace (every CTA's arrival at and release from each of the five phase barriers of a layer)."""
-    import tempfile
-
-    import numpy as np
-
-    from .. import Engine, Entry, load_model, write_random_model
-    from ..engine import cluster as cl
-    cfg = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": a.layers,
-           "hidden_size": a.hidden, "num_attention_heads": a.heads, "num_key_value_heads": a.kv_heads,
-           "intermediate_size": a.intermediate, "vocab_size": a.vocab, "rope_theta": 100000.0, "rms_norm_eps": 1e-5,
-           "tie_word_embeddings": True, "max_position_embeddings": 8192}
-    if a.clusters:
-        cl.MAX_CLUSTERS = a.clusters
-    B, L = a.batch, a.layers
-    with tempfile.TemporaryDirectory() as d:
-        write_random_model(d, cfg, seed=0)
-        model = load_model(d, torch.bfloat16, "cuda:0")
-        rng = np.random.default_rng(0)
-        out = {"kernel": "decode_cluster", "batch": B, "ctx": a.ctx, "layers": L}
-        for name, kw in (("graph_of_launches", {"cluster_decode": False}), ("cluster_kernel", {"cluster_decode": True})):
-            eng = Engine(model, B * (a.ctx + 256), **kw)
-            slots = [eng.open() for _ in range(B)]
-            eng.step([Entry(s, rng.integers(0, a.vocab, size=a.ctx).tolist(), [a.ctx - 1]) for s in slots])
-            step = lambda: eng.step([Entry(s, [5], [0]) for s in slots])
-            for _ in range(4):
-                step()                                    # the decode step's graph is recorded here
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(a.repeat):
-                step()
-            e1.record()
-            torch.cuda.synchronize()
-            out[name + "_ms_per_step"] = round(e0.elapsed_time(e1) / a.repeat, 4)
-            if name == "cluster_kernel":
-                plan = eng.cluster
-                if not plan.ok:
-                    print(json.dumps({"kernel": "decode_cluster", "not_applicable": plan.why}))
-                    return 0
-                eager = Engine(model, B * (a.ctx + 256), cluster_decode=True, use_graphs=False)
-                slots2 = [eager.open() for _ in range(B)]
-                eager.step([Entry(s, rng.integers(0, a.vocab, size=a.ctx).tolist(), [a.ctx - 1]) for s in slots2])
-                eager.step([Entry(s, [5], [0]) for s in slots2])
-                if eager.cluster.last_shape is None:
-                    print(json.dumps({"kernel": "decode_cluster", "not_applicable": "the kernel does not take this step's shape"}))
-                    return 0
-                rows, parts = eager.cluster.last_shape
-                n_cta = -(-B // rows) * plan.cs
-                tr = torch.zeros((5 * L, n_cta, 2), dtype=torch.int64, device="cuda")
-                eager.cluster.trace = tr
-                eager.step([Entry(s, [5], [0]) for s in slots2])
-                torch.cuda.synchronize()
-                eager.cluster.trace = None
-                t = tr.cpu().numpy()
-                arr, rel = t[:, :, 0], t[:, :, 1]
-                out.update({"rows_per_cluster": rows, "attention_parts": parts, "ctas": n_cta,
-                            "kernel_span_us": round(float(rel.max() - arr[0].min()) / 1e3, 1)})
-                c0 = slice(0, plan.cs)                    # the first cluster
-                for ph, pname in enumerate(("qkv", "attention", "out", "gate_up", "down")):
-                    work, wait = [], []
-                    for l in range(1, L):
-                        i = l * 5 + ph
-                        work.append(np.median(arr[i, c0] - rel[i - 1, c0]))
-                        wait.append(np.median(rel[i, c0]) - arr[i, c0].max())
-                    if work:
-                        out[f"{pname}_work_us"] = round(float(np.mean(work)) / 1e3, 2)
-                        out[f"{pname}_barrier_us"] = round(float(np.mean(wait)) / 1e3, 2)
         print(json.dumps(out))
     return 0
 
@@ -171,16 +97,13 @@ def main(argv=None) -> int:
     ap.add_argument("--k", type=int, default=0, help="tc_*/cublas_linear: inner size (default hidden)")
     ap.add_argument("--splits", type=int, default=0, help="attn_decode: key splits (0: the engine's choice)")
     ap.add_argument("--groups", type=int, default=4, help="attn_prefill: warp groups sharing a tile's key blocks")
-    ap.add_argument("--layers", type=int, default=6, help="decode_cluster, prefill_step: layers of the random model")
-    ap.add_argument("--clusters", type=int, default=0, help="decode_cluster: deal the batch out to at most this many clusters")
+    ap.add_argument("--layers", type=int, default=6, help="prefill_step: layers of the random model")
     ap.add_argument("--temp", type=float, default=0.0, help="sample: temperature (0: greedy)")
     ap.add_argument("--top-p", type=float, default=0.9, help="sample: nucleus mass, with --temp")
     ap.add_argument("--repeat", type=int, default=50)
     ap.add_argument("--no-graph", action="store_true")
     a = ap.parse_args(argv)
     dev = ops.require_cuda("cuda:0")
-    if a.kernel == "decode_cluster":
-        return _decode_cluster(a)
     if a.kernel == "prefill_step":
         return _prefill_step(a)
     M, hid, H, Hkv, D, I, V = a.batch, a.hidden, a.heads, a.kv_heads, a.head_dim, a.intermediate, a.vocab

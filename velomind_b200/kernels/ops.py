@@ -464,67 +464,6 @@ def decode_advance(sampled: torch.Tensor, tokens: torch.Tensor, positions: torch
                                        _ptr(history), _ptr(iteration), _c_int(B), _stream()), "decode_advance")
 
 
-def decode_mega_layer_bytes() -> int:
-    fn = library("decode_mega").vm_decode_mega_layer_bytes
-    fn.restype = ctypes.c_int
-    return int(fn())
-
-
-def decode_mega(layers: torch.Tensor, n_layers: int, B: int, hid: int, H: int, Hkv: int, D: int, I: int, V: int, scale: float,
-                window: int, inv_freq: Optional[torch.Tensor], rot_dim: int, tokens: torch.Tensor, positions: torch.Tensor,
-                seq_of_token: torch.Tensor, block_table: torch.Tensor, n_pages: int, embed: torch.Tensor, h: torch.Tensor,
-                q: torch.Tensor, att: torch.Tensor, act: torch.Tensor, xf: torch.Tensor, logits: torch.Tensor,
-                final_norm: torch.Tensor, final_eps: float, head: torch.Tensor, partial: torch.Tensor, counters: torch.Tensor,
-                n_splits: int, barrier: torch.Tensor, err: Optional[torch.Tensor], trace: Optional[torch.Tensor] = None) -> None:
-    """One whole decode step (embedding, every layer, final norm, head) in one persistent kernel: B <= 16 sequences with
-    one new token each, bfloat16.  `layers` is the device table of per-layer pointers (see csrc/decode_mega.cu);
-    `barrier` (uint32, 1 element) must be zero at launch; `counters` zero (left zero).  `trace` (int64 [phases, 148, 2],
-    optional) receives each CTA's arrival at and departure from every grid barrier in nanoseconds."""
-    _check(library("decode_mega").vm_decode_mega(_ptr(layers), _c_int(n_layers), _c_int(B), _c_int(hid), _c_int(H), _c_int(Hkv), _c_int(D),
-                                    _c_int(I), _c_int(V), _c_f(scale), _c_int(window), _ptr(inv_freq), _c_int(rot_dim),
-                                    _ptr(tokens), _ptr(positions), _ptr(seq_of_token), _ptr(block_table),
-                                    _c_int(block_table.shape[1]), _c_int(n_pages), _ptr(embed), _c_int(dtype_code(embed)),
-                                    _ptr(h), _ptr(q), _ptr(att), _ptr(act), _ptr(xf), _ptr(logits), _ptr(final_norm),
-                                    _c_f(final_eps), _ptr(head), _ptr(partial), _ptr(counters), _c_int(n_splits), _ptr(barrier),
-                                    _ptr(err), _ptr(trace), _c_int(trace.shape[0] if trace is not None else 0), _stream()),
-           "decode_mega")
-
-
-def decode_cluster_layer_bytes() -> int:
-    fn = library("decode_cluster").vm_decode_cluster_layer_bytes
-    fn.restype = ctypes.c_int
-    return int(fn())
-
-
-def decode_cluster_fit(rows: int, cs: int, n_layers: int, hid: int, H: int, Hkv: int, D: int, I: int, max_blocks: int, ks_target: int,
-                       parts: int) -> int:
-    """Ring stages the cluster decode kernel would have for `rows` rows per cluster of `cs` CTAs at these sizes;
-    less than 3 (or -1) means it does not take them."""
-    fn = library("decode_cluster").vm_decode_cluster_fit
-    fn.restype = ctypes.c_int
-    return int(fn(_c_int(rows), _c_int(cs), _c_int(n_layers), _c_int(hid), _c_int(H), _c_int(Hkv), _c_int(D), _c_int(I), _c_int(max_blocks),
-                  _c_int(ks_target), _c_int(parts)))
-
-
-def decode_cluster(layers: torch.Tensor, n_layers: int, B: int, rows_per_cluster: int, cs: int, hid: int, H: int, Hkv: int,
-                   D: int, I: int, V: int, scale: float, window: int, inv_freq: Optional[torch.Tensor], rot_dim: int,
-                   tokens: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor, n_pages: int,
-                   embed: torch.Tensor, h_out: torch.Tensor, rank_stride: int, ks_target: int, parts: int,
-                   err: torch.Tensor, trace: Optional[torch.Tensor] = None) -> None:
-    """Embedding and all layers of one decode step (one new token per sequence) in one launch of thread-block
-    clusters, each taking `rows_per_cluster` sequences through every layer; the residual stream of the rows goes to
-    h_out [B, hid] float32.  `layers` is the device table of per-layer records (packed weight stream, cache pages,
-    norm eps: csrc/decode_cluster.cu); the streams must have been packed for this `cs` and `ks_target`.  `trace` (int64
-    [5 * n_layers, CTAs, 2], optional) receives every CTA's arrival at and release from each phase barrier in ns."""
-    _check(library("decode_cluster").vm_decode_cluster(_ptr(layers), _c_int(n_layers), _c_int(B), _c_int(rows_per_cluster), _c_int(cs),
-                                       _c_int(hid), _c_int(H), _c_int(Hkv), _c_int(D), _c_int(I), _c_int(V), _c_f(scale),
-                                       _c_int(window), _ptr(inv_freq), _c_int(rot_dim), _ptr(tokens), _ptr(positions),
-                                       _ptr(block_table), _c_int(block_table.shape[1]), _c_int(n_pages), _ptr(embed),
-                                       _c_int(dtype_code(embed)), _ptr(h_out), _c_ll(rank_stride), _c_int(ks_target),
-                                       _c_int(parts), _ptr(err), _ptr(trace), _stream()),
-           "decode_cluster")
-
-
 def require_cuda(device) -> torch.device:
     """The device an engine may run on, or a loud refusal."""
     dev = torch.device(device)

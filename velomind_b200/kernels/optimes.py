@@ -20,7 +20,7 @@ from . import ops
 TIMED = ("embed_gather", "add_rmsnorm", "residual_add", "swiglu", "convert", "rope_kv_write", "attention_generic",
          "attention_prefill_bf16", "attention_prefill_tc_bf16", "attention_decode_bf16", "linear", "skinny_linear",
          "skinny_swiglu", "skinny_qkv_rope", "tc_linear", "tc_swiglu", "tc_qkv_rope", "sample", "decode_advance",
-         "decode_mega", "decode_cluster", "upload")
+         "upload")
 
 
 def _cuda_event():

@@ -56,14 +56,6 @@ class GroupedQueryAttention(Part):
     def cache_need(self) -> CacheNeed:
         return CacheNeed("window" if self.window > 0 else "all", self.kv_heads, self.head_dim, self.window)
 
-    def fused_decode_info(self):
-        """What the persistent decode kernel needs to know of this mixer (None: it cannot be part of one)."""
-        if self.qkv is None or self.qkv.weight.dtype != torch.bfloat16 or self.out.weight.dtype != torch.bfloat16:
-            return None
-        return {"kind": "grouped_query_attention", "wqkv": self.qkv.weight, "wo": self.out.weight, "hidden": self.hidden,
-                "heads": self.heads, "kv_heads": self.kv_heads, "head_dim": self.head_dim, "scale": self.scale,
-                "window": self.window, "inv_freq": self.inv_freq, "rotary_dim": self.rotary_dim}
-
     def can_fuse(self, ctx, norm) -> bool:
         """True if this step can run as: [norm +] qkv + rotary + cache write -> attention -> out + residual,
         with the weight-streaming kernels (few tokens) or the tensor-core kernels (many tokens)."""

@@ -22,16 +22,6 @@ class PreNormBlock:
         return {"mixer": self.mixer, "feed_forward": self.feed_forward, "mixer_norm": self.mixer_norm,
                 "feed_forward_norm": self.feed_forward_norm}
 
-    def fused_decode_info(self):
-        """The layer as the persistent decode kernel sees it: pre-norm, mixer, pre-norm, feed-forward (None if a part
-        cannot describe itself for it)."""
-        infos = [getattr(part, "fused_decode_info", lambda: None)() for part in (self.mixer, self.feed_forward)]
-        norms = [getattr(n, "as_rms", None) for n in (self.mixer_norm, self.feed_forward_norm)]
-        if any(i is None for i in infos) or any(n is None for n in norms):
-            return None
-        return {"arrangement": "prenorm", "mixer": infos[0], "feed_forward": infos[1], "mixer_norm": norms[0](),
-                "feed_forward_norm": norms[1]()}
-
     def forward(self, ctx, h, pending):
         hid = h.shape[1]
         # A part that can take the preceding norm into its first kernel and the residual sum into its last one

@@ -31,13 +31,6 @@ class SwiGLU(Part):
         self.gate_up = Linear([weights["gate_proj.weight"], weights["up_proj.weight"]], bc)
         self.down = Linear([weights["down_proj.weight"]], bc)
 
-    def fused_decode_info(self):
-        """What the persistent decode kernel needs to know of this feed-forward (None: it cannot be part of one)."""
-        if self.gate_up is None or self.gate_up.weight.dtype != torch.bfloat16 or self.down.weight.dtype != torch.bfloat16:
-            return None
-        return {"kind": "swiglu", "wgu": self.gate_up.weight, "wd": self.down.weight, "hidden": self.hidden,
-                "intermediate": self.intermediate}
-
     def can_fuse(self, ctx, norm) -> bool:
         if getattr(norm, "as_rms", None) is None or ctx.act_dtype != torch.bfloat16:
             return False
