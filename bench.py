@@ -7,8 +7,15 @@ for context 4096), timed on the device with CUDA events over exactly K decode st
 the step function and the device sampler and hands the tokens to the host.  `e2e` is the same through
 `TextEngine.generate` (host token ids in, host token ids out, wall clock of its decode steps).  `prefill`
 is one prompt of 2,048 tokens; `points` holds decode at batch 1 and 64; `roofline` compares the decode
-step with the bytes it has to read.  The reference publishes no number (`vs_baseline` is null) and cannot
-be installed as a Python package, so `--impl reference` reports itself unavailable.
+step with the bytes it has to read.  The reference publishes no number (`vs_baseline` is null).
+
+`--impl reference` runs the UNMODIFIED reference, built by baseline/build_reference.py into baseline/_ref (its core,
+its CUDA backend and its own benchmark tool; pip cannot install it, it is a CMake project without a Python package):
+`value` and `prefill` come from its own `benchmark_baseline --device cuda --synthetic` (one execute of its decode
+graph at context 512, one execute of its 2,048-token prompt graph: benchmarks/benchmark_runner.cpp:134-158,190-249),
+`e2e` from its public engine API (`prefill` + `forward_step`, host tokens in, host logits out, graph build and
+allocation of every step included, as its own generation loop pays them).  The reference runs one sequence at a time:
+its batch of 8 is eight sequences one after another, so its tokens per second do not grow with the batch.
 """
 from __future__ import annotations
 
@@ -186,6 +193,95 @@ def prefill_run(text_engine, T, vocab, repeats=5):
     return statistics.median(times)
 
 
+def _parse_reference_table(markdown: str):
+    """Rows of the reference tool's report: {S: (prefill ms, prefill tok/s, decode ms, decode tok/s)} of the CUDA backend."""
+    rows = {}
+    for line in markdown.splitlines():
+        cells = [c.strip() for c in line.strip().strip("|").split("|")]
+        if len(cells) < 8 or cells[0] != "CUDA":
+            continue
+        try:
+            S = int(cells[1])
+            prefill_ms = float(cells[4].split("/")[0])
+            prefill_tps = float(cells[5].split()[0])
+            decode_ms = float(cells[6].split("/")[0])
+            decode_tps = float(cells[7].split()[0])
+        except (ValueError, IndexError):
+            continue
+        rows[S] = (prefill_ms, prefill_tps, decode_ms, decode_tps)
+    return rows
+
+
+def reference_arm(args):
+    """The reference's own numbers for the same metric and sizes, or the one-line reason why there are none."""
+    if args.gpus != 1:
+        return {"impl": "reference", "unavailable": "the reference runs on one device only"}
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    tool, driver = os.path.join(ref_dir, "benchmark_baseline"), os.path.join(ref_dir, "reference_driver")
+    if not (os.path.isfile(tool) and os.path.isfile(driver)):
+        try:
+            sys.path.insert(0, os.path.join(ROOT, "baseline"))
+            import build_reference
+            build_reference.build()
+        except Exception as ex:      # no checkout of the reference, or no compiler
+            return {"impl": "reference", "unavailable": f"the reference could not be built here: {str(ex).splitlines()[0][:200]}"}
+    B, prompt_len, T = 8, 512, 2048
+    steps, warmup = max(1, args.steps), max(args.warmup, 3)
+    clock = ClockSampler()
+    with tempfile.TemporaryDirectory(prefix="velomind_ref_") as work:
+        report = os.path.join(work, "report.md")
+        clock.start()
+        # its own tool: median over `steps` executes after `warmup`; S = 512 gives decode at context 512, S = 2048 the prompt
+        r = subprocess.run([tool, "--device", "cuda", "--synthetic", "--seq-lens", f"{prompt_len},{T}", "--iters", str(min(steps, 20)),
+                            "--warmup", str(warmup), "--quiet", "--markdown", report], cwd=work, capture_output=True, text=True, timeout=1500)
+        clocks = clock.stop()
+        if r.returncode != 0 or not os.path.isfile(report):
+            return {"impl": "reference", "unavailable": f"the reference's benchmark tool failed (exit {r.returncode}): {(r.stderr or r.stdout).strip().splitlines()[-1][:200] if (r.stderr or r.stdout).strip() else ''}"}
+        with open(report) as f:
+            rows = _parse_reference_table(f.read())
+        if prompt_len not in rows or T not in rows:
+            return {"impl": "reference", "unavailable": "the reference's report has no CUDA rows (no CUDA device?)"}
+        # end to end through its public engine API: B sequences one after another, host tokens in, host logits out
+        d = subprocess.run([driver, "cuda", str(B), str(prompt_len), str(min(steps, 20)), "3", str(T)], cwd=work, capture_output=True,
+                           text=True, timeout=1500)
+        e2e = None
+        if d.returncode == 0:
+            try:
+                rec = json.loads(d.stdout.strip().splitlines()[-1])
+                n = rec["sequences"] * rec["decode_steps"]
+                e2e = {"value": n * 1000.0 / rec["decode_ms_total"], "unit": "tokens/s", "h2d_bytes_per_step": 4,
+                       "d2h_bytes_per_step": rec["logit_bytes_per_step"], "ms_per_token": rec["decode_ms_median"],
+                       "prefill_2048_ms": rec["prefill_ms_median"]}
+            except (ValueError, KeyError, IndexError):
+                e2e = None
+    _, _, decode_ms, decode_tps = rows[prompt_len]
+    prefill_ms, prefill_tps, _, _ = rows[T]
+    pk = peaks()
+    cfg = {"hidden_size": 576, "intermediate_size": 1536, "vocab_size": 49152, "num_attention_heads": 9, "num_key_value_heads": 3}
+    per_layer, _, _, D = model_bytes_and_flops(cfg, 30)
+    flops = 2.0 * T * per_layer * 30 + 4.0 * D * 9 * (T * (T + 1) / 2.0) * 30 + 2.0 * 49152 * 576
+    line = {
+        "impl": "reference",
+        "metric": "decode tok/s at batch 8 (SmolLM2-135M shape, prompts of 512 tokens)",
+        "value": decode_tps, "unit": "tokens/s", "n_gpus": 1, "steps": min(steps, 20), "warmup": warmup,
+        "ms_per_step": decode_ms * B, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32",
+        "data": "synthetic",
+        "config": {"model": "SmolLM2-135M shape, the reference's own --synthetic weights", "global_batch": B, "seq_len": prompt_len,
+                   "parallelism": "single GPU", "layers": 30, "layers_of_config": 30, "hidden": 576, "heads": 9, "kv_heads": 3,
+                   "head_dim": 64, "intermediate": 1536, "vocab": 49152,
+                   "batching": "none in the reference: 8 sequences one after another, tokens/s equal its batch-1 figure",
+                   "timing": "the reference's own tool: host clock around one execute of its decode graph, median",
+                   "built_from": "unmodified sources, CUDA backend for sm_100, cuBLAS float32"},
+        "prefill": {"value": prefill_tps, "tokens": T, "ms": prefill_ms, "frac": flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)},
+        "points": {"decode_b1": decode_tps, "decode_b64": decode_tps},
+        "clocks": clocks,
+        "gpu_launches": 0,
+    }
+    if e2e is not None:
+        line["e2e"] = e2e
+    return line
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -199,8 +295,7 @@ def main() -> int:
     args = ap.parse_args()
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference is a C++/CMake project without setup.py or pyproject.toml: pip cannot install it offline"}))
+        print(json.dumps(reference_arm(args)))
         return 0
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU library: --gpus {args.gpus} is not supported, run with --gpus 1")

@@ -14,10 +14,28 @@ def _run(*args):
 
 
 def test_reference_arm_says_why_it_is_unavailable():
+    """Without a CUDA device the reference arm (the reference's own benchmark tool, built from its unmodified sources)
+    has no numbers: it says so in one line and exits 0."""
     proc = _run("--impl", "reference", "--gpus", "1", "--steps", "2", "--warmup", "1")
     assert proc.returncode == 0
     line = json.loads(proc.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and isinstance(line["unavailable"], str) and "\n" not in line["unavailable"]
+
+
+def test_reference_report_rows_are_read():
+    """The reference tool's report (benchmarks/benchmark_reporter.cpp) as bench.py reads it: backend, S, graph, allocation,
+    prompt ms, prompt tokens/s, decode ms, decode tokens/s."""
+    sys.path.insert(0, ROOT)
+    import bench
+    report = (
+        "| 后端 | S | 构图(中位/P95) | 分配(中位/P95) | Prefill(中位/P95) | Prefill吞吐 | Decode(中位/P95) | Decode吞吐 | D2H(中位) |\n"
+        "| :--- | :---: | :---: | :---: | :---: | :---: | :---: | :---: | :---: |\n"
+        "| CPU | 512 | 0.3/0.4 ms | 3.3/3.4 ms | 180.3/181.0 ms | 44.4 tok/s | 58.38/58.67 ms | 17.1 tok/s | 0.02 ms |\n"
+        "| CUDA | 512 | 0.3/0.7 ms | 7.6/7.7 ms | 14.3/14.5 ms | 35741.4 tok/s | 5.74/5.80 ms | 174.3 tok/s | 0.03 ms |\n"
+        "| CUDA | 2048 | 0.3/0.7 ms | 20.7/20.9 ms | 104.1/104.2 ms | 19682.6 tok/s | 12.25/12.30 ms | 81.7 tok/s | 0.03 ms |\n")
+    rows = bench._parse_reference_table(report)
+    assert sorted(rows) == [512, 2048]
+    assert rows[512] == (14.3, 35741.4, 5.74, 174.3) and rows[2048][1] == 19682.6
 
 
 def test_more_than_one_gpu_is_refused_with_one_line():

@@ -18,7 +18,6 @@ namespace {
 
 constexpr int DEC_WARPS = 4;
 constexpr int DEC_WARPS_WIDE = 10;
-constexpr int DEC_WIDE_MAX_CTAS = 148;
 using namespace vmad;
 
 template <int D, int WARPS>
@@ -70,7 +69,7 @@ VM_API int vm_attention_decode_bf16(const void* q, int q_row_stride, const void*
     dim3 grid(n_splits, Hkv * ((G + DEC_ROWS - 1) / DEC_ROWS), B);
     const __nv_bfloat16 *qq = (const __nv_bfloat16*)q, *kk = (const __nv_bfloat16*)kpages, *vv = (const __nv_bfloat16*)vpages;
     // one split and a CTA per SM at most: ten warps per CTA, if their pages fit into shared memory
-    const bool wide = n_splits == 1 && (long long)grid.y * grid.z <= DEC_WIDE_MAX_CTAS;
+    const bool wide = n_splits == 1 && (long long)grid.y * grid.z <= vm_sm_count();
 #define VM_DEC_CASE(DD)                                                                                                \
     case DD:                                                                                                           \
         if (wide && attn_decode_smem_bytes<DD, DEC_WARPS_WIDE>() <= 227 * 1024)                                        \
@@ -114,13 +113,17 @@ VM_API int vm_attention_decode_bf16_no_alloc(const void* q, int q_row_stride, co
                                              int n_pages, int* err, cudaStream_t stream) {
     if (B <= 0) return 0;
     if (H <= 0 || D <= 0 || n_splits < 1) return VM_ERR_BAD_ARG;
+    // everything the kernel's own launcher would refuse is refused here, before anything is put on the stream
+    if (Hkv <= 0 || H % Hkv != 0 || n_splits > MAX_SPLITS || (q_row_stride % 8) != 0 || D % 16 != 0 || D > 128)
+        return VM_ERR_UNSUPPORTED;
     if (vm_attention_decode_no_alloc_bytes(B, H, D, n_splits) > VM_NO_ALLOC_SCRATCH_BYTES) return VM_NO_ALLOC_TOO_LARGE;
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
     if (dev < 0 || dev >= NO_ALLOC_MAX_DEVICES) return VM_ERR_UNSUPPORTED;
     if (no_alloc_base[dev] == nullptr) {
-        // once per device, with that device current: the symbol's address ON THIS DEVICE
+        // once per device, with that device current: the symbol's address ON THIS DEVICE.  (No lock: two host threads
+        // that both make a device's first call look the same address up and store the same value.)
         void* p = nullptr;
         e = cudaGetSymbolAddress(&p, vm_no_alloc_scratch);
         if (e != cudaSuccess) return (int)e;

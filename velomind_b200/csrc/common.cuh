@@ -14,6 +14,9 @@ enum : int { VM_ERR_UNSUPPORTED = -1, VM_ERR_BAD_ARG = -2 };
 
 constexpr int VM_PAGE_TOKENS = 64;
 
+// Which two values of a head are rotated together by a rotary position encoding: (j, j + rot_dim/2) or (2j, 2j + 1).
+enum : int { VM_PAIR_HALF_SPLIT = 0, VM_PAIR_INTERLEAVED = 1 };
+
 __device__ __forceinline__ float vm_to_float(float x) { return x; }
 __device__ __forceinline__ float vm_to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
 template <typename T> __device__ __forceinline__ T vm_from_float(float x);
@@ -70,6 +73,18 @@ static inline cudaError_t vm_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim
     cfg.attrs = attr;
     cfg.numAttrs = vm_pdl_enabled ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// Streaming multiprocessors of the current device (asked once per device; 0 if the runtime cannot tell).
+static inline int vm_sm_count() {
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess) cached[dev] = n;
+    }
+    return cached[dev];
 }
 
 static inline int vm_launch_status() {

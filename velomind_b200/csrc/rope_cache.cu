@@ -1,11 +1,13 @@
-// Position encoding (half-split rotary pairs) of queries and keys, fused with the write of the new
-// keys and values into the paged cache.
+// Rotary position encoding of queries and keys, fused with the write of the new keys and values into the
+// paged cache.
 //
 // Reference: src/cpu/ops/rotary_embedding.cpp:30-44 (pairs (j, j + half): y[j] = a*c - b*s,
 // y[j+half] = b*c + a*s) with the angle of examples/common/llama/llama_rope_mask.cpp:17-24
 // (float(pos) * inv_freq[j] in float32, then cos/sin).  inv_freq comes from the host as a float32
-// table, so a position encoding with other frequencies only changes the table.  Keys are cached after
-// rotation (examples/common/llama/llama_graph.cpp:210-215).
+// table, so a position encoding with other frequencies only changes the table; which two values of a head
+// make pair j is an argument too (`pairing`: VM_PAIR_HALF_SPLIT = (j, j + rot_dim/2), what the reference
+// does; VM_PAIR_INTERLEAVED = (2j, 2j + 1)).  Keys are cached after rotation
+// (examples/common/llama/llama_graph.cpp:210-215).
 //
 // qkv is [T, (H + 2*Hkv) * D]: queries, then keys, then values of one token.  Queries are rotated in
 // place; keys and values go to page block_table[seq, pos / 64], row pos % 64 of their kv head.
@@ -15,7 +17,7 @@
 template <typename T>
 __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
                                      const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
-                                     int max_blocks, const float* __restrict__ inv_freq, int rot_dim,
+                                     int max_blocks, const float* __restrict__ inv_freq, int rot_dim, int pairing,
                                      T* __restrict__ kpages, T* __restrict__ vpages, int H, int Hkv, int D,
                                      int n_pages, int* __restrict__ err) {
     const int t = blockIdx.x;
@@ -39,18 +41,20 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
     for (int it = threadIdx.x; it < n_pairs; it += blockDim.x) {
         const int head = it / half, j = it - head * half;
         T* x = row + (size_t)head * D;
-        const float a = vm_to_float(x[j]), b = vm_to_float(x[j + half]);
+        const int ia = pairing == VM_PAIR_INTERLEAVED ? 2 * j : j;
+        const int ib = pairing == VM_PAIR_INTERLEAVED ? 2 * j + 1 : j + half;
+        const float a = vm_to_float(x[ia]), b = vm_to_float(x[ib]);
         float s, c;
         sincosf(fpos * inv_freq[j], &s, &c);
         const float ya = a * c - b * s;
         const float yb = b * c + a * s;
         if (head < H) {
-            x[j] = vm_from_float<T>(ya);
-            x[j + half] = vm_from_float<T>(yb);
+            x[ia] = vm_from_float<T>(ya);
+            x[ib] = vm_from_float<T>(yb);
         } else {
             T* dst = kpages + (size_t)page * page_stride + ((size_t)(head - H) * VM_PAGE_TOKENS + in_page) * D;
-            dst[j] = vm_from_float<T>(ya);
-            dst[j + half] = vm_from_float<T>(yb);
+            dst[ia] = vm_from_float<T>(ya);
+            dst[ib] = vm_from_float<T>(yb);
         }
     }
     if (!write_kv) return;                      // a run that reads another run's cache only rotates its queries
@@ -141,11 +145,12 @@ rope_kv_write_bf16_vec_kernel(__nv_bfloat16* __restrict__ qkv, const int* __rest
 }
 
 VM_API int vm_rope_kv_write(void* qkv, const int* positions, const int* seq_of_token, const int* block_table,
-                            int max_blocks, const float* inv_freq, int rot_dim, void* kpages, void* vpages,
+                            int max_blocks, const float* inv_freq, int rot_dim, int pairing, void* kpages, void* vpages,
                             int T, int H, int Hkv, int D, int n_pages, int act_dtype, int* err, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (rot_dim < 0 || rot_dim > D || (rot_dim & 1) || (rot_dim > 0 && inv_freq == nullptr)) return VM_ERR_BAD_ARG;
-    if (act_dtype == VM_BF16 && rot_dim == D && D % 16 == 0 && (reinterpret_cast<uintptr_t>(qkv) & 15) == 0 &&
+    if (pairing != VM_PAIR_HALF_SPLIT && pairing != VM_PAIR_INTERLEAVED) return VM_ERR_BAD_ARG;
+    if (act_dtype == VM_BF16 && pairing == VM_PAIR_HALF_SPLIT && rot_dim == D && D % 16 == 0 && (reinterpret_cast<uintptr_t>(qkv) & 15) == 0 &&
         ((reinterpret_cast<uintptr_t>(kpages) | reinterpret_cast<uintptr_t>(vpages)) & 15) == 0) {
         // (a thread takes eight pairs of a head: 64 threads cover this model's 9 + 3 heads of 64 in one round)
         const int threads = (H + Hkv) * (D / 16) <= 64 ? 64 : 128;
@@ -158,10 +163,10 @@ VM_API int vm_rope_kv_write(void* qkv, const int* positions, const int* seq_of_t
     const int threads = work >= 512 ? 256 : 128;
     if (act_dtype == VM_F32)
         rope_kv_write_kernel<float><<<T, threads, 0, stream>>>((float*)qkv, positions, seq_of_token, block_table, max_blocks,
-            inv_freq, rot_dim, (float*)kpages, (float*)vpages, H, Hkv, D, n_pages, err);
+            inv_freq, rot_dim, pairing, (float*)kpages, (float*)vpages, H, Hkv, D, n_pages, err);
     else if (act_dtype == VM_BF16)
         rope_kv_write_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>((__nv_bfloat16*)qkv, positions, seq_of_token, block_table, max_blocks,
-            inv_freq, rot_dim, (__nv_bfloat16*)kpages, (__nv_bfloat16*)vpages, H, Hkv, D, n_pages, err);
+            inv_freq, rot_dim, pairing, (__nv_bfloat16*)kpages, (__nv_bfloat16*)vpages, H, Hkv, D, n_pages, err);
     else
         return VM_ERR_UNSUPPORTED;
     return vm_launch_status();

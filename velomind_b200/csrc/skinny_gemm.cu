@@ -153,12 +153,15 @@ VM_API int vm_skinny_swiglu(const void* A, int pro, const float* norm_w, float e
 }
 
 // q_out[M, H*D] = rope(x Wq^T); rope(x Wk^T) and x Wv^T go to the cache pages; W = [Wq; Wk; Wv] is [(H+2Hkv)*D, K].
-// rot_dim must be 0 (no rotation) or D.  kpages == nullptr: nothing is cached.
+// rot_dim must be 0 (no rotation) or D, the pairing half-split (another pairing is refused with VM_ERR_UNSUPPORTED: the
+// caller then takes the unfused product followed by vm_rope_kv_write, which rotates either pairing).  kpages == nullptr:
+// nothing is cached.
 VM_API int vm_skinny_qkv_rope(const void* A, int pro, const float* norm_w, float eps, const void* W, int M, int K,
                               void* q_out, const int* positions, const int* seq_of_token, const int* block_table,
-                              int max_blocks, const float* inv_freq, int rot_dim, void* kpages, void* vpages, int H, int Hkv,
+                              int max_blocks, const float* inv_freq, int rot_dim, int pairing, void* kpages, void* vpages, int H, int Hkv,
                               int D, int n_pages, int* err, cudaStream_t stream) {
     if (D % 16 != 0 || !(rot_dim == 0 || rot_dim == D) || (rot_dim > 0 && inv_freq == nullptr)) return VM_ERR_UNSUPPORTED;
+    if (rot_dim > 0 && pairing != VM_PAIR_HALF_SPLIT) return VM_ERR_UNSUPPORTED;
     SkinnyParams p{};
     p.A = A; p.pro = pro; p.norm_w = norm_w; p.eps = eps; p.W = (const __nv_bfloat16*)W; p.M = M; p.N = (H + 2 * Hkv) * D; p.K = K;
     p.out = q_out; p.out_stride = H * D; p.epi = EPI_ROPE_KV; p.tiles = 2;

@@ -471,12 +471,13 @@ VM_API int vm_tc_swiglu(const void* A, long long lda, const void* W, int M, int 
 }
 
 // One head per tile: q_out[M, H*D] = rope(A Wq^T); rope(A Wk^T) and A Wv^T go to the cache pages.  D is 64 or 128,
-// rot_dim 0 or D.
+// rot_dim 0 or D; half-split pairing only (another pairing is refused: the caller takes the unfused path).
 VM_API int vm_tc_qkv_rope(const void* A, long long lda, const void* W, int M, int K, void* q_out, const int* positions,
                           const int* seq_of_token, const int* block_table, int max_blocks, const float* inv_freq,
-                          int rot_dim, void* kpages, void* vpages, int H, int Hkv, int D, int n_pages, int* err,
+                          int rot_dim, int pairing, void* kpages, void* vpages, int H, int Hkv, int D, int n_pages, int* err,
                           cudaStream_t stream) {
     if (M <= 0) return 0;
+    if (rot_dim > 0 && pairing != VM_PAIR_HALF_SPLIT) return VM_ERR_UNSUPPORTED;
     if (K % 8 != 0 || !(D == 64 || D == 128) || !(rot_dim == 0 || rot_dim == D) || (rot_dim > 0 && inv_freq == nullptr))
         return VM_ERR_UNSUPPORTED;
     TcParams p{};

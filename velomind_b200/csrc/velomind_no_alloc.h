@@ -20,14 +20,16 @@
 //     kernels are loaded holds these 8 MiB until the process exits, whether or not this function is called.
 //   * A call whose scratch would not fit, i.e. 256-byte-rounded 4 * B * H bytes of counters plus
 //     4 * B * H * n_splits * (D + 2) bytes of partials > VM_NO_ALLOC_SCRATCH_BYTES, is refused with
-//     VM_NO_ALLOC_TOO_LARGE and nothing is launched.  vm_attention_decode_no_alloc_bytes() tells the need.
+//     VM_NO_ALLOC_TOO_LARGE before anything is put on the stream (no memset, no kernel), and so is every size the
+//     kernel does not take (-1).  vm_attention_decode_no_alloc_bytes() tells the need.
 //   * All calls on a device share the one array, and it keeps whatever the last call left.  The function
 //     clears the counters on the caller's stream before every launch; the partials need no clearing (every
 //     value that is read is written first).  Two calls that overlap on the GPU (different streams without an
 //     ordering between them, or different host threads) race on the scratch and give wrong results: order
 //     them.
 //   * The first call on each device looks up the array's device address with cudaGetSymbolAddress (with that
-//     device current) and remembers it.  Make that first call outside of any stream capture.
+//     device current) and remembers it.  Make that first call outside of any stream capture.  The lookup takes no
+//     lock: host threads that race on a device's first call store the same address, which is harmless.
 //
 // Return value: 0 on success; VM_NO_ALLOC_TOO_LARGE (-3); -1 / -2 for unsupported sizes or bad arguments as
 // in the ordinary entry point; a positive cudaError_t if CUDA reports one.

@@ -16,6 +16,7 @@ import torch
 from .library import KernelLibraryError, library
 
 F32, BF16 = 0, 1
+PAIR_HALF_SPLIT, PAIR_INTERLEAVED = 0, 1      # which two values of a head a rotary encoding turns together (csrc/common.cuh)
 _CODES = {torch.float32: F32, torch.bfloat16: BF16}
 
 _c_int, _c_ll, _c_f, _c_p = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p
@@ -129,14 +130,16 @@ def convert(src: torch.Tensor, out: torch.Tensor) -> None:
 
 def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
                   inv_freq: Optional[torch.Tensor], rot_dim: int, k_pages: Optional[torch.Tensor],
-                  v_pages: Optional[torch.Tensor], H: int, Hkv: int, D: int, err: Optional[torch.Tensor] = None) -> None:
+                  v_pages: Optional[torch.Tensor], H: int, Hkv: int, D: int, err: Optional[torch.Tensor] = None,
+                  pairing: int = 0) -> None:
     """Rotate queries (in place) and keys of qkv [T, (H+2Hkv)*D]; write keys and values into the pages
     k_pages/v_pages [n_pages, Hkv, 64, D] at block_table[seq, pos // 64] (int32 [B, max_blocks]).
-    With k_pages None only the queries are rotated (a run that reads another run's cache)."""
+    With k_pages None only the queries are rotated (a run that reads another run's cache).
+    pairing: PAIR_HALF_SPLIT (j, j + rot_dim/2) or PAIR_INTERLEAVED (2j, 2j + 1)."""
     T = qkv.shape[0]
     n_pages = k_pages.shape[0] if k_pages is not None else 0
     _check(library().vm_rope_kv_write(_ptr(_contig(qkv, "qkv")), _ptr(positions), _ptr(seq_of_token), _ptr(block_table),
-                                      _c_int(block_table.shape[1]), _ptr(inv_freq), _c_int(rot_dim), _ptr(k_pages),
+                                      _c_int(block_table.shape[1]), _ptr(inv_freq), _c_int(rot_dim), _c_int(pairing), _ptr(k_pages),
                                       _ptr(v_pages), _c_int(T), _c_int(H), _c_int(Hkv), _c_int(D),
                                       _c_int(n_pages), _c_int(dtype_code(qkv)), _ptr(err), _stream()), "rope_kv_write")
 
@@ -203,17 +206,17 @@ def decode_counters(device) -> torch.Tensor:
     return _decode_counters[key]
 
 
-B200_SMS = 148                 # streaming multiprocessors of the GPU this library is written for
 DECODE_ONE_CTA_BLOCKS = 16     # block tables up to this wide (1,024 tokens): at most two rounds of pages for ten warps
 
 
-def decode_splits(B: int, Hkv: int, G: int, table_width: int) -> int:
+def decode_splits(B: int, Hkv: int, G: int, table_width: int, device=None) -> int:
     """How many CTAs share the keys of one (sequence, kv head): enough to fill the GPU, a function of the
     step's SHAPE only (so that a captured launch stays valid as sequences grow)."""
     groups = B * Hkv * (-(-G // 16))          # a CTA serves up to 16 query heads of one kv head
-    if groups <= B200_SMS and table_width <= DECODE_ONE_CTA_BLOCKS:
+    sms = sm_count(device)
+    if groups <= sms and table_width <= DECODE_ONE_CTA_BLOCKS:
         return 1                              # short sequences: one CTA of ten warps holds all pages, nothing is merged across CTAs
-    want = -(-B200_SMS // groups)             # about one CTA per SM ...
+    want = -(-sms // groups)                  # about one CTA per SM ...
     table_width = max(1, table_width // 4)    # ... and at least a page per warp of a CTA (the width bounds the pages)
     return max(1, min(want, MAX_DECODE_SPLITS, table_width))
 
@@ -241,7 +244,7 @@ def attention(ctx, q: torch.Tensor, q_row_stride: int, k_pages: torch.Tensor, v_
     prefill kernel; float32, or a head size those refuse -> the generic kernel."""
     fast = out.dtype == torch.bfloat16 and D % 16 == 0 and D <= 128 and q_row_stride % 8 == 0
     if fast and ctx.one_token_each and ctx.B * H <= DECODE_COUNTERS:
-        n_splits = decode_splits(ctx.B, Hkv, H // Hkv, block_table.shape[1])
+        n_splits = decode_splits(ctx.B, Hkv, H // Hkv, block_table.shape[1], out.device)
         partial = ctx.take((ctx.B_cap * H * MAX_DECODE_SPLITS * (D + 2),), torch.float32)   # sized by shape, not by lengths
         attention_decode_bf16(q, q_row_stride, k_pages, v_pages, block_table, ctx.positions, out, partial,
                               decode_counters(out.device), H, Hkv, D, n_splits, scale, window, ctx.err)
@@ -270,12 +273,18 @@ def attention(ctx, q: torch.Tensor, q_row_stride: int, k_pages: torch.Tensor, v_
 _sm_counts = {}
 
 
+def sm_count(device=None) -> int:
+    """Streaming multiprocessors of `device` (the current one if None), asked once."""
+    key = str(device) if device is not None else "current"
+    if key not in _sm_counts:
+        dev = device if device is not None else torch.cuda.current_device()
+        _sm_counts[key] = torch.cuda.get_device_properties(dev).multi_processor_count
+    return _sm_counts[key]
+
+
 def _tc_attention_slots(device) -> int:
     """CTAs of the tcgen05 attention kernel the GPU holds at once."""
-    key = str(device)
-    if key not in _sm_counts:
-        _sm_counts[key] = torch.cuda.get_device_properties(device).multi_processor_count
-    return _sm_counts[key] * TC_ATTENTION_CTAS_PER_SM
+    return sm_count(device) * TC_ATTENTION_CTAS_PER_SM
 
 
 def err_ok(ctx) -> bool:
@@ -341,16 +350,17 @@ def skinny_swiglu(x: torch.Tensor, norm, weight: torch.Tensor, out: torch.Tensor
 def skinny_qkv_rope(x: torch.Tensor, norm, weight: torch.Tensor, q_out: torch.Tensor, positions: torch.Tensor,
                     seq_of_token: torch.Tensor, block_table: torch.Tensor, inv_freq: Optional[torch.Tensor], rot_dim: int,
                     k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], H: int, Hkv: int, D: int,
-                    err: Optional[torch.Tensor] = None) -> None:
+                    err: Optional[torch.Tensor] = None, pairing: int = 0) -> None:
     """q_out[M, H*D] = rotated queries; rotated keys and values go straight into the cache pages.
-    weight = [Wq; Wk; Wv] stacked; x' as in skinny_linear; rot_dim 0 or D."""
+    weight = [Wq; Wk; Wv] stacked; x' as in skinny_linear; rot_dim 0 or D; half-split pairing only."""
     M, K = x.shape
     pro, nw, eps = _norm_args(norm)
     n_pages = k_pages.shape[0] if k_pages is not None else 0
     _check(library().vm_skinny_qkv_rope(_ptr(_contig(x, "x")), _c_int(pro), _ptr(nw), _c_f(eps), _ptr(weight), _c_int(M), _c_int(K),
                                         _ptr(_contig(q_out, "q_out")), _ptr(positions), _ptr(seq_of_token), _ptr(block_table),
-                                        _c_int(block_table.shape[1]), _ptr(inv_freq), _c_int(rot_dim), _ptr(k_pages), _ptr(v_pages),
-                                        _c_int(H), _c_int(Hkv), _c_int(D), _c_int(n_pages), _ptr(err), _stream()), "skinny_qkv_rope")
+                                        _c_int(block_table.shape[1]), _ptr(inv_freq), _c_int(rot_dim), _c_int(pairing), _ptr(k_pages),
+                                        _ptr(v_pages), _c_int(H), _c_int(Hkv), _c_int(D), _c_int(n_pages), _ptr(err), _stream()),
+           "skinny_qkv_rope")
 
 
 # Many rows (prefill): the tcgen05 kernels with fused epilogues exist and are tested, but at this model family's
@@ -392,14 +402,15 @@ def tc_swiglu(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, err: Opt
 
 def tc_qkv_rope(x: torch.Tensor, weight: torch.Tensor, q_out: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
                 block_table: torch.Tensor, inv_freq: Optional[torch.Tensor], rot_dim: int, k_pages: Optional[torch.Tensor],
-                v_pages: Optional[torch.Tensor], H: int, Hkv: int, D: int, err: Optional[torch.Tensor] = None) -> None:
+                v_pages: Optional[torch.Tensor], H: int, Hkv: int, D: int, err: Optional[torch.Tensor] = None,
+                pairing: int = 0) -> None:
     """Like skinny_qkv_rope for many rows: one head per tile, rotation and cache write in the epilogue. D 64 or 128."""
     M, K = x.shape
     n_pages = k_pages.shape[0] if k_pages is not None else 0
     _check(library().vm_tc_qkv_rope(_ptr(x), _c_ll(x.stride(0)), _ptr(weight), _c_int(M), _c_int(K), _ptr(_contig(q_out, "q_out")),
                                     _ptr(positions), _ptr(seq_of_token), _ptr(block_table), _c_int(block_table.shape[1]),
-                                    _ptr(inv_freq), _c_int(rot_dim), _ptr(k_pages), _ptr(v_pages), _c_int(H), _c_int(Hkv),
-                                    _c_int(D), _c_int(n_pages), _ptr(err), _stream()), "tc_qkv_rope")
+                                    _ptr(inv_freq), _c_int(rot_dim), _c_int(pairing), _ptr(k_pages), _ptr(v_pages), _c_int(H),
+                                    _c_int(Hkv), _c_int(D), _c_int(n_pages), _ptr(err), _stream()), "tc_qkv_rope")
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor, seed: torch.Tensor,
