@@ -12,14 +12,6 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200)")
 
 
-@pytest.fixture
-def emulated(monkeypatch):
-    """The package with its kernels replaced by the CPU stand-ins of tests/emulated_ops.py."""
-    import emulated_ops
-    emulated_ops.install(monkeypatch)
-    return emulated_ops
-
-
 @pytest.fixture(scope="session")
 def model_folders(tmp_path_factory):
     """Tiny random models A and B, written once per test session into a temporary folder."""

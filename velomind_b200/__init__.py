@@ -1,16 +1,22 @@
 """velomind_b200: a small generation library for one GPU (NVIDIA B200, sm_100a), built from parts.
 
+The library is C++ and CUDA (`include/velomind_b200/velomind.h`); this package is its thin Python binding.
+
     import velomind_b200 as vm
     engine = vm.load("path/to/model_folder", dtype="bfloat16")
     results = engine.generate([[1, 2, 3], [4, 5]], temperature=0.0, max_tokens=16)
 """
-from . import models  # noqa: F401
-from .api import SMOLLM2_135M, EngineConfig, TextEngine, TextStreamer, load
-from .engine.generate import GenerationLoop, Request, Result
-from .engine.model import DecoderModel, load_model
-from .engine.step import Engine, Entry
-from .sampling.sampler import DeviceSampler, SamplingParams
-from .weights.synthetic import write_random_model
+from .binding import (CacheError, ConfigError, Engine, EngineConfig, Entry, GenerationLoop, KernelError, KernelLibraryError, Model, OpTimes,
+                      Request, Result, SamplingParams, TextEngine, Timing, Tokenizer, WeightError, check_model_folder, describe_config, load,
+                      load_model, pretokenize, registered_architectures, smollm2_135m_config, weight_table, write_random_model)
 
-__all__ = ["SMOLLM2_135M", "EngineConfig", "TextEngine", "TextStreamer", "load", "GenerationLoop", "Request", "Result",
-           "DecoderModel", "load_model", "Engine", "Entry", "DeviceSampler", "SamplingParams", "write_random_model"]
+__all__ = ["CacheError", "ConfigError", "Engine", "EngineConfig", "Entry", "GenerationLoop", "KernelError", "KernelLibraryError", "Model",
+           "OpTimes", "Request", "Result", "SamplingParams", "TextEngine", "Timing", "Tokenizer", "WeightError", "check_model_folder",
+           "describe_config", "load", "load_model", "pretokenize", "registered_architectures", "smollm2_135m_config", "weight_table",
+           "write_random_model", "SMOLLM2_135M"]
+
+
+def __getattr__(name):
+    if name == "SMOLLM2_135M":          # examples/smollm2/model.h:11-22: the sizes the reference's `--synthetic` switch uses
+        return smollm2_135m_config()
+    raise AttributeError(name)

@@ -4,18 +4,11 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+// The launchers' declarations, dtype and status codes, the page size and the rotary pairings: one header shared
+// with the host library, so that a launcher's definition here is checked against what its callers see.
+#include "../include/velomind_b200/kernels.h"
+
 #define VM_API extern "C" __attribute__((visibility("default")))
-
-// dtype codes shared with kernels/ops.py
-enum : int { VM_F32 = 0, VM_BF16 = 1 };
-
-// Status codes returned by launchers: 0 ok, >0 a cudaError_t, <0 one of these.
-enum : int { VM_ERR_UNSUPPORTED = -1, VM_ERR_BAD_ARG = -2 };
-
-constexpr int VM_PAGE_TOKENS = 64;
-
-// Which two values of a head are rotated together by a rotary position encoding: (j, j + rot_dim/2) or (2j, 2j + 1).
-enum : int { VM_PAIR_HALF_SPLIT = 0, VM_PAIR_INTERLEAVED = 1 };
 
 __device__ __forceinline__ float vm_to_float(float x) { return x; }
 __device__ __forceinline__ float vm_to_float(__nv_bfloat16 x) { return __bfloat162float(x); }

@@ -1,14 +1,12 @@
-"""Builds and loads the CUDA kernel libraries (`csrc/*.cu` -> shared objects) and nothing else.
+"""Builds and loads the library: the CUDA kernels (`csrc/*.cu`) and the C++ host (`config/`, `weights/`, `parts/`,
+`cache/`, `engine/`, `models/`, `text/`, `capi/`, `apps/`) in ONE shared object, plus the two programs.
 
-The kernels are plain CUDA with `extern "C"` launchers; they are compiled with
-nvcc for sm_100a and loaded through ctypes, so the build needs neither the
-torch headers nor a writable HOME.  The first call compiles what is missing or
-out of date (a few files in parallel, a progress line now and then on stderr);
-later calls find the library by the hash of its sources and flags.  The kernels every engine needs are one
-library ("core"); each optional decode kernel is a library of its own, compiled when an engine first asks for it.
+The kernels are plain CUDA with `extern "C"` launchers, compiled with nvcc for sm_100a; the host is C++17, compiled
+with g++.  Neither needs the torch headers nor a writable HOME.  The first call compiles what is missing or out of
+date (files in parallel, a progress line now and then on stderr); later calls find the library by the hash of its
+sources and flags.  `CMakeLists.txt` at the repository root builds the same targets from the same file lists.
 
-There is no fallback: if the library cannot be built or loaded, every kernel
-call raises `KernelLibraryError`.
+There is no fallback: if the library cannot be built or loaded, every call raises `KernelLibraryError`.
 """
 from __future__ import annotations
 
@@ -24,10 +22,15 @@ import time
 from concurrent.futures import ThreadPoolExecutor
 from typing import List, Optional
 
-CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc")
+PACKAGE = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+CSRC = os.path.join(PACKAGE, "csrc")
+INCLUDE = os.path.join(PACKAGE, "include")
+HOST_DIRS = ["config", "weights", "cache", "parts", "engine", "models", "text", "capi", "apps"]
+PROGRAMS = {"smollm2_chat": "apps/smollm2_chat_main.cpp", "trace_run": "apps/trace_run_main.cpp"}
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC"]
-LIB_NAME = "libvelomind_b200_kernels.so"
+CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall"]
+LIB_NAME = "libvelomind_b200.so"
 # optional kernels, each a library of its own (group name -> source files); everything else is the "core" library
 OPTIONAL = {}
 
@@ -57,8 +60,29 @@ def lib_name(group: str = "core") -> str:
     return LIB_NAME if group == "core" else f"libvelomind_b200_{group}.so"
 
 
+def host_sources() -> List[str]:
+    """The C++ files of the library itself (the programs' `*_main.cpp` are linked against it, not into it)."""
+    out = []
+    for d in HOST_DIRS:
+        folder = os.path.join(PACKAGE, d)
+        if os.path.isdir(folder):
+            out += [os.path.join(folder, f) for f in os.listdir(folder) if f.endswith(".cpp") and not f.endswith("_main.cpp")]
+    return sorted(out)
+
+
 def _headers() -> List[str]:
-    return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h")))
+    found = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
+    for base, _, files in os.walk(INCLUDE):
+        found += [os.path.join(base, f) for f in files if f.endswith(".h")]
+    for d in HOST_DIRS:
+        folder = os.path.join(PACKAGE, d)
+        if os.path.isdir(folder):
+            found += [os.path.join(folder, f) for f in os.listdir(folder) if f.endswith(".h") or f.endswith("_main.cpp")]
+    return sorted(found)
+
+
+def _cuda_home() -> str:
+    return os.path.dirname(os.path.dirname(_nvcc()))
 
 
 def _nvcc() -> str:
@@ -71,11 +95,11 @@ def _nvcc() -> str:
 
 def _digest(group: str = "core") -> str:
     h = hashlib.sha256()
-    for p in sources(group) + _headers():
-        h.update(os.path.basename(p).encode())
+    for p in sources(group) + (host_sources() if group == "core" else []) + _headers():
+        h.update(os.path.relpath(p, PACKAGE).encode())
         with open(p, "rb") as f:
             h.update(f.read())
-    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
+    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS + CXX_FLAGS).encode())
     return h.hexdigest()[:16]
 
 
@@ -110,7 +134,12 @@ def _say(msg: str) -> None:
 
 
 def _compile_one(nvcc: str, src: str, obj: str, verbose_ptxas: bool) -> None:
-    cmd = [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, "-I", CSRC, "-c", src, "-o", obj]
+    if src.endswith(".cpp"):
+        cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
+        cmd = [cxx, *CXX_FLAGS, "-I", INCLUDE, "-I", os.path.join(_cuda_home(), "include"), "-c", src, "-o", obj]
+        verbose_ptxas = False
+    else:
+        cmd = [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, "-I", CSRC, "-c", src, "-o", obj]
     if verbose_ptxas:
         cmd[1:1] = ["-Xptxas", "-v"]
     r = subprocess.run(cmd, capture_output=True, text=True)
@@ -133,8 +162,8 @@ def build(force: bool = False, verbose_ptxas: bool = False, group: str = "core")
             if f.read().strip() == digest:
                 return target
     nvcc = _nvcc()
-    srcs = sources(group)
-    _say(f"compiling {len(srcs)} CUDA file{'s' if len(srcs) > 1 else ''} ({group}) for sm_100a into {bdir} (first call only)")
+    srcs = sources(group) + (host_sources() if group == "core" else [])
+    _say(f"compiling {len(sources(group))} CUDA files for sm_100a and {len(srcs) - len(sources(group))} C++ files into {bdir} (first call only)")
     t0 = time.time()
     done = threading.Event()
 
@@ -145,18 +174,29 @@ def build(force: bool = False, verbose_ptxas: bool = False, group: str = "core")
     hb = threading.Thread(target=heartbeat, daemon=True)
     hb.start()
     try:
-        objs = [os.path.join(bdir, os.path.basename(s)[:-3] + f".{digest}.o") for s in srcs]
+        objs = [os.path.join(bdir, os.path.relpath(s, PACKAGE).replace(os.sep, "_") + f".{digest}.o") for s in srcs]
         with ThreadPoolExecutor(max_workers=min(len(srcs), os.cpu_count() or 4)) as pool:
             futs = [pool.submit(_compile_one, nvcc, s, o, verbose_ptxas) for s, o in zip(srcs, objs)]
             for s, fu in zip(srcs, futs):
                 fu.result()
                 _say(f"compiled {os.path.basename(s)} ({time.time() - t0:.0f} s)")
         tmp_target = target + f".{os.getpid()}.tmp"
-        r = subprocess.run([nvcc, *ARCH_FLAGS, "-shared", "-o", tmp_target, *objs, "-lcudart"],
-                           capture_output=True, text=True)
+        lib64 = os.path.join(_cuda_home(), "lib64")
+        r = subprocess.run([nvcc, *ARCH_FLAGS, "-shared", "-o", tmp_target, *objs, "-L", lib64, "-lcublas", "-lpthread",
+                            "-Xlinker", f"-rpath={lib64}"], capture_output=True, text=True)
         if r.returncode != 0:
             raise KernelLibraryError(f"linking {name} failed:\n{r.stdout}\n{r.stderr}")
         os.replace(tmp_target, target)
+        if group == "core":
+            cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
+            for prog, main in PROGRAMS.items():
+                tmp_prog = os.path.join(bdir, f"{prog}.{os.getpid()}.tmp")
+                r = subprocess.run([cxx, *CXX_FLAGS, "-I", INCLUDE, "-I", os.path.join(_cuda_home(), "include"), os.path.join(PACKAGE, main),
+                                    "-o", tmp_prog, "-L", bdir, "-l:" + name, "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{lib64}"],
+                                   capture_output=True, text=True)
+                if r.returncode != 0:
+                    raise KernelLibraryError(f"linking {prog} failed:\n{r.stdout}\n{r.stderr}")
+                os.replace(tmp_prog, os.path.join(bdir, prog))
         with open(stamp, "w") as f:
             f.write(digest)
         for o in objs:
@@ -168,6 +208,14 @@ def build(force: bool = False, verbose_ptxas: bool = False, group: str = "core")
         done.set()
     _say(f"kernel library {name} ready ({time.time() - t0:.0f} s)")
     return target
+
+
+def program(name: str) -> str:
+    """The path of a built program (`smollm2_chat`, `trace_run`); builds the library first if need be."""
+    if name not in PROGRAMS:
+        raise KernelLibraryError(f"no program named {name!r}")
+    build()
+    return os.path.join(build_dir(), name)
 
 
 def library(group: str = "core") -> ctypes.CDLL:
