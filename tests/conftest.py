@@ -23,3 +23,10 @@ def model_folders(tmp_path_factory):
         "tiny_b": write_random_model(str(root / "tiny_b"), TINY_B, **TINY_B_INIT),
         "tiny_c": write_random_model(str(root / "tiny_c"), TINY_C, **TINY_C_INIT),
     }
+
+
+@pytest.fixture(scope="session")
+def toy_plugin(tmp_path_factory):
+    """tests/cpp/toy_parts.cu built into a plug-in library and loaded: its parts and architectures are registered."""
+    import toy_plugin as plugin
+    return plugin.load(str(tmp_path_factory.mktemp("toy_plugin")))

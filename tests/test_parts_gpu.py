@@ -1,201 +1,206 @@
-"""Each part of a layer ALONE against the plain function of the same name: the parts of a one-layer model (sizes
-that no other test uses) are called one by one, outside `DecoderModel.forward`, on inputs made here, in a real step
-context (descriptors, cache, workspace) of an engine.
+"""Each part of a layer ALONE against the plain function of the same name.
 
-norm, position (its frequency table), mixer (attention with its cache: a prompt step, then one token each),
-feed-forward, arrangement (the block), embedding, head.
+A part is built, bound and stepped by the engine like any other, inside a probe model (tests/cpp/toy_parts.cu,
+"ProbeForCausalLM") whose every other part passes the residual stream through unchanged: an identity norm, an identity
+head (logits = what reaches the head) and arrangements that run only the mixer or only the feed-forward.  The token
+embedding supplies the inputs (a random table: any row is as good an input as any other), at sizes no other test uses.
+
+norm, position (through the mixer that applies it: half-split, interleaved, partial, other frequencies), mixer
+(attention with its cache: a prompt step of unequal lengths, then one token each; a window), feed-forward, arrangement
+(the block), embedding, head.
 """
 import numpy as np
 import pytest
-import torch
 
 import plain_llama as P
+import schedules as S
 
 pytestmark = pytest.mark.gpu
-DEV = "cuda:0"
 
-PARTS_CFG = {
-    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "vocab_size": 90, "hidden_size": 80,
-    "intermediate_size": 112, "num_hidden_layers": 1, "num_attention_heads": 5, "num_key_value_heads": 1,
-    "rms_norm_eps": 3e-6, "rope_theta": 5000.0, "max_position_embeddings": 512, "tie_word_embeddings": False,
-    "hidden_act": "silu",
-}
-TOL = {torch.float32: 3e-5, torch.bfloat16: 2e-2}       # times the largest reference value (at least 1)
+HID, VOCAB, HEADS, KV, D, INTER, EPS, THETA = 80, 90, 5, 1, 16, 112, 3e-6, 5000.0
+TOL = {"float32": 3e-5, "bfloat16": 2e-2}       # times the largest reference value (at least 1)
+
+IDENTITY_NORM = {"kind": "identity", "args": {"size": HID}}
+RMSNORM = {"kind": "rmsnorm", "args": {"size": HID, "eps": EPS}}
+IDENTITY_HEAD = {"kind": "identity", "args": {"size": HID}}
+SWIGLU = {"kind": "swiglu", "args": {"hidden": HID, "intermediate": INTER}}
 
 
-@pytest.fixture(scope="module")
-def folder(tmp_path_factory):
+def _attention(position=None, window=0):
+    position = position or {"kind": "rotary_half_split", "args": {"head_dim": D, "theta": THETA}}
+    return {"kind": "grouped_query_attention", "args": {"hidden": HID, "heads": HEADS, "kv_heads": KV, "head_dim": D, "position": position,
+                                                        "window": window}}
+
+
+def _probe(vocab=HID, final_norm=IDENTITY_NORM, head=IDENTITY_HEAD, blocks=()):
+    return {"architectures": ["ProbeForCausalLM"], "hidden": HID, "vocab": vocab, "limit": 512,
+            "embedding": {"kind": "token_table", "args": {"vocab": vocab, "hidden": HID}}, "final_norm": final_norm, "head": head,
+            "blocks": list(blocks)}
+
+
+def _block(arrangement, mixer=None, feed_forward=SWIGLU, mixer_norm=IDENTITY_NORM, feed_forward_norm=IDENTITY_NORM):
+    return {"arrangement": arrangement, "mixer": mixer or _attention(), "feed_forward": feed_forward, "mixer_norm": mixer_norm,
+            "feed_forward_norm": feed_forward_norm}
+
+
+@pytest.fixture
+def build(tmp_path, toy_plugin):
     import velomind_b200 as vm
-    d = str(tmp_path_factory.mktemp("parts_model"))
-    vm.write_random_model(d, PARTS_CFG, seed=5, std=0.08, norm_jitter=0.3)
-    return d
 
-
-def _engine(folder, dtype):
-    import velomind_b200 as vm
-    model = vm.load_model(folder, dtype, DEV)
-    return vm.Engine(model, 64 * 4, max_slots=2, use_graphs=False), model
-
-
-class _Step:
-    """A step context for `entries` with the workspace open: what a part's `forward` is given."""
-
-    def __init__(self, engine, entries):
-        self.engine, self.entries = engine, entries
-        chunk = [(i, 0, len(e.tokens)) for i, e in enumerate(entries)]
-        desc, T, B, R, widths, self.new_len, _ = engine._describe(entries, chunk)
-        self.ctx = engine._context(desc, T, B, R, widths)
-        self.ctx.run = 0
-
-    def __enter__(self):
-        self.engine.ws.begin(("parts test", self.ctx.T))
-        return self.ctx
-
-    def __exit__(self, *exc):
-        self.engine.ws.end()
-        torch.cuda.synchronize()
-        self.engine.raise_if_error()
-        for e, n in zip(self.entries, self.new_len):
-            self.engine.cache.commit(e.slot, n)
+    def make(config, dtype, seed=5, std=0.5):
+        folder = vm.write_random_model(str(tmp_path / f"probe{len(list(tmp_path.iterdir()))}"), config, seed=seed, std=std, norm_jitter=0.3)
+        _, w = P.read_model(folder)
+        model = vm.load_model(folder, dtype, "cuda:0")
+        return vm.Engine(model, 64 * 6, max_slots=3), w
+    return make
 
 
 def _close(got, want, dtype):
     want = np.asarray(want, dtype=np.float32)
-    got = got.float().cpu().numpy()
     assert got.shape == want.shape
-    assert np.abs(got - want).max() <= TOL[dtype] * max(1.0, float(np.abs(want).max()))
+    assert np.isfinite(got).all()
+    err = float(np.abs(got - want).max())
+    assert err <= TOL[dtype] * max(1.0, float(np.abs(want).max())), err
 
 
-def _act(x, dtype):
-    """A float32 array as the activation dtype sees it (and back), so that both sides start from the same numbers."""
-    t = torch.from_numpy(np.asarray(x, dtype=np.float32)).to(dtype)
-    return t.to(DEV), t.float().numpy()
+def _run(engine, steps):
+    return S.run_steps_in_process(engine, steps)
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_norm_embedding_head_feed_forward_alone(folder, dtype):
-    import velomind_b200 as vm
-    cfg, w = P.read_model(folder)
-    engine, model = _engine(folder, dtype)
+def _whole(tokens_by_id):
+    return [{"step": 0, "entries": [{"id": k, "tokens": v, "want": list(range(len(v)))} for k, v in tokens_by_id.items()], "end": list(tokens_by_id)}]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embedding_norm_and_head_alone(build, dtype):
     rng = np.random.default_rng(1)
-    hid, V = cfg["hidden_size"], cfg["vocab_size"]
-    s = engine.open()
-    tokens = [int(t) for t in rng.integers(0, V, 7)]
-    with _Step(engine, [vm.Entry(s, tokens, [0, 6])]) as ctx:
-        layer = model.layers[0]
-        # ---- norm: h += delta; out = rmsnorm(h) * w
-        h0 = rng.standard_normal((7, hid)).astype(np.float32) * 2
-        delta_d, delta = _act(rng.standard_normal((7, hid)), dtype)
-        h = torch.from_numpy(h0).to(DEV)
-        out = torch.empty(7, hid, dtype=dtype, device=DEV)
-        layer.block.mixer_norm.forward(ctx, h, delta_d, out)
-        _close(h, h0 + delta, torch.float32)
-        _close(out, P.rmsnorm(h0 + delta, w["model.layers.0.input_layernorm.weight"], cfg["rms_norm_eps"]), dtype)
-        rows = torch.tensor([6, 2], dtype=torch.int32, device=DEV)                     # only some rows, nothing added
-        out2 = torch.empty(2, hid, dtype=dtype, device=DEV)
-        model.final_norm.forward(ctx, h, None, out2, rows)
-        _close(out2, P.rmsnorm((h0 + delta)[[6, 2]], w["model.norm.weight"], cfg["rms_norm_eps"]), dtype)
-        # ---- embedding
-        e = torch.empty(7, hid, dtype=torch.float32, device=DEV)
-        model.embedding.forward(ctx, ctx.tokens, e)
-        _close(e, P.embedding(w["model.embed_tokens.weight"], tokens), torch.float32)
-        # ---- head (its own matrix: the embeddings are not tied here)
-        x_d, x = _act(rng.standard_normal((2, hid)), dtype)
-        logits = torch.empty(2, V, dtype=torch.float32, device=DEV)
-        model.head.forward(ctx, x_d, logits)
-        _close(logits, P.linear(x, w["lm_head.weight"]), dtype)
-        # ---- feed-forward
-        x_d, x = _act(rng.standard_normal((7, hid)), dtype)
-        y = torch.empty(7, hid, dtype=dtype, device=DEV)
-        layer.feed_forward.forward(ctx, x_d, y)
-        p = "model.layers.0.mlp."
-        _close(y, P.linear(P.swiglu(P.linear(x, w[p + "gate_proj.weight"]), P.linear(x, w[p + "up_proj.weight"])),
-                           w[p + "down_proj.weight"]), dtype)
-    engine.close(s)
+    tokens = [int(t) for t in rng.integers(0, HID, 7)]
+    # ---- embedding: identity norm and head, no layer: the logits ARE the rows of the table
+    engine, w = build(_probe(), dtype)
+    got = _run(engine, _whole({"a": tokens}))[0]
+    assert np.array_equal(got, P.embedding(w["embed.weight"], tokens))
+    # ---- norm: all rows, and only some (the gather path of the last norm)
+    engine, w = build(_probe(final_norm=RMSNORM), dtype)
+    got = _run(engine, [{"step": 0, "entries": [{"id": "a", "tokens": tokens, "want": [6, 2]}, {"id": "b", "tokens": tokens[:3], "want": [0, 1, 2]}],
+                         "end": ["a", "b"]}])[0]
+    x = P.embedding(w["embed.weight"], tokens)
+    _close(got, P.rmsnorm(np.concatenate([x[[6, 2]], x[:3]]), w["norm.weight"], EPS), dtype)
+    # ---- head (a matrix of its own, a vocabulary that is no multiple of 8)
+    tokens = [int(t) for t in rng.integers(0, VOCAB, 7)]
+    engine, w = build(_probe(vocab=VOCAB, head={"kind": "linear", "args": {"vocab": VOCAB, "hidden": HID}}), dtype)
+    got = _run(engine, _whole({"a": tokens}))[0]
+    _close(got, P.linear(P.embedding(w["embed.weight"], tokens), w["head.weight"]), dtype)
 
 
-def test_position_alone(folder):
-    """The position part owns the frequencies: the table it hands to the mixer against the plain cosines and sines."""
-    from velomind_b200.parts import PartSpec, build_part
-    from velomind_b200.parts.base import BindContext
-    D, theta = 48, 777.0
-    part = build_part("position", PartSpec("rotary_half_split", {"head_dim": D, "theta": theta}))
-    inv_freq, rot = part.tables(BindContext(torch.float32, torch.device(DEV)))
-    assert rot == D and tuple(inv_freq.shape) == (D // 2,)
-    positions = np.array([0, 1, 63, 64, 500], dtype=np.int32)
-    cos, sin = P.rope_tables(positions, D, theta)
-    angle = positions[:, None].astype(np.float32) * inv_freq.cpu().numpy()[None, :]
-    assert cos.shape == angle.shape
-    assert np.abs(np.cos(angle) - cos).max() < 1e-6 and np.abs(np.sin(angle) - sin).max() < 1e-6
-    none = build_part("position", PartSpec("none", {}))
-    assert none.tables(BindContext(torch.float32, torch.device(DEV))) == (None, 0)
-
-
-def _plain_mixer(cfg, w, x, positions):
-    H, Hkv, D = P.sizes(cfg)
-    p = "model.layers.0.self_attn."
-    S = x.shape[0]
-    q = P.linear(x, w[p + "q_proj.weight"]).reshape(S, H, D)
-    k = P.linear(x, w[p + "k_proj.weight"]).reshape(S, Hkv, D)
-    v = P.linear(x, w[p + "v_proj.weight"]).reshape(S, Hkv, D)
-    cos, sin = P.rope_tables(positions, D, cfg["rope_theta"])
-    att = P.attention(P.rope(q, cos, sin), P.rope(k, cos, sin), v, 1.0 / np.sqrt(np.float32(D)), positions)
-    return P.linear(att.reshape(S, H * D), w[p + "o_proj.weight"])
-
-
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_mixer_alone_with_its_cache(folder, dtype):
-    """The attention part: two prompts of unequal length in one step, then one token each from the cache the first
-    step left; its inputs are made here (not the model's activations)."""
-    import velomind_b200 as vm
-    cfg, w = P.read_model(folder)
-    engine, model = _engine(folder, dtype)
-    mixer = model.layers[0].mixer
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_feed_forward_alone(build, dtype):
     rng = np.random.default_rng(2)
-    hid = cfg["hidden_size"]
-    lens = (70, 5)
-    xs = [rng.standard_normal((n + 1, hid)).astype(np.float32) for n in lens]            # a prompt and one more row
-    slots = [engine.open(), engine.open()]
-    x_d, x = _act(np.concatenate([xs[0][:70], xs[1][:5]]), dtype)
-    with _Step(engine, [vm.Entry(slots[0], [1] * 70, []), vm.Entry(slots[1], [1] * 5, [])]) as ctx:
-        out = torch.empty(75, hid, dtype=dtype, device=DEV)
-        mixer.forward(ctx, x_d, out)
-    want = np.concatenate([_plain_mixer(cfg, w, x[:70], np.arange(70)), _plain_mixer(cfg, w, x[70:], np.arange(5))])
-    _close(out, want, dtype)
-    # one more token each: the keys and values of the prompts come from the cache
-    y_d, y = _act(np.stack([xs[0][70], xs[1][5]]), dtype)
-    with _Step(engine, [vm.Entry(slots[0], [1], [0]), vm.Entry(slots[1], [1], [0])]) as ctx:
-        out = torch.empty(2, hid, dtype=dtype, device=DEV)
-        mixer.forward(ctx, y_d, out)
-    want = np.stack([_plain_mixer(cfg, w, np.concatenate([x[:70], y[:1]]), np.arange(71))[-1],
-                     _plain_mixer(cfg, w, np.concatenate([x[70:], y[1:]]), np.arange(6))[-1]])
-    _close(out, want, dtype)
-    for s in slots:
-        engine.close(s)
+    tokens = [int(t) for t in rng.integers(0, HID, 9)]
+    engine, w = build(_probe(blocks=[_block("feed_forward_only")]), dtype)
+    got = _run(engine, _whole({"a": tokens}))[0]
+    x = P.embedding(w["embed.weight"], tokens)
+    p = "layers.0.feed_forward."
+    y = P.linear(P.swiglu(P.linear(x, w[p + "gate_proj.weight"]), P.linear(x, w[p + "up_proj.weight"])), w[p + "down_proj.weight"])
+    _close(got - x, y, dtype)
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("lens", [(9, 3), (1, 1)])
-def test_arrangement_alone(folder, dtype, lens):
-    """The block (norms, mixer, feed-forward and the residual sums as it wires them) on a residual stream made here:
-    a step of several tokens per sequence, and a step of one token each (the fused decode kernels in bfloat16)."""
-    import velomind_b200 as vm
-    from velomind_b200.kernels import ops
-    cfg, w = P.read_model(folder)
-    engine, model = _engine(folder, dtype)
-    block = model.layers[0].block
+def _rope_interleaved(x, cos, sin):
+    """pairs (2j, 2j + 1) instead of the reference's (j, j + D/2); x [S, heads, R]."""
+    a, b = x[..., 0::2], x[..., 1::2]
+    out = np.empty_like(x)
+    out[..., 0::2] = a * cos[:, None, :] - b * sin[:, None, :]
+    out[..., 1::2] = b * cos[:, None, :] + a * sin[:, None, :]
+    return out
+
+
+def _tables(positions, inv_freq):
+    angle = positions.astype(np.float32)[:, None] * inv_freq[None, :].astype(np.float32)
+    return np.cos(angle).astype(np.float32), np.sin(angle).astype(np.float32)
+
+
+def _plain_mixer(w, x, positions, kind="half", rotary_dim=D, window=0, inv_freq=None):
+    p = "layers.0.mixer."
+    n = x.shape[0]
+    q = P.linear(x, w[p + "q_proj.weight"]).reshape(n, HEADS, D)
+    k = P.linear(x, w[p + "k_proj.weight"]).reshape(n, KV, D)
+    v = P.linear(x, w[p + "v_proj.weight"]).reshape(n, KV, D)
+    if kind != "none":
+        if inv_freq is None:
+            cos, sin = P.rope_tables(positions, rotary_dim, THETA)
+        else:
+            cos, sin = _tables(positions, inv_freq)
+        turn = _rope_interleaved if kind == "interleaved" else P.rope
+        q = np.concatenate([turn(q[..., :rotary_dim], cos, sin), q[..., rotary_dim:]], axis=-1)
+        k = np.concatenate([turn(k[..., :rotary_dim], cos, sin), k[..., rotary_dim:]], axis=-1)
+    att = P.attention(q, k, v, 1.0 / np.sqrt(np.float32(D)), positions, window=window)
+    return P.linear(att.reshape(n, HEADS * D), w[p + "o_proj.weight"])
+
+
+POSITIONS = {
+    "half": ({"kind": "rotary_half_split", "args": {"head_dim": D, "theta": THETA}}, dict(kind="half")),
+    "interleaved": ({"kind": "rotary_interleaved", "args": {"head_dim": D, "theta": THETA}}, dict(kind="interleaved")),
+    "partial": ({"kind": "rotary_half_split", "args": {"head_dim": D, "theta": THETA, "rotary_dim": 8}}, dict(kind="half", rotary_dim=8)),
+    "none": ({"kind": "none", "args": {}}, dict(kind="none")),
+    "evenly_spaced": ({"kind": "toy_evenly_spaced_rotary", "args": {"head_dim": D, "top": 0.5, "interleaved": 0}},
+                      dict(kind="half", inv_freq=np.arange(1, D // 2 + 1, dtype=np.float32) * np.float32(0.5 / (D // 2)))),
+    "evenly_spaced_interleaved": ({"kind": "toy_evenly_spaced_rotary", "args": {"head_dim": D, "top": 0.5, "interleaved": 1}},
+                                  dict(kind="interleaved", inv_freq=np.arange(1, D // 2 + 1, dtype=np.float32) * np.float32(0.5 / (D // 2)))),
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("position", sorted(POSITIONS))
+def test_mixer_alone_with_its_cache_and_every_position_encoding(build, dtype, position):
+    """The attention part: two prompts of unequal length in one step, then one token each from the cache the first step left.
+    The position part owns constants only; the mixer's kernels apply whatever table and pairing it hands over."""
+    spec, plain_args = POSITIONS[position]
     rng = np.random.default_rng(3)
-    hid = cfg["hidden_size"]
-    slots = [engine.open(), engine.open()]
-    h0 = rng.standard_normal((sum(lens), hid)).astype(np.float32)
-    h = torch.from_numpy(h0).to(DEV)
-    with _Step(engine, [vm.Entry(s, [1] * n, []) for s, n in zip(slots, lens)]) as ctx:
-        pending = block.forward(ctx, h, None)
-        if pending is not None:                                    # a delta the next norm would have added
-            ops.residual_add(h, pending)
-            ctx.ws.give(pending)
-    a, b = lens
-    want = np.concatenate([P.layer_forward(cfg, w, 0, h0[:a], np.arange(a)), P.layer_forward(cfg, w, 0, h0[a:], np.arange(b))])
-    _close(h, want, dtype)
-    for s in slots:
-        engine.close(s)
+    a = [int(t) for t in rng.integers(0, HID, 71)]
+    b = [int(t) for t in rng.integers(0, HID, 6)]
+    engine, w = build(_probe(blocks=[_block("mixer_only", mixer=_attention(spec))]), dtype)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:70], "want": list(range(70))}, {"id": "b", "tokens": b[:5], "want": list(range(5))}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": a[70:], "want": [0]}, {"id": "b", "tokens": b[5:], "want": [0]}], "end": ["a", "b"]}]
+    got = _run(engine, steps)
+    xa, xb = P.embedding(w["embed.weight"], a), P.embedding(w["embed.weight"], b)
+    ya, yb = _plain_mixer(w, xa, np.arange(71), **plain_args), _plain_mixer(w, xb, np.arange(6), **plain_args)
+    _close(got[0] - np.concatenate([xa[:70], xb[:5]]), np.concatenate([ya[:70], yb[:5]]), dtype)
+    _close(got[1] - np.stack([xa[70], xb[5]]), np.stack([ya[70], yb[5]]), dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixer_alone_with_a_window(build, dtype):
+    """A window of 70 keys: a query at position 150 must not see key 80, and the group gives pages back as the sequence grows."""
+    rng = np.random.default_rng(4)
+    a = [int(t) for t in rng.integers(0, HID, 160)]
+    engine, w = build(_probe(blocks=[_block("mixer_only", mixer=_attention(window=70))]), dtype)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:150], "want": [0, 69, 70, 149]}], "end": []}]
+    steps += [{"step": 1 + j, "entries": [{"id": "a", "tokens": [a[150 + j]], "want": [0]}], "end": ["a"] if j == 9 else []} for j in range(10)]
+    got = _run(engine, steps)
+    x = P.embedding(w["embed.weight"], a)
+    y = _plain_mixer(w, x, np.arange(160), window=70)
+    _close(got[0] - x[[0, 69, 70, 149]], y[[0, 69, 70, 149]], dtype)
+    for j in range(10):
+        _close(got[1 + j] - x[150 + j][None], y[150 + j][None], dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("lens", [(9, 3), (1, 1), (40, 1)])
+def test_arrangement_alone(build, dtype, lens):
+    """The block (norms, mixer, feed-forward and the residual sums as it wires them): a step of several tokens per
+    sequence, and a step of one token each (the fused decode kernels in bfloat16)."""
+    rng = np.random.default_rng(5)
+    seqs = {f"r{i}": [int(t) for t in rng.integers(0, HID, n)] for i, n in enumerate(lens)}
+    engine, w = build(_probe(blocks=[_block("prenorm", mixer_norm=RMSNORM, feed_forward_norm=RMSNORM)]), dtype, std=0.15)
+    got = _run(engine, _whole(seqs))[0]
+    cfg = {"hidden_size": HID, "num_attention_heads": HEADS, "num_key_value_heads": KV, "rms_norm_eps": EPS, "rope_theta": THETA,
+           "intermediate_size": INTER}
+    names = {"input_layernorm.": "mixer_norm.", "post_attention_layernorm.": "feed_forward_norm.", "self_attn.": "mixer.", "mlp.": "feed_forward."}
+    as_llama = {}
+    for k, v in w.items():
+        if k.startswith("layers.0."):
+            rest = k[len("layers.0."):]
+            for new, old in names.items():
+                if rest.startswith(old):
+                    as_llama["model.layers.0." + new + rest[len(old):]] = v
+    want = np.concatenate([P.layer_forward(cfg, as_llama, 0, P.embedding(w["embed.weight"], t), np.arange(len(t))) for t in seqs.values()])
+    _close(got, want, dtype)

@@ -1,11 +1,10 @@
 """The order in which layers run is data: a schedule that runs a layer twice (each run with a cache of its own) and
-lets a run read another run's cache, registered from this test as an architecture of its own, stepped under every
-cut and compared with a plain whole-sequence computation that is written here from the plain parts."""
-import dataclasses
+lets a run read another run's cache, registered by the tests' plug-in (tests/cpp/toy_parts.cu) as an architecture of its
+own, stepped under every cut and compared with a plain whole-sequence computation that is written here from the plain
+parts."""
 
 import numpy as np
 import pytest
-import torch
 
 import plain_llama as P
 import schedules as S
@@ -45,33 +44,20 @@ def _plain_looped(cfg, w, tokens):
     return P.linear(hn, P.head_weight(cfg, w))
 
 
-@pytest.fixture
-def looped():
-    from velomind_b200.config import LlamaConfig, register_architecture, unregister_architecture
-    from velomind_b200.models.llama import llama_plan
-    from velomind_b200.parts import ScheduleEntry
-
-    def plan(cfg):
-        return dataclasses.replace(llama_plan(cfg), schedule=tuple(ScheduleEntry(l, cache_of=r) for l, r in SCHEDULE))
-
-    register_architecture("LoopedLlamaForCausalLM", LlamaConfig.from_dict, plan)
-    yield
-    unregister_architecture("LoopedLlamaForCausalLM")
-
-
 @pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", 2e-2)])
 @pytest.mark.parametrize("base,init", [(TINY_B, TINY_B_INIT), (TINY_C, TINY_C_INIT)])
-def test_a_layer_runs_twice_and_a_run_reads_anothers_cache(looped, tmp_path, dtype, tol, base, init):
+def test_a_layer_runs_twice_and_a_run_reads_anothers_cache(toy_plugin, tmp_path, dtype, tol, base, init):
     import velomind_b200 as vm
-    cfg_json = dict(base, architectures=["LoopedLlamaForCausalLM"], num_hidden_layers=2)
+    cfg_json = dict(base, architectures=["LoopedLlamaForCausalLM"], num_hidden_layers=2,
+                    schedule=[[layer, -1 if reads is None else reads] for layer, reads in SCHEDULE])
     folder = vm.write_random_model(str(tmp_path / "looped"), cfg_json, **init)
     cfg, w = P.read_model(folder)
     requests = S.make_requests(cfg_json["vocab_size"], (70, 5, 130, 64, 1, 33), seed=17)
     plain = {rid: _plain_looped(cfg, w, toks) for rid, toks in requests.items()}
-    model = vm.load_model(folder, {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype], "cuda:0")
-    assert [n is not None for n in model.cache_needs()] == [True, True, True, False]
+    model = vm.load_model(folder, dtype, "cuda:0")
+    assert model.info["runs"] == 4
     engine = vm.Engine(model, 64 * 8, max_slots=3)
-    assert engine.cache.groups[0].n_layers == 3                     # three runs own keys and values, the fourth borrows
+    assert engine.cache.groups[0]["layers"] == 3                    # three runs own keys and values, the fourth borrows
     scale = max(1.0, max(float(np.abs(v).max()) for v in plain.values()))
     for cut in (S.steps_whole, S.steps_tail_one_by_one, S.steps_unequal_batches):
         steps = cut(requests)
@@ -109,39 +95,19 @@ def _plain_windowed(cfg, w, tokens):
     return P.linear(hn, P.head_weight(cfg, w))
 
 
-@pytest.fixture
-def windowed():
-    from velomind_b200.config import LlamaConfig, register_architecture, unregister_architecture
-    from velomind_b200.models.llama import llama_plan
-    from velomind_b200.parts import PartSpec
-
-    def plan(cfg):
-        base = llama_plan(cfg)
-        blocks = []
-        for l, b in enumerate(base.blocks):
-            if l % 2:
-                b = dataclasses.replace(b, mixer=PartSpec(b.mixer.kind, dict(b.mixer.args, window=WINDOW)))
-            blocks.append(b)
-        return dataclasses.replace(base, blocks=tuple(blocks))
-
-    register_architecture("WindowedLlamaForCausalLM", LlamaConfig.from_dict, plan)
-    yield
-    unregister_architecture("WindowedLlamaForCausalLM")
-
-
 @pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", 2e-2)])
-def test_layers_with_a_window_keep_their_own_pages(windowed, tmp_path, dtype, tol):
+def test_layers_with_a_window_keep_their_own_pages(toy_plugin, tmp_path, dtype, tol):
     """Layers that see all keys and layers that see a window of 70 in one model: two cache groups with storage of
     their own; the windowed group gives pages back while a sequence grows; every cut agrees with the plain model."""
     import velomind_b200 as vm
-    cfg_json = dict(TINY_C, architectures=["WindowedLlamaForCausalLM"], num_hidden_layers=4)
+    cfg_json = dict(TINY_C, architectures=["WindowedLlamaForCausalLM"], num_hidden_layers=4, window=WINDOW)
     folder = vm.write_random_model(str(tmp_path / "windowed"), cfg_json, **TINY_C_INIT)
     cfg, w = P.read_model(folder)
     requests = S.make_requests(cfg_json["vocab_size"], (300, 5, 139, 71, 70, 200), seed=19)
     plain = {rid: _plain_windowed(cfg, w, toks) for rid, toks in requests.items()}
-    model = vm.load_model(folder, {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype], "cuda:0")
+    model = vm.load_model(folder, dtype, "cuda:0")
     engine = vm.Engine(model, 64 * 12, max_slots=3)
-    kinds = sorted((g.need.kind, g.n_layers) for g in engine.cache.groups)
+    kinds = sorted((g["kind"], g["layers"]) for g in engine.cache.groups)
     assert kinds == [("all", 2), ("window", 2)]
     scale = max(1.0, max(float(np.abs(v).max()) for v in plain.values()))
     for cut in (S.steps_whole, S.steps_tail_one_by_one, S.steps_unequal_batches):
@@ -153,7 +119,7 @@ def test_layers_with_a_window_keep_their_own_pages(windowed, tmp_path, dtype, to
     # while a long sequence is held, the windowed group holds fewer pages than the group that keeps every key
     slot = engine.open()
     engine.step([vm.Entry(slot, requests["r0"], [299])])
-    held = {g.need.kind: g.pages.held_count for g in engine.cache.groups}
+    held = {g["kind"]: g["pages_held"] for g in engine.cache.groups}
     assert held["all"] == 5 and held["window"] < held["all"]
     engine.close(slot)
     engine.raise_if_error()
