@@ -6,7 +6,7 @@
 // (tests/test_smollm2_e2e.cpp:180-200): parse_config_json, load_safetensors,
 // bind_smollm2_weights, build_forward_graph_prefill, Graph::build(CPU),
 // populate_smollm2_weights, execute.  Output: [S, vocab] little-endian float32.
-// Built by make_golden.sh against the reference's source tree; no reference source is copied here.
+// Built by make_golden.py against the reference's source tree; no reference source is copied here.
 #include <cstdint>
 #include <cstdio>
 #include <fstream>

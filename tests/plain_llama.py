@@ -40,6 +40,8 @@ def read_safetensors(path):
             a = np.frombuffer(raw, dtype="<f2").astype(np.float32)
         elif d["dtype"] == "I32":
             a = np.frombuffer(raw, dtype="<i4")
+        elif d["dtype"] == "I64":
+            a = np.frombuffer(raw, dtype="<i8").astype(np.int32)
         else:
             raise ValueError(f"{name}: dtype {d['dtype']}")
         out[name] = a.reshape(d["shape"]).copy()

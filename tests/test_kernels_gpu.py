@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 import torch
 
-import emulated_ops as E
+import kernel_refs as E
 import plain_llama as P
 
 pytestmark = pytest.mark.gpu
@@ -103,8 +103,10 @@ def _paged(K, V, lens, n_pages, seed):
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-6), (torch.bfloat16, 1.5e-2)])
+@pytest.mark.parametrize("pairing", [0, 1])
 @pytest.mark.parametrize("H,Hkv,D,rot", [(5, 5, 48, 48), (6, 2, 16, 16), (7, 1, 80, 32), (4, 4, 128, 0)])
-def test_rope_kv_write(dtype, tol, H, Hkv, D, rot):
+def test_rope_kv_write(dtype, tol, H, Hkv, D, rot, pairing):
+    """pairing 0: half-split pairs (j, j + rot/2), the reference's; pairing 1: interleaved pairs (2j, 2j + 1)."""
     lens_before, new = [3, 70, 0], [5, 1, 66]
     B = 3
     T = sum(new)
@@ -117,11 +119,11 @@ def test_rope_kv_write(dtype, tol, H, Hkv, D, rot):
     kp = torch.zeros(n_pages, Hkv, 64, D, dtype=dtype)
     vp = torch.zeros_like(kp)
     want_qkv, want_k, want_v = qkv.clone(), kp.clone(), vp.clone()
-    E.rope_kv_write(want_qkv, positions, seq, table, inv_freq, rot, want_k, want_v, H, Hkv, D)
+    E.rope_kv_write(want_qkv, positions, seq, table, inv_freq, rot, want_k, want_v, H, Hkv, D, pairing=pairing)
     d_qkv, d_k, d_v = qkv.to(DEV), kp.to(DEV), vp.to(DEV)
     err = torch.zeros(1, dtype=torch.int32, device=DEV)
     ops().rope_kv_write(d_qkv, positions.to(DEV), seq.to(DEV), table.to(DEV), None if inv_freq is None else inv_freq.to(DEV),
-                        rot, d_k, d_v, H, Hkv, D, err)
+                        rot, d_k, d_v, H, Hkv, D, err, pairing)
     assert int(err.item()) == 0
     q_cols = H * D
     assert (d_qkv.float().cpu()[:, :q_cols] - want_qkv.float()[:, :q_cols]).abs().max() <= tol * 4
@@ -132,7 +134,7 @@ def test_rope_kv_write(dtype, tol, H, Hkv, D, rot):
     d_k2 = torch.zeros_like(d_k)
     d_qkv2 = qkv.to(DEV)
     ops().rope_kv_write(d_qkv2, positions.to(DEV), seq.to(DEV), table.to(DEV), None if inv_freq is None else inv_freq.to(DEV),
-                        rot, None, None, H, Hkv, D, err)
+                        rot, None, None, H, Hkv, D, err, pairing)
     assert torch.equal(d_qkv2.cpu()[:, :q_cols], d_qkv.cpu()[:, :q_cols]) and float(d_k2.abs().sum()) == 0
     # a missing page is reported, not written through
     bad = table.clone(); bad[2, 1] = -1

@@ -46,7 +46,7 @@ def _lib():
     lib = library()
     if not _declared:
         for name in ("vmb_last_error", "vmb_config_describe", "vmb_weight_table", "vmb_registered_architectures", "vmb_smollm2_135m_config",
-                     "vmb_tokenizer_decode", "vmb_pretokenize", "vmb_model_info", "vmb_engine_stats", "vmb_engine_generate",
+                     "vmb_tokenizer_decode", "vmb_pretokenize", "vmb_safetensors_info", "vmb_model_info", "vmb_engine_stats", "vmb_engine_generate",
                      "vmb_text_describe", "vmb_text_generate", "vmb_op_times_table"):
             getattr(lib, name).restype = _c_s
         for name in ("vmb_tokenizer_load", "vmb_tokenizer_from_json", "vmb_model_load", "vmb_engine_create", "vmb_text_create",
@@ -120,6 +120,16 @@ def weight_table(config: Dict[str, Any]) -> Dict[str, Dict[str, Any]]:
 def check_model_folder(folder: str) -> None:
     """Reads config.json and model.safetensors of `folder` and checks the tensors against the model (no GPU needed)."""
     _ok(_lib().vmb_check_model_folder(str(folder).encode()))
+
+
+def check_safetensors_header(blob: bytes, data_bytes: int) -> int:
+    """Validates a safetensors header against `data_bytes` bytes of payload (raises WeightError); returns the tensor count."""
+    return _ok(_lib().vmb_safetensors_check_header(blob, _c_ll(len(blob)), _c_ll(int(data_bytes))))
+
+
+def safetensors_info(path: str) -> Dict[str, Dict[str, Any]]:
+    """name -> {"dtype", "shape"} of a safetensors file, as stored."""
+    return json.loads(_text(_lib().vmb_safetensors_info(str(path).encode())))
 
 
 def registered_architectures() -> List[str]:
@@ -650,5 +660,5 @@ class OpTimes:
 
 __all__ = ["ConfigError", "WeightError", "CacheError", "KernelError", "KernelLibraryError", "Entry", "SamplingParams", "Request", "Result",
            "Timing", "Model", "Engine", "GenerationLoop", "EngineConfig", "TextEngine", "Tokenizer", "OpTimes", "load", "load_model",
-           "write_random_model", "weight_table", "describe_config", "check_model_folder", "registered_architectures", "smollm2_135m_config",
+           "write_random_model", "weight_table", "describe_config", "check_model_folder", "check_safetensors_header", "safetensors_info", "registered_architectures", "smollm2_135m_config",
            "pretokenize"]

@@ -192,6 +192,26 @@ int vmb_write_random_model(const char* folder, const char* config_json, unsigned
     });
 }
 
+int vmb_safetensors_check_header(const char* blob, long long n, long long data_bytes) {
+    return status([&] { return static_cast<int>(parse_safetensors_header(std::string(blob, static_cast<size_t>(n)), data_bytes).size()); });
+}
+
+const char* vmb_safetensors_info(const char* path) {
+    return text([&] {
+        json::Value out;
+        out.object();
+        for (const auto& kv : load_safetensors(path)) {
+            json::Value o;
+            o.set("dtype", dtype_name(kv.second.dtype));
+            json::Array shape;
+            for (long long d : kv.second.shape) shape.emplace_back(d);
+            o.set("shape", json::Value(std::move(shape)));
+            out.set(kv.first, o);
+        }
+        return out.dump();
+    });
+}
+
 const char* vmb_registered_architectures(void) {
     return text([&] {
         json::Array a;

@@ -23,6 +23,10 @@ const char* vmb_weight_table(const char* config_json);
 int vmb_check_model_folder(const char* folder);
 // Random-weights mode: writes folder/config.json and folder/model.safetensors.  dtype "bfloat16" or "float32".
 int vmb_write_random_model(const char* folder, const char* config_json, unsigned long long seed, double std, double norm_jitter, const char* dtype);
+// Validates a safetensors header blob of `n` bytes against `data_bytes` bytes of payload; the tensor count, or negative.
+int vmb_safetensors_check_header(const char* blob, long long n, long long data_bytes);
+// name -> {"dtype", "shape"} of a safetensors file as stored (nothing is cast); null on error
+const char* vmb_safetensors_info(const char* path);
 const char* vmb_registered_architectures(void);       // JSON list
 const char* vmb_smollm2_135m_config(void);            // the reference's built-in sizes as a config.json object
 
