@@ -118,20 +118,22 @@ def model_bytes_and_flops(cfg, layers):
     return per_layer, weight_bytes, kv_bytes_per_token, D
 
 
-def decode_run(text_engine, B, prompt_len, steps, warmup, vocab, clock=None):
-    """K timed decode steps at batch B; returns (ms per step, mean context, own-kernel launches, library calls)."""
+def decode_run(text_engine, B, prompt_len, steps, warmup, vocab, clock=None, context_fill=0):
+    """K timed decode steps at batch B; returns (ms per step, mean context, own-kernel launches, library calls, clocks).
+    Timed on the device: CUDA events on the engine's own stream around exactly K steps, each of which runs the step function,
+    the device sampler and the token feedback."""
     import numpy as np
     import torch
     from velomind_b200 import Entry, SamplingParams
-    from velomind_b200.kernels import ops
-    eng, sampler = text_engine.engine, text_engine.sampler
+    eng = text_engine.engine
+    stream = eng.stream
     rng = np.random.default_rng(B)
     slots = [eng.open() for _ in range(B)]
     params = [SamplingParams(temperature=0.0)] * B
     streams = list(range(B))
-    logits = eng.step([Entry(s, rng.integers(0, vocab, prompt_len).tolist(), [prompt_len - 1]) for s in slots])
-    toks = sampler.sample(logits, params, streams, [0] * B)
-
+    first = context_fill or prompt_len
+    logits = eng.step([Entry(s, rng.integers(0, vocab, first).tolist(), [first - 1]) for s in slots])
+    toks = eng.sample(logits, params, streams, [0] * B)
     state = {"toks": toks, "done": 1}
 
     def run(k):
@@ -144,24 +146,25 @@ def decode_run(text_engine, B, prompt_len, steps, warmup, vocab, clock=None):
         k = min(eng.MAX_DECODE_RUN, warmup - done)
         run(k)
         done += k
-    run(min(eng.MAX_DECODE_RUN, steps))          # the shape of the timed run, captured before the clock starts
-    torch.cuda.synchronize()
+    run(min(eng.MAX_DECODE_RUN, steps))          # the shape of the timed run, recorded before the clock starts
+    eng.synchronize()
     ctx0 = eng.length(slots[0])
-    l0, c0 = ops.launch_count, ops.library_calls
+    c0 = eng.counters
     if clock:
         clock.start()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
+    ev0.record(stream)
     done = 0
     while done < steps:
         k = min(eng.MAX_DECODE_RUN, steps - done)
         run(k)
         done += k
-    ev1.record()
-    torch.cuda.synchronize()
+    ev1.record(stream)
+    eng.synchronize()
     clocks = clock.stop() if clock else None
     ms = ev0.elapsed_time(ev1) / steps
-    launches, calls = ops.launch_count - l0, ops.library_calls - c0
+    c1 = eng.counters
+    launches, calls = c1["own_launches"] - c0["own_launches"], c1["library_calls"] - c0["library_calls"]
     mean_ctx = ctx0 + (steps + 1) / 2.0
     for s in slots:
         eng.close(s)
@@ -169,28 +172,41 @@ def decode_run(text_engine, B, prompt_len, steps, warmup, vocab, clock=None):
     return ms, mean_ctx, launches, calls, clocks
 
 
-def prefill_run(text_engine, T, vocab, repeats=5):
+def prefill_run(engine, T, vocab, repeats=5):
+    """Median device time of one whole prompt of T tokens (with the head on its last row): CUDA events on the engine's stream."""
     import numpy as np
     import torch
     from velomind_b200 import Entry
-    eng = text_engine.engine
     rng = np.random.default_rng(7)
+    stream = engine.stream
     times = []
     for r in range(repeats + 2):
         toks = rng.integers(0, vocab, T).tolist()
-        slot = eng.open()
-        entries = [Entry(slot, toks, [T - 1])]
-        torch.cuda.synchronize()
+        slot = engine.open()
+        engine.synchronize()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        ev0.record()
-        eng.step(entries)
-        ev1.record()
-        torch.cuda.synchronize()
-        eng.close(slot)
+        ev0.record(stream)
+        engine.step([Entry(slot, toks, [T - 1])], synchronize=False)
+        ev1.record(stream)
+        engine.synchronize()
+        engine.close(slot)
         if r >= 2:
             times.append(ev0.elapsed_time(ev1))
-    eng.raise_if_error()
+    engine.raise_if_error()
     return statistics.median(times)
+
+
+def unequal_batch_run(text_engine, batch, lo, hi, decode_steps, vocab):
+    """BASELINE.json's 360M run: `batch` prompts of lengths uniform in [lo, hi], then `decode_steps` tokens each through the
+    public entry point; returns (decoded tokens per second, prompt tokens per second, prompt tokens)."""
+    import numpy as np
+    rng = np.random.default_rng(16)
+    prompts = [rng.integers(0, vocab, int(n)).tolist() for n in rng.integers(lo, hi + 1, batch)]
+    text_engine.generate(prompts, temperature=0.0, max_tokens=4, stop_tokens=())          # warm-up: plans and graphs of these shapes
+    text_engine.generate(prompts, temperature=0.0, max_tokens=decode_steps + 1, stop_tokens=())
+    tm = text_engine.last_timing
+    n_prompt = sum(len(p) for p in prompts)
+    return batch * tm.decode_steps / tm.decode_seconds, n_prompt / tm.prefill_seconds, n_prompt
 
 
 def _parse_reference_table(markdown: str):
@@ -302,9 +318,8 @@ def main() -> int:
         return 2
     warmup = max(args.warmup, 3)
 
-    import torch
+    import numpy as np
     import velomind_b200 as vm
-    from velomind_b200.kernels import ops
 
     cfg = dict(vm.SMOLLM2_135M)
     cfg.update(SHAPES[args.shape])
@@ -317,7 +332,7 @@ def main() -> int:
 
     with tempfile.TemporaryDirectory(prefix="velomind_bench_") as folder:
         vm.write_random_model(folder, cfg, seed=0, std=0.02)
-        te = vm.TextEngine(vm.EngineConfig(model_path=folder, dtype="bfloat16", max_tokens=64 * context, max_batch=64)).load()
+        te = vm.TextEngine(vm.EngineConfig(model_path=folder, dtype="bfloat16", max_tokens=64 * context + 8192, max_batch=64)).load()
 
     per_layer, weight_bytes, kv_per_token, D = model_bytes_and_flops(cfg, layers)
 
@@ -327,41 +342,54 @@ def main() -> int:
     step_bytes = weight_bytes + kv_per_token * mean_ctx * B
     achieved = step_bytes / (ms * 1e-3) / 1e9
 
-    # prefill of 2,048 tokens: linears + causal attention + the head on one row
+    # prefill of 2,048 tokens: linears + causal attention + the head on one row.  The headline figure is a FIRST-SEEN shape: the
+    # step's kernels launched one by one from the host, which is what a prompt of a new length gets; the same step replayed from
+    # its CUDA graph (what a repeated shape gets) goes to `points`.
     T = 2048
-    pms = prefill_run(te, T, vocab)
+    fresh = vm.Engine(te.model, T + 64, use_graphs=False)
+    pms = prefill_run(fresh, T, vocab)
+    del fresh
     H = cfg["num_attention_heads"]
     flops = 2.0 * T * per_layer * layers + 4.0 * D * H * (T * (T + 1) / 2.0) * layers + 2.0 * vocab * cfg["hidden_size"]
     prefill = {"value": T * 1000.0 / pms, "tokens": T, "ms": pms, "frac": flops / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12)}
 
     points, e2e = {}, None
     if not args.quick:
+        replayed_ms = prefill_run(te.engine, T, vocab)
+        points["prefill_2048_replayed"] = T * 1000.0 / replayed_ms
         for b in (1, 64):
             m, _, _, _, _ = decode_run(te, b, prompt_len, args.steps, warmup, vocab)
             points[f"decode_b{b}"] = b * 1000.0 / m
         # end to end through the public entry point: host token ids in, host token ids out
-        import numpy as np
         rng = np.random.default_rng(1)
         prompts = [rng.integers(0, vocab, prompt_len).tolist() for _ in range(B)]
         # the host reads every step's tokens and sends the next step's descriptors (steps_per_sync=1), as the contract asks
         te.generate(prompts, temperature=0.0, max_tokens=warmup + 1, stop_tokens=(), steps_per_sync=1)
-        from velomind_b200.kernels import ops as kernel_ops
         # bytes are counted where they are copied (descriptors and sampler parameters up, sampled tokens down); what the
         # prompt step alone moves is taken off, as the timed region is the decode steps
-        h2d0, d2h0 = kernel_ops.h2d_bytes, kernel_ops.d2h_bytes
+        c0 = te.engine.counters
         te.generate(prompts, temperature=0.0, max_tokens=1, stop_tokens=(), steps_per_sync=1)
-        h2d_prompt, d2h_prompt = kernel_ops.h2d_bytes - h2d0, kernel_ops.d2h_bytes - d2h0
-        h2d0, d2h0 = kernel_ops.h2d_bytes, kernel_ops.d2h_bytes
+        c1 = te.engine.counters
+        h2d_prompt, d2h_prompt = c1["h2d_bytes"] - c0["h2d_bytes"], c1["d2h_bytes"] - c0["d2h_bytes"]
         te.generate(prompts, temperature=0.0, max_tokens=args.steps + 1, stop_tokens=(), steps_per_sync=1)
+        c2 = te.engine.counters
         tm = te.last_timing
         e2e = {"value": B * tm.decode_steps / tm.decode_seconds, "unit": "tokens/s",
-               "h2d_bytes_per_step": round((kernel_ops.h2d_bytes - h2d0 - h2d_prompt) / max(tm.decode_steps, 1)),
-               "d2h_bytes_per_step": round((kernel_ops.d2h_bytes - d2h0 - d2h_prompt) / max(tm.decode_steps, 1))}
-
-    if e2e is not None:
+               "h2d_bytes_per_step": round((c2["h2d_bytes"] - c1["h2d_bytes"] - h2d_prompt) / max(tm.decode_steps, 1)),
+               "d2h_bytes_per_step": round((c2["d2h_bytes"] - c1["d2h_bytes"] - d2h_prompt) / max(tm.decode_steps, 1))}
         # the same call with 8 decode steps queued per host round trip
         te.generate(prompts, temperature=0.0, max_tokens=args.steps + 1, stop_tokens=(), steps_per_sync=8)
         points["e2e_queued_8"] = B * te.last_timing.decode_steps / te.last_timing.decode_seconds
+        if args.shape == "360m":
+            # BASELINE.json's run at this shape: batch 16, prompt lengths uniform in [64, 1024], 256 decode steps
+            dec, pre, n_prompt = unequal_batch_run(te, 16, 64, 1024, 256, vocab)
+            points["unequal_b16_decode"] = dec
+            points["unequal_b16_prompt_tokens_per_s"] = pre
+        if args.shape == "1.7b":
+            # BASELINE.json's run at this shape: decode at batch 1 / 8 / 64 up to context 4096
+            for b in (1, 8, 64):
+                m, _, _, _, _ = decode_run(te, b, prompt_len, min(args.steps, 32), 3, vocab, context_fill=context - 64)
+                points[f"decode_b{b}_ctx4096"] = b * 1000.0 / m
     line = {
         "metric": f"decode tok/s at batch 8 (SmolLM2-{args.shape.upper()} shape, prompts of 512 tokens)",
         "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": ms,
@@ -371,6 +399,7 @@ def main() -> int:
                    "hidden": cfg["hidden_size"], "heads": H, "kv_heads": cfg["num_key_value_heads"], "head_dim": D,
                    "intermediate": cfg["intermediate_size"], "vocab": vocab, "rope_theta": cfg["rope_theta"],
                    "rms_eps": cfg["rms_norm_eps"], "tied_embeddings": True, "sampling": "greedy on device",
+                   "prefill_shape": "first seen (kernels launched one by one); points.prefill_2048_replayed: from its CUDA graph",
                    "l2": "inputs larger than L2 (weights + cache > 126 MB)", "peaks": pk["source"]},
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"]},

@@ -438,6 +438,12 @@ class Engine:
     def synchronize(self) -> None:
         _ok(_lib().vmb_engine_synchronize(self._h))
 
+    @property
+    def stream(self):
+        """The engine's CUDA stream as a torch stream (to record events on, or to order torch work behind the engine's)."""
+        import torch
+        return torch.cuda.ExternalStream(int(_lib().vmb_engine_stream(self._h)))
+
     def raise_if_error(self) -> None:
         """Synchronise and raise if a kernel reported a fault of the step's descriptors (no page, bad id)."""
         _ok(_lib().vmb_engine_raise_if_error(self._h))

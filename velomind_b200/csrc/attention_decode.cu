@@ -107,6 +107,30 @@ VM_API long long vm_attention_decode_no_alloc_bytes(int B, int H, int D, int n_s
     return no_alloc_counter_bytes(B, H) + 4ll * B * H * n_splits * (D + 2);
 }
 
+namespace {
+// The array's address on the current device: looked up once per device, with that device current.  (No lock: two host
+// threads that both make a device's first call look the same address up and store the same value.)
+int no_alloc_address(unsigned char** base) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= NO_ALLOC_MAX_DEVICES) return VM_ERR_UNSUPPORTED;
+    if (no_alloc_base[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, vm_no_alloc_scratch);
+        if (e != cudaSuccess) return (int)e;
+        no_alloc_base[dev] = static_cast<unsigned char*>(p);
+    }
+    *base = no_alloc_base[dev];
+    return 0;
+}
+}  // namespace
+
+VM_API void* vm_attention_decode_no_alloc_scratch(void) {
+    unsigned char* base = nullptr;
+    return no_alloc_address(&base) == 0 ? base : nullptr;
+}
+
 VM_API int vm_attention_decode_bf16_no_alloc(const void* q, int q_row_stride, const void* kpages, const void* vpages,
                                              const int* block_table, int max_blocks, const int* positions, void* out,
                                              int B, int H, int Hkv, int D, int n_splits, float scale, int window,
@@ -117,23 +141,13 @@ VM_API int vm_attention_decode_bf16_no_alloc(const void* q, int q_row_stride, co
     if (Hkv <= 0 || H % Hkv != 0 || n_splits > MAX_SPLITS || (q_row_stride % 8) != 0 || D % 16 != 0 || D > 128)
         return VM_ERR_UNSUPPORTED;
     if (vm_attention_decode_no_alloc_bytes(B, H, D, n_splits) > VM_NO_ALLOC_SCRATCH_BYTES) return VM_NO_ALLOC_TOO_LARGE;
-    int dev = -1;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return (int)e;
-    if (dev < 0 || dev >= NO_ALLOC_MAX_DEVICES) return VM_ERR_UNSUPPORTED;
-    if (no_alloc_base[dev] == nullptr) {
-        // once per device, with that device current: the symbol's address ON THIS DEVICE.  (No lock: two host threads
-        // that both make a device's first call look the same address up and store the same value.)
-        void* p = nullptr;
-        e = cudaGetSymbolAddress(&p, vm_no_alloc_scratch);
-        if (e != cudaSuccess) return (int)e;
-        no_alloc_base[dev] = static_cast<unsigned char*>(p);
-    }
-    unsigned char* base = no_alloc_base[dev];
+    unsigned char* base = nullptr;
+    const int looked_up = no_alloc_address(&base);
+    if (looked_up != 0) return looked_up;
     int* counters = reinterpret_cast<int*>(base);
     float* partial = reinterpret_cast<float*>(base + no_alloc_counter_bytes(B, H));
     // the array keeps the last call's contents: the counters must start at zero
-    e = cudaMemsetAsync(counters, 0, (size_t)no_alloc_counter_bytes(B, H), stream);
+    const cudaError_t e = cudaMemsetAsync(counters, 0, (size_t)no_alloc_counter_bytes(B, H), stream);
     if (e != cudaSuccess) return (int)e;
     return vm_attention_decode_bf16(q, q_row_stride, kpages, vpages, block_table, max_blocks, positions, out, partial,
                                     counters, B, H, Hkv, D, n_splits, scale, window, n_pages, err, stream);

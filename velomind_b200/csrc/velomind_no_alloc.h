@@ -46,6 +46,11 @@ extern "C" {
 // Bytes of the static scratch a call with these sizes would use.
 long long vm_attention_decode_no_alloc_bytes(int B, int H, int D, int n_splits);
 
+// The device address of the static scratch on the current device (looked up like the entry point's first call does), or
+// null.  For tests and diagnostics: a test fills the array with garbage between calls to show that a call depends on
+// nothing an earlier call left there.
+void* vm_attention_decode_no_alloc_scratch(void);
+
 // q [B, H, D] bf16 rows with stride q_row_stride (elements); kpages/vpages [n_pages, Hkv, 64, D] bf16;
 // block_table int32 [B, max_blocks]; positions int32 [B] (place of each sequence's new token);
 // out [B, H*D] bf16.  One new token per sequence.

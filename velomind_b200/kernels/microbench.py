@@ -2,8 +2,7 @@
 
 The kernel is launched `--repeat` times in one CUDA graph (as the decode step launches it) and the mean
 time per launch is printed with the bytes it has to read and the bandwidth that corresponds to.  Weights
-rotate through enough copies to exceed the L2 cache.  This is the command the ncu summaries under
-profiles/ were made with.
+rotate through enough copies to exceed the L2 cache.
 """
 from __future__ import annotations
 
@@ -21,8 +20,10 @@ KERNELS = ["qkv_rope", "out_residual", "gate_up_swiglu", "down_residual", "head"
 
 def _prefill_step(a) -> int:
     """One whole prompt of --tokens tokens through a random model of the given sizes (--layers layers): the step's time
-    when replayed from its CUDA graph, and eagerly (the launches one by one, for a launch list under a profiler)."""
+    when replayed from its CUDA graph, and eagerly (the launches one by one, for a launch list under a profiler).  Host clock
+    around a call that waits for the device."""
     import tempfile
+    import time
 
     import numpy as np
 
@@ -42,13 +43,10 @@ def _prefill_step(a) -> int:
             times = []
             for _ in range(4 if graphs else 2):
                 slot = eng.open()
-                torch.cuda.synchronize()
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record()
-                eng.step([Entry(slot, toks, [T - 1])])
-                e1.record()
-                torch.cuda.synchronize()
-                times.append(e0.elapsed_time(e1))
+                eng.synchronize()
+                t0 = time.perf_counter()
+                eng.step([Entry(slot, toks, [T - 1])])          # waits for the device
+                times.append((time.perf_counter() - t0) * 1e3)
                 eng.close(slot)
             out[name + "_ms"] = round(min(times), 4)
         print(json.dumps(out))
