@@ -1,9 +1,9 @@
-"""The device operations the parts are made of: thin checked wrappers over the CUDA launchers.
+"""The kernel launchers of the library (include/velomind_b200/kernels.h) bound for Python: thin checked wrappers that take
+torch CUDA tensors and launch on torch's current stream.  The kernel tests and the microbenchmark call the kernels alone
+through these; the engine itself is C++ and calls the launchers directly (engine/ops.h).
 
-Every function takes CUDA tensors and launches on torch's current stream.
-There is no other implementation: a tensor that is not on a CUDA device, or a
-missing kernel library, raises.  Activations are float32 or bfloat16 (one dtype
-per engine); the residual stream is always float32.
+There is no other implementation: a tensor that is not on a CUDA device, or a missing library, raises.  Activations are
+float32 or bfloat16; the residual stream is always float32.
 """
 from __future__ import annotations
 
@@ -189,10 +189,6 @@ def attention_prefill_tc_bf16(q: torch.Tensor, q_row_stride: int, k_pages: torch
            "attention_prefill_tc_bf16")
 
 
-TC_ATTENTION = True            # head size 64: prefill attention of long prompts on tcgen05 instead of mma.sync
-TC_ATTENTION_MIN_BLOCKS = 20   # ... when a tile sees at least this many key blocks of 64
-TC_ATTENTION_CTAS_PER_SM = 3   # CTAs of that kernel an SM holds at once (registers and shared memory)
-
 _decode_counters = {}
 DECODE_COUNTERS = 1 << 16
 MAX_DECODE_SPLITS = 16
@@ -237,39 +233,6 @@ def attention_decode_bf16(q: torch.Tensor, q_row_stride: int, k_pages: torch.Ten
            "attention_decode_bf16")
 
 
-def attention(ctx, q: torch.Tensor, q_row_stride: int, k_pages: torch.Tensor, v_pages: torch.Tensor,
-              block_table: torch.Tensor, out: torch.Tensor, H: int, Hkv: int, D: int, scale: float, window: int = 0) -> None:
-    """Attention of the step's tokens over the cache; picks the kernel for the step's shape and dtype:
-    bfloat16 with one new token per sequence -> split-KV decode kernel; bfloat16 otherwise -> tensor-core
-    prefill kernel; float32, or a head size those refuse -> the generic kernel."""
-    fast = out.dtype == torch.bfloat16 and D % 16 == 0 and D <= 128 and q_row_stride % 8 == 0
-    if fast and ctx.one_token_each and ctx.B * H <= DECODE_COUNTERS:
-        n_splits = decode_splits(ctx.B, Hkv, H // Hkv, block_table.shape[1], out.device)
-        partial = ctx.take((ctx.B_cap * H * MAX_DECODE_SPLITS * (D + 2),), torch.float32)   # sized by shape, not by lengths
-        attention_decode_bf16(q, q_row_stride, k_pages, v_pages, block_table, ctx.positions, out, partial,
-                              decode_counters(out.device), H, Hkv, D, n_splits, scale, window, ctx.err)
-        ctx.ws.give(partial)
-    elif fast:      # the tile count follows from the sequences' new-token counts, which are part of a recorded step's shape
-        lens = ctx.host_cu_tokens[1:] - ctx.host_cu_tokens[:-1]
-        # the longest chain of key blocks a tile walks, and how many CTAs there are to hide it behind
-        most_blocks = (min(ctx.max_ctx_len, window + 64) if window > 0 else ctx.max_ctx_len) // 64 + 1
-        if TC_ATTENTION and D == 64 and most_blocks >= TC_ATTENTION_MIN_BLOCKS and err_ok(ctx):
-            # long prompts: the tcgen05 kernel, a tile's key blocks dealt out to as many CTAs (2 to 4) as still fit the GPU at once
-            # (measured, 9 heads: 1,536 tokens 23.7 us against 32.2 us for the mma.sync kernel; 2,048: 33.6 / 39.4; 4,096: 89.9 / 123.8;
-            #  1,024: 17.6 / 16.6, hence the threshold)
-            n_tiles = int(((lens + 127) // 128).sum())
-            attention_prefill_tc_bf16(q, q_row_stride, k_pages, v_pages, block_table, ctx.positions, ctx.cu_tokens, n_tiles, out,
-                                      H, Hkv, D, scale, window, ctx.err, max(2, min(4, _tc_attention_slots(out.device) // max(1, n_tiles * H))))
-            return
-        n_tiles = int(((lens + 63) // 64).sum())
-        groups = 2 if most_blocks >= 8 else 1      # measured at 9 heads of 64: 2 groups 39 us, 1 group 43 us, 4 groups 46 us (2,048 tokens)
-        attention_prefill_bf16(q, q_row_stride, k_pages, v_pages, block_table, ctx.positions, ctx.cu_tokens, n_tiles, out,
-                               H, Hkv, D, scale, window, ctx.err, groups)
-    else:
-        attention_generic(q, q_row_stride, k_pages, v_pages, block_table, ctx.positions, ctx.seq_of_token, out,
-                          H, Hkv, D, scale, window, ctx.err)
-
-
 _sm_counts = {}
 
 
@@ -282,20 +245,9 @@ def sm_count(device=None) -> int:
     return _sm_counts[key]
 
 
-def _tc_attention_slots(device) -> int:
-    """CTAs of the tcgen05 attention kernel the GPU holds at once."""
-    return sm_count(device) * TC_ATTENTION_CTAS_PER_SM
-
-
-def err_ok(ctx) -> bool:
-    """True if the step has an error word for kernels that may give up a wait."""
-    return getattr(ctx, "err", None) is not None
-
-
 def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
-    """out = x @ weight^T.  x [T, K], weight [N, K] (the checkpoint's [out, in] layout), out [T, N].
-    A library matrix product, as in the reference (src/cuda/ops/matmul.cu:87-96); float32 runs without
-    any reduced-precision mode."""
+    """out = x @ weight^T through torch (cuBLAS): the library product the microbenchmark compares this library's kernels with.
+    x [T, K], weight [N, K], out [T, N]; float32 runs without any reduced-precision mode."""
     if not x.is_cuda:
         raise KernelError("this library runs on CUDA devices only; got a tensor on " + str(x.device))
     global library_calls
@@ -306,17 +258,6 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
         torch.mm(x, weight.t(), out=out)
     else:
         torch.mm(x, weight.t(), out_dtype=out.dtype, out=out)
-
-
-SKINNY_MAX_ROWS = 32       # beyond this the library product wins (the A tile is staged once per CTA; measured per decode
-#                            step at 33 / 48 / 64 rows: 1.07 / 1.20 / 1.25 ms fused against 1.02 / 1.07 / 1.05 ms with cuBLAS)
-SKINNY_NORM_ROWS = 32      # up to this many rows the norm is fused into the product that follows it (measured per decode
-#                            step at 17 / 24 / 32 rows: 0.70 / 0.72 / 0.86 ms against 0.82 / 0.84 / 0.92 ms with a norm kernel)
-
-
-def skinny_ok(M: int, K: int, weight: torch.Tensor) -> bool:
-    """True if the weight-streaming kernels take this product (few rows, bfloat16, K a multiple of 32)."""
-    return 0 < M <= SKINNY_MAX_ROWS and K % 32 == 0 and weight.dtype == torch.bfloat16 and weight.is_contiguous()
 
 
 def _norm_args(norm):
@@ -361,22 +302,6 @@ def skinny_qkv_rope(x: torch.Tensor, norm, weight: torch.Tensor, q_out: torch.Te
                                         _c_int(block_table.shape[1]), _ptr(inv_freq), _c_int(rot_dim), _c_int(pairing), _ptr(k_pages),
                                         _ptr(v_pages), _c_int(H), _c_int(Hkv), _c_int(D), _c_int(n_pages), _ptr(err), _stream()),
            "skinny_qkv_rope")
-
-
-# Many rows (prefill): the tcgen05 kernels with fused epilogues exist and are tested, but at this model family's
-# small inner sizes (K = 576 .. 1536) the library product plus separate elementwise kernels is still faster
-# (measured: profiles/tc_gemm_vs_cublas.md), so the fused tensor-core path is taken only at or above this many
-# rows.  None: never.  Set by Engine(fused_prefill_rows=...).
-TC_FUSED_MIN_ROWS = None
-
-
-def tc_fused_rows(T: int) -> bool:
-    return TC_FUSED_MIN_ROWS is not None and T >= TC_FUSED_MIN_ROWS
-
-
-def tc_ok(M: int, K: int, weight: torch.Tensor) -> bool:
-    """True if the tensor-core (tcgen05 + TMA) products take this shape: bfloat16, rows of 16-byte multiples."""
-    return M > 0 and K % 8 == 0 and weight.dtype == torch.bfloat16 and weight.is_contiguous()
 
 
 def tc_linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor], residual: Optional[torch.Tensor] = None,
