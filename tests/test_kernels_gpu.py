@@ -201,6 +201,9 @@ def _run_attention(kind, dtype, H, Hkv, D, lens_before, new, window, seed=0, gro
         n_tiles = sum(-(-n // 128) for n in new)
         o.attention_prefill_tc_bf16(d(qkv), stride, d(kp), d(vp), d(table), d(positions), d(cu), n_tiles, out, H, Hkv, D, scale,
                                     window, err, groups)
+    elif kind == "prefill_ws":
+        o.attention_prefill_ws_bf16(d(qkv), stride, d(kp), d(vp), d(table), d(positions), d(cu), cu.tolist(), out, H, Hkv, D, scale,
+                                    window, err, groups)
     else:
         B = len(new)
         n_splits = o.decode_splits(B, Hkv, H // Hkv, table.shape[1])
@@ -245,6 +248,47 @@ def test_attention_prefill_tcgen05(H, Hkv, window, groups):
     got, want = _run_attention("prefill_tc", torch.bfloat16, H, Hkv, 64, [0, 130, 63, 0, 200, 0, 0, 17],
                                [200, 67, 2, 1, 1, 128, 129, 600], window, groups=groups)
     assert np.isfinite(got).all() and np.abs(got - want).max() <= 2e-2
+
+
+# (heads, kv heads): three heads of a group per CTA; four; one head and three row tiles per CTA; two heads and two row tiles
+@pytest.mark.parametrize("H,Hkv", [(9, 3), (4, 1), (5, 5), (4, 2), (5, 1)])
+@pytest.mark.parametrize("window", [0, 70, 64, 200])
+@pytest.mark.parametrize("cluster", [0, 1, 2, 3, 5, 8])
+def test_attention_prefill_warp_specialised(H, Hkv, window, cluster):
+    """The warp-specialised tensor-memory kernel (head size 64): prompts of awkward lengths around its 128-token tiles and
+    64-key blocks, a continued sequence, single tokens, long prompts whose tile groups are walked in pairs, and every way of
+    dealing the key blocks out to a cluster."""
+    got, want = _run_attention("prefill_ws", torch.bfloat16, H, Hkv, 64, [0, 130, 63, 0, 200, 0, 0, 17, 0],
+                               [200, 67, 2, 1, 1, 128, 129, 600, 1100], window, groups=cluster)
+    assert np.isfinite(got).all() and np.abs(got - want).max() <= 2e-2
+
+
+def test_attention_prefill_warp_specialised_moves_its_reference_maximum():
+    """Scores that grow along the keys by far more than the gap the kernel lets its reference maximum lag behind: the rows'
+    sums in tensor memory are rescaled several times."""
+    o = ops()
+    H = Hkv = 1
+    D, L = 64, 700
+    rng = np.random.default_rng(5)
+    k = rng.standard_normal((L, Hkv, D)).astype(np.float32)
+    v = rng.standard_normal((L, Hkv, D)).astype(np.float32)
+    q = rng.standard_normal((L, H, D)).astype(np.float32)
+    k[:, 0, 0] = np.arange(L) * 0.35                       # with q[.., 0] = 8: the raw score grows by 2.8 per key, 180 per block
+    q[:, 0, 0] = 8.0
+    scale = 1.0 / math.sqrt(D)
+    bf = torch.bfloat16
+    Kt, Vt, Qt = [torch.from_numpy(k).to(bf)], [torch.from_numpy(v).to(bf)], torch.from_numpy(q).to(bf)
+    want = P.attention(Qt.float().numpy(), Kt[0].float().numpy(), Vt[0].float().numpy(), scale).reshape(L, H * D)
+    kp, vp, table = _paged(Kt, Vt, [L], 14, 3)
+    out = torch.full((L, H * D), float("nan"), dtype=bf, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    cu = torch.tensor([0, L], dtype=torch.int32)
+    for cluster in (1, 2):
+        o.attention_prefill_ws_bf16(Qt.reshape(L, H * D).to(DEV), H * D, kp.to(bf).to(DEV), vp.to(bf).to(DEV), table.to(DEV),
+                                    torch.arange(L, dtype=torch.int32, device=DEV), cu.to(DEV), [0, L], out, H, Hkv, D, scale, 0, err, cluster)
+        assert int(err.item()) == 0
+        got = out.float().cpu().numpy()
+        assert np.isfinite(got).all() and np.abs(got - want).max() <= 2e-2
 
 
 @pytest.mark.parametrize("H,Hkv,D", SHAPES + [(12, 1, 64), (16, 16, 64)])

@@ -50,6 +50,11 @@ int vm_attention_prefill_bf16(const void* q, int q_row_stride, const void* kpage
 int vm_attention_prefill_tc_bf16(const void* q, int q_row_stride, const void* kpages, const void* vpages, const int* block_table,
                                  int max_blocks, const int* positions, const int* cu_tokens, int B, int n_tiles, void* out, int H,
                                  int Hkv, int D, float scale, int window, int n_pages, int* err, int groups, cudaStream_t stream);
+// the warp-specialised tcgen05 kernel: host_cu_tokens [B + 1] (host memory) repeats cu_tokens, the launch is shaped from it
+int vm_attention_prefill_ws_bf16(const void* q, int q_row_stride, const void* kpages, const void* vpages, const int* block_table,
+                                 int max_blocks, const int* positions, const int* cu_tokens, const int* host_cu_tokens, int B,
+                                 void* out, int H, int Hkv, int D, float scale, int window, int n_pages, int* err, int groups,
+                                 cudaStream_t stream);
 long long vm_attention_decode_scratch_floats(int B, int H, int D, int n_splits);
 int vm_attention_decode_bf16(const void* q, int q_row_stride, const void* kpages, const void* vpages, const int* block_table,
                              int max_blocks, const int* positions, void* out, float* partial, int* counters, int B, int H,

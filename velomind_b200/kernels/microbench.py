@@ -14,7 +14,7 @@ import torch
 
 from . import ops
 
-KERNELS = ["qkv_rope", "out_residual", "gate_up_swiglu", "down_residual", "head", "attn_decode", "attn_prefill", "attn_prefill_tc",
+KERNELS = ["qkv_rope", "out_residual", "gate_up_swiglu", "down_residual", "head", "attn_decode", "attn_prefill", "attn_prefill_tc", "attn_prefill_ws",
            "add_rmsnorm", "sample", "tc_linear", "tc_residual", "tc_swiglu", "cublas_linear", "prefill_step"]
 
 
@@ -95,6 +95,7 @@ def main(argv=None) -> int:
     ap.add_argument("--k", type=int, default=0, help="tc_*/cublas_linear: inner size (default hidden)")
     ap.add_argument("--splits", type=int, default=0, help="attn_decode: key splits (0: the engine's choice)")
     ap.add_argument("--groups", type=int, default=4, help="attn_prefill: warp groups sharing a tile's key blocks")
+    ap.add_argument("--cluster", type=int, default=0, help="attn_prefill_ws: CTAs per cluster (0: the launcher's choice)")
     ap.add_argument("--layers", type=int, default=6, help="prefill_step: layers of the random model")
     ap.add_argument("--temp", type=float, default=0.0, help="sample: temperature (0: greedy)")
     ap.add_argument("--top-p", type=float, default=0.9, help="sample: nucleus mass, with --temp")
@@ -125,7 +126,7 @@ def main(argv=None) -> int:
     n_pages = M * width
     inv = torch.ones(D // 2, device=dev)
     bytes_read = 0
-    if a.kernel in ("qkv_rope", "attn_decode", "attn_prefill", "attn_prefill_tc"):
+    if a.kernel in ("qkv_rope", "attn_decode", "attn_prefill", "attn_prefill_tc", "attn_prefill_ws"):
         kp = torch.randn(n_pages, Hkv, 64, D, device=dev).to(bf)
         vp = torch.randn_like(kp)
     if a.kernel == "qkv_rope":
@@ -161,7 +162,7 @@ def main(argv=None) -> int:
         fn = lambda: ops.attention_decode_bf16(q, H * D, kp, vp, table, pos, out, partial, ops.decode_counters(dev), H, Hkv, D,
                                                splits, 1.0 / math.sqrt(D))
         bytes_read = M * (a.ctx + 1) * 2 * Hkv * D * 2
-    elif a.kernel in ("attn_prefill", "attn_prefill_tc"):
+    elif a.kernel in ("attn_prefill", "attn_prefill_tc", "attn_prefill_ws"):
         T = a.tokens
         width = 1
         while width < T // 64 + 1:
@@ -177,6 +178,10 @@ def main(argv=None) -> int:
             err = torch.zeros(1, dtype=torch.int32, device=dev)
             fn = lambda: ops.attention_prefill_tc_bf16(qkv, (H + 2 * Hkv) * D, kp, vp, table, positions, cu, -(-T // 128), out, H, Hkv,
                                                        D, 1.0 / math.sqrt(D), 0, err, a.groups)
+        elif a.kernel == "attn_prefill_ws":
+            err = torch.zeros(1, dtype=torch.int32, device=dev)
+            fn = lambda: ops.attention_prefill_ws_bf16(qkv, (H + 2 * Hkv) * D, kp, vp, table, positions, cu, [0, T], out, H, Hkv,
+                                                       D, 1.0 / math.sqrt(D), 0, err, a.cluster)
         else:
             fn = lambda: ops.attention_prefill_bf16(qkv, (H + 2 * Hkv) * D, kp, vp, table, positions, cu, -(-T // 64), out, H, Hkv, D,
                                                     1.0 / math.sqrt(D), groups=a.groups)

@@ -189,6 +189,24 @@ def attention_prefill_tc_bf16(q: torch.Tensor, q_row_stride: int, k_pages: torch
            "attention_prefill_tc_bf16")
 
 
+def attention_prefill_ws_bf16(q: torch.Tensor, q_row_stride: int, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                              block_table: torch.Tensor, positions: torch.Tensor, cu_tokens: torch.Tensor, host_cu_tokens,
+                              out: torch.Tensor, H: int, Hkv: int, D: int, scale: float, window: int = 0,
+                              err: Optional[torch.Tensor] = None, groups: int = 0) -> None:
+    """The warp-specialised tcgen05 attention (head size 64): a CTA per group of 128-row tiles that share a kv head,
+    softmax warps, a copy warp (TMA) and a product warp; clusters of `groups` CTAs (0: chosen) take a pair of tile groups'
+    key blocks in turn.  host_cu_tokens: the offsets of cu_tokens as a list of ints."""
+    global tc_attention_calls
+    tc_attention_calls += 1
+    B = cu_tokens.shape[0] - 1
+    host = (ctypes.c_int * (B + 1))(*[int(x) for x in host_cu_tokens])
+    _check(library().vm_attention_prefill_ws_bf16(_ptr(q), _c_int(q_row_stride), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+                                                  _c_int(block_table.shape[1]), _ptr(positions), _ptr(cu_tokens), host, _c_int(B),
+                                                  _ptr(out), _c_int(H), _c_int(Hkv), _c_int(D), _c_f(scale), _c_int(window),
+                                                  _c_int(k_pages.shape[0]), _ptr(err), _c_int(groups), _stream()),
+           "attention_prefill_ws_bf16")
+
+
 _decode_counters = {}
 DECODE_COUNTERS = 1 << 16
 MAX_DECODE_SPLITS = 16
