@@ -109,6 +109,31 @@ def test_decoding_thousands_of_tokens_in(tmp_path):
         assert _worst(got, S.expected_rows(steps, requests, plain)) <= TOL[dtype]
 
 
+def test_prompts_of_thousands_of_tokens_take_the_warp_specialised_attention(tmp_path):
+    """Head size 64 and block tables of 40 pages and more: the warp-specialised tensor-memory attention.  A prompt of 3,000
+    tokens beside a short one, then a prompt cut into steps of 1,700 and 1,300 tokens (the second step's queries start 1,700
+    keys in), then single tokens; logits at places spread over the prompts against the plain model, with a spike: the weights
+    are scaled so that attention is sharp and a lost or doubled key block shows."""
+    import velomind_b200 as vm
+    cfg = dict(TINY_C, max_position_embeddings=4096)
+    folder = vm.write_random_model(str(tmp_path / "long"), cfg, seed=4, std=0.08, norm_jitter=0.3)
+    requests = S.make_requests(cfg["vocab_size"], (3003, 40, 3005), seed=37)
+    plain = S.plain_logits(folder, requests)
+    a, b, c = requests["r0"], requests["r1"], requests["r2"]
+    steps = [{"step": 0, "entries": [{"id": "r0", "tokens": a[:3000], "want": [0, 63, 64, 127, 128, 1500, 2047, 2048, 2943, 2944, 2999]},
+                                     {"id": "r1", "tokens": b, "want": [39]}], "end": ["r1"]}]
+    steps += [{"step": len(steps) + j, "entries": [{"id": "r0", "tokens": [a[3000 + j]], "want": [0]}], "end": ["r0"] if j == 2 else []} for j in range(3)]
+    steps.append({"step": len(steps), "entries": [{"id": "r2", "tokens": c[:1700], "want": [1699]}], "end": []})
+    steps.append({"step": len(steps), "entries": [{"id": "r2", "tokens": c[1700:3000], "want": [0, 100, 1299]}], "end": []})
+    steps += [{"step": len(steps) + j, "entries": [{"id": "r2", "tokens": [c[3000 + j]], "want": [0]}], "end": ["r2"] if j == 4 else []} for j in range(5)]
+    engine = _engine(folder, "bfloat16", max_tokens=64 * 100)
+    before = engine.counters["tc_attention_calls"]
+    got = S.run_steps_in_process(engine, steps)
+    engine.raise_if_error()
+    assert engine.counters["tc_attention_calls"] >= before + 3 * cfg["num_hidden_layers"]
+    assert _worst(got, S.expected_rows(steps, requests, plain)) <= TOL["bfloat16"]
+
+
 def test_the_last_places_of_the_longest_context_and_the_refusal_beyond(tmp_path):
     """A sequence of 8,190 tokens goes on to 8,192, the model's limit (`max_position_embeddings`): the two last places still
     equal the plain model; one more token is refused on the host, and the sequence is untouched by the refusal."""
