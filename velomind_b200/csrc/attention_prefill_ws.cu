@@ -11,8 +11,9 @@
 //   * Warps 0 .. 4 NT - 1 are softmax warps: thread r of a tile owns query row r, tensor-memory lane r holds its scores
 //     and its output sums.  Warps 4 NT .. 5 NT - 1 issue the products, one warp per tile (an mbarrier wait costs a
 //     couple of hundred cycles here even when the barrier is complete, so the tiles' chains of waits run side by side).
-//     Warp 5 NT copies: a key page and its value page arrive through TMA (tensor maps over the page pools, 128-byte
-//     swizzle) into a ring of four stages.  In these warps every lane walks the loop and one elected lane issues.
+//     Warp 5 NT copies: the query tiles, then a key page and its value page per block arrive through TMA (tensor maps
+//     over the query rows and the page pools, 128-byte swizzle), the pages into a ring of four stages.  In these warps
+//     every lane walks the loop and one elected lane issues.
 //   * Per key block (one cache page of 64 keys) and tile:  S = Q K^T (M 128, N 64, K 64: four tcgen05.mma) into the
 //     tile's score columns; the row's thread reads its 64 scores, and as soon as they are in registers the scores of
 //     the NEXT block are multiplied into the same columns while the thread masks, exponentiates and writes the
@@ -103,7 +104,8 @@ static_assert(ws_smem_bytes<3>() <= 227 * 1024, "three tiles per CTA must fit an
 
 template <int NT>
 __global__ void __launch_bounds__((5 * NT + 1) * 32) __maxnreg__(NT <= 2 ? 168 : 128)
-attn_prefill_ws_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const WsParams p) {
+attn_prefill_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, const WsParams p) {
     constexpr int ST = WS_STAGES, NSOFT = NT * 128, D = WS_D, BN = WS_BN;
     constexpr uint32_t TMEM_COLS = NT == 1 ? 128u : (NT == 2 ? 256u : 512u);        // per tile: scores 0..63, output sums 64..127
     // instruction descriptors: float32 accumulate (bits 4-5 = 1), A and B bf16 (bits 7-9 and 10-12 = 1), B MN-major
@@ -188,7 +190,7 @@ attn_prefill_ws_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         abort_flag = (ta_u32(smem_raw) & 1023u) ? 1 : 0;    // misaligned tiles would give wrong sums: give up instead
 #pragma unroll
         for (int s = 0; s < NT; ++s) {
-            ta_bar_init(WS_BAR(B_QFULL + s), 4); ta_bar_init(WS_BAR(B_SFULL + s), 1); ta_bar_init(WS_BAR(B_SFREE + s), 4);
+            ta_bar_init(WS_BAR(B_QFULL + s), 1); ta_bar_init(WS_BAR(B_SFULL + s), 1); ta_bar_init(WS_BAR(B_SFREE + s), 4);
             ta_bar_init(WS_BAR(B_PFULL + s), 4); ta_bar_init(WS_BAR(B_PVDONE + s), 1);
         }
 #pragma unroll
@@ -230,18 +232,6 @@ attn_prefill_ws_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             my_valid = sl.valid;
             const uint32_t t_s = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)my_s * 128u;
             const uint32_t t_o = t_s + 64u;
-            if (ok && sl.valid) {                           // the row's queries -> shared, swizzled (rows past the sequence's end are zero)
-                const uint32_t qdst = ta_u32(sQ) + my_s * WS_QTILE + row * 128;
-                const bool live = row < sl.n_rows;
-                const __nv_bfloat16* src = p.q + (size_t)(sl.t0 + (live ? row : 0)) * p.q_row_stride + (size_t)sl.head * D;
-#pragma unroll
-                for (int ch = 0; ch < 8; ++ch) ta_cp_async16(qdst + ((ch ^ (row & 7)) << 4), src + ch * 8, live);
-                ta_commit_group();
-                ta_wait_group<0>();
-                ta_fence_async_smem();
-                __syncwarp();
-                if (lane == 0) ta_bar_arrive(WS_BAR(B_QFULL + my_s));
-            }
             const int pos_r = sl.pos0 + row;
             const int lo_r = (p.window > 0) ? pos_r - p.window + 1 : 0;
             bool has_o = false, pending = false;            // a P V has been issued in this pass; its completion is not yet awaited
@@ -418,6 +408,16 @@ attn_prefill_ws_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             // =============================================================== copies: the key page and the value page of this CTA's
             // blocks (the whole warp walks the loop; one elected lane issues)
             if (ok) {
+                // the query tiles (rows past the sequence's end are whatever follows them, or zeros past the last token: such rows
+                // are computed and never stored)
+#pragma unroll
+                for (int s = 0; s < NT; ++s) {
+                    const WsSlot sl = ws_slot(p, NR, rtg, s, head0, tok_a, tok_b, n_rt, pos_a);
+                    if (sl.valid && ta_elect_one()) {
+                        ta_bar_expect_tx(WS_BAR(B_QFULL + s), WS_QTILE);
+                        ta_tma_load_2d(ta_u32(sQ) + s * WS_QTILE, &map_q, sl.head * D, sl.t0, WS_BAR(B_QFULL + s));
+                    }
+                }
                 int page_next = -1;
                 if (n_my > 0) { const int blk = blk_lo + rank; page_next = (blk < p.max_blocks) ? table[blk] : -1; }
                 for (int it = 0; it < n_my; ++it) {
@@ -486,23 +486,31 @@ attn_prefill_ws_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                         const float* mine = xstage + (size_t)(s2 * WS_BM + trow) * WS_RW;
                         const float* theirs = xrecv + (size_t)(s2 * RPR + idx) * WS_RW;       // + source rank * NT * RPR rows
                         const size_t hop = (size_t)NT * RPR * WS_RW;
-                        float M = mine[D];
-                        for (int g = 0; g < n_grp; ++g)
-                            if (g != rank) M = fmaxf(M, theirs[g * hop + D]);
+                        // maxima and denominators of all sources first, then the sums with every source's loads in flight
+                        float mg[WS_MAX_NC], fg[WS_MAX_NC];
+                        float M = -INFINITY;
+#pragma unroll
+                        for (int g = 0; g < WS_MAX_NC; ++g) {
+                            mg[g] = -INFINITY;
+                            if (g < n_grp) { mg[g] = (g == rank) ? mine[D] : theirs[g * hop + D]; M = fmaxf(M, mg[g]); }
+                        }
                         const float u = (M == -INFINITY) ? 0.f : M;
                         float acc[16], L = 0.f;
 #pragma unroll
                         for (int d = 0; d < 16; ++d) acc[d] = 0.f;
-#pragma unroll 2
-                        for (int g = 0; g < n_grp; ++g) {
-                            const float* src = (g == rank) ? mine : theirs + g * hop;
-                            const float f = ta_exp2((src[D] - u) * p.scale_log2);
-                            L += src[D + 1] * f;
-                            const float4* s4 = reinterpret_cast<const float4*>(src + qd * 16);
 #pragma unroll
-                            for (int c = 0; c < 4; ++c) {
-                                const float4 v = s4[c];
-                                acc[4 * c] += v.x * f; acc[4 * c + 1] += v.y * f; acc[4 * c + 2] += v.z * f; acc[4 * c + 3] += v.w * f;
+                        for (int g = 0; g < WS_MAX_NC; ++g) fg[g] = (g < n_grp) ? ta_exp2((mg[g] - u) * p.scale_log2) : 0.f;
+#pragma unroll
+                        for (int g = 0; g < WS_MAX_NC; ++g) {
+                            if (g < n_grp) {
+                                const float* src = (g == rank) ? mine : theirs + g * hop;
+                                L += src[D + 1] * fg[g];
+                                const float4* s4 = reinterpret_cast<const float4*>(src + qd * 16);
+#pragma unroll
+                                for (int c = 0; c < 4; ++c) {
+                                    const float4 v = s4[c];
+                                    acc[4 * c] += v.x * fg[g]; acc[4 * c + 1] += v.y * fg[g]; acc[4 * c + 2] += v.z * fg[g]; acc[4 * c + 3] += v.w * fg[g];
+                                }
                             }
                         }
                         const float inv = 1.f / L;
@@ -520,6 +528,7 @@ attn_prefill_ws_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             __syncwarp();
             ws_cluster_sync();                              // everybody has its rows: every CTA's copies have been read
         }
+        if (n_pass > 1) __syncthreads();                     // (a cluster of one: the next pass overwrites the query tiles)
         if (*abort_p) ok = false;
     }
 
@@ -581,6 +590,33 @@ int ws_page_map(CUtensorMap* out, const void* base, long long rows) {
     return 0;
 }
 
+// The step's query rows [T][H * 64 of q_row_stride values]; a box is one head's 128 rows.
+int ws_query_map(CUtensorMap* out, const void* q, long long T, int H, int q_row_stride) {
+    struct Entry { const void* q; long long T; int H, stride, device; CUtensorMap map; };
+    static std::mutex lock;
+    static Entry cache[64];
+    static int used = 0, next = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return VM_ERR_BAD_ARG;
+    std::lock_guard<std::mutex> guard(lock);
+    for (int i = 0; i < used; ++i)
+        if (cache[i].q == q && cache[i].T == T && cache[i].H == H && cache[i].stride == q_row_stride && cache[i].device == dev) { *out = cache[i].map; return 0; }
+    WsEncodeTiledFn fn = ws_encode_fn();
+    if (fn == nullptr) return VM_ERR_UNSUPPORTED;
+    cuuint64_t dims[2] = {(cuuint64_t)H * WS_D, (cuuint64_t)T};
+    cuuint64_t strides[1] = {(cuuint64_t)q_row_stride * 2};
+    cuuint32_t box[2] = {(cuuint32_t)WS_D, (cuuint32_t)WS_BM};
+    cuuint32_t estr[2] = {1, 1};
+    CUtensorMap map;
+    if (fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(q), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return VM_ERR_BAD_ARG;
+    const int at = used < 64 ? used++ : (next++ % 64);
+    cache[at] = Entry{q, T, H, q_row_stride, dev, map};
+    *out = map;
+    return 0;
+}
+
 // Clusters of `nc` CTAs of this kernel that the GPU holds at once (asked once per size).
 template <int NT>
 int ws_active_clusters(int nc) {
@@ -603,7 +639,7 @@ int ws_active_clusters(int nc) {
 }
 
 template <int NT>
-int ws_launch(const CUtensorMap& mk, const CUtensorMap& mv, const WsParams& p, long long units, int grid_y, int est_blocks, int groups,
+int ws_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const WsParams& p, long long units, int grid_y, int est_blocks, int groups,
               cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
@@ -632,7 +668,7 @@ int ws_launch(const CUtensorMap& mk, const CUtensorMap& mv, const WsParams& p, l
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = nc; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, attn_prefill_ws_kernel<NT>, mk, mv, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attn_prefill_ws_kernel<NT>, mq, mk, mv, p);
     if (e != cudaSuccess) return (int)e;
     return vm_launch_status();
 }
@@ -666,8 +702,10 @@ VM_API int vm_attention_prefill_ws_bf16(const void* q, int q_row_stride, const v
         units += (n_rtg + 1) / 2;
     }
     if (units <= 0) return 0;
-    CUtensorMap mk, mv;
-    int rc = ws_page_map(&mk, kpages, rows);
+    CUtensorMap mq, mk, mv;
+    int rc = ws_query_map(&mq, q, host_cu_tokens[B], H, q_row_stride);
+    if (rc) return rc;
+    rc = ws_page_map(&mk, kpages, rows);
     if (rc) return rc;
     rc = ws_page_map(&mv, vpages, rows);
     if (rc) return rc;
@@ -679,6 +717,6 @@ VM_API int vm_attention_prefill_ws_bf16(const void* q, int q_row_stride, const v
     int est = max_blocks;                                   // key blocks a pair of tile groups walks, bounded by the table's width
     if (window > 0 && window / WS_BN + 2 < est) est = 2 * (window / WS_BN + 2);
     const int grid_y = Hkv * (G / NH);
-    if (NT == 3) return ws_launch<3>(mk, mv, p, units, grid_y, est, groups, stream);
-    return ws_launch<2>(mk, mv, p, units, grid_y, est, groups, stream);
+    if (NT == 3) return ws_launch<3>(mq, mk, mv, p, units, grid_y, est, groups, stream);
+    return ws_launch<2>(mq, mk, mv, p, units, grid_y, est, groups, stream);
 }
