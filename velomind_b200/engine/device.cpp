@@ -318,7 +318,7 @@ constexpr int MAX_DECODE_SPLITS = 16;
 constexpr int DECODE_ONE_CTA_BLOCKS = 16;     // block tables up to this wide (1,024 tokens): at most two rounds of pages for ten warps
 constexpr int TC_ATTENTION_MIN_BLOCKS = 20;   // head size 64: the tcgen05 prefill attention when a tile may see this many key blocks
 constexpr int TC_ATTENTION_CTAS_PER_SM = 3;   // CTAs of that kernel an SM holds at once (registers and shared memory)
-int WS_ATTENTION_MIN_BLOCKS = 36;             // head size 64: the warp-specialised tcgen05 attention when a tile may see this many key blocks
+int WS_ATTENTION_MIN_BLOCKS = 32;             // head size 64: the warp-specialised tcgen05 attention when a tile may see this many key blocks
 
 int* decode_counters() {
     static std::unique_ptr<DeviceBuffer> per_device[64];
@@ -371,7 +371,7 @@ void attention(StepContext& ctx, const void* q, int q_row_stride, const KVView& 
         if (D == 64 && most_blocks >= WS_ATTENTION_MIN_BLOCKS && (group % 3 == 0 || group % 2 == 0) && ctx.err != nullptr) {
             // the longest prompts: softmax warps, a copy warp and product warps, clusters dealt out to pairs of tile groups
             // (measured, 9 heads: 4,096 tokens 78 us against 88 us for the kernel below, 8,192: 224 / 262; 2,048: 32 / 33;
-            //  2,560: 37 / 48, 3,072: 51 / 58, 1,024: 22 / 18: every CTA pays for its set-up and its cluster's exchange once, whatever its share of the keys;
+            //  2,560: 37 / 48, 3,072: 51 / 58, 1,536: 27 / 24, 1,024: 22 / 18: every CTA pays for its set-up and its cluster's exchange once, whatever its share of the keys;
             //  with one query head per kv head a CTA takes three row tiles of the head instead, which gains nothing: 32 heads, 4,096 tokens 243 / 234 us)
             ++counters().tc_attention_calls;
             Timed t("attention_prefill_ws_bf16", s);
