@@ -266,7 +266,13 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int V, con
 // in shared memory, every pass sums its own eighth, and the eight partial results meet through distributed shared
 // memory (every CTA writes its number into every CTA's table, one hardware cluster barrier, every CTA adds the eight
 // numbers in rank order: the same sum everywhere, so all eight take the same decisions).  Same rules, same results.
-constexpr int SC_CTAS = 8, SC_THREADS = 256, SC_WARPS = SC_THREADS / 32, SC_WAYS = 7, SC_VALS = 8;   // SC_VALS >= SC_WAYS: numbers per exchange
+// What a step costs here is its cluster barrier (2 to 3 us), so there are as few as possible: the largest probability is
+// known without asking (the maximum's own), the nucleus search counts as it sums and, as soon as at most SC_CAND_MAX
+// probabilities are left between its bounds, every CTA receives all of them and finishes the search by itself, and the CTA
+// in whose range the drawn number falls writes the token without a last exchange.
+constexpr int SC_CTAS = 8, SC_THREADS = 256, SC_WARPS = SC_THREADS / 32, SC_WAYS = 7;
+constexpr int SC_VALS = 16;                       // numbers per exchange: SC_WAYS sums and SC_WAYS + 1 counts
+constexpr int SC_CAND_MAX = 2048;                 // the search goes on inside every CTA once this few probabilities are left
 
 __device__ __forceinline__ void sc_cluster_sync() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -284,6 +290,8 @@ struct ScShared {
     int warp_i[SC_WARPS];
     double prefix[SC_THREADS];
     int choice;
+    int scan[SC_WARPS];
+    float cand[SC_CAND_MAX];                  // the probabilities still in question, the same list in every CTA
 };
 
 // Every CTA contributes up to SC_VALS numbers; the caller reads sh.gather[parity][source][k] after the call.
@@ -400,67 +408,142 @@ sample_cluster_kernel(const float* __restrict__ logits, long long row_stride, in
     const float inv_sum = (float)(1.0 / total);
     auto prob = [&](int j) -> float { const float r = sraw[j]; return r < 0.f ? -1.f : r * inv_sum; };
 
-    // ---- nucleus threshold: the largest tau with sum{p_i >= tau} >= top_p (eight-way search on the float bits: what a
-    //      pass costs here is its cluster barrier, so few passes with several thresholds each)
+    // ---- nucleus threshold: the largest tau with sum{p_i >= tau} >= top_p (eight-way search on the float bits)
     float tau = 0.f;
+    const int chunk = (n + SC_THREADS - 1) / SC_THREADS;
+    const int j0 = min(n, tid * chunk), j1 = min(n, j0 + chunk);            // this thread's tokens of the slice, in index order
     if (tp < 1.0f) {
-        float pmax = 0.f;
-        for (int j = tid; j < n; j += SC_THREADS) pmax = fmaxf(pmax, prob(j));
-        pmax = vm_warp_max(pmax);
-        __syncthreads();
-        if (lane == 0) sh.warp_v[warp] = pmax;
-        __syncthreads();
-        pmax = 0.f;
-        for (int k = 0; k < SC_WARPS; ++k) pmax = fmaxf(pmax, sh.warp_v[k]);
-        mine[0] = (double)pmax;
-        sc_all_gather(sh, parity, rank, mine, 1);
-        pmax = 0.f;
-        for (int c = 0; c < SC_CTAS; ++c) pmax = fmaxf(pmax, (float)sh.gather[parity][c][0]);
-        parity ^= 1;
+        const float pmax = 1.0f * inv_sum;                    // the probability of the maximum itself (its exponential is 1)
         uint32_t lo = 0u, hi = __float_as_uint(pmax) + 1u;   // cond(lo) holds or tau stays 0; cond(hi) fails
         double above = 0.0;                                   // the mass of p >= hi: known from the pass that lowered hi
-        while (hi - lo > 1u) {                                // (the same trip count in every CTA: the sums are the same)
+        long long left = (long long)V;                        // probabilities in [lo, hi), an upper bound before the first pass
+        // One pass: the masses above SC_WAYS thresholds between lo and hi (only what lies between the bounds is summed again)
+        // and, with `count`, how many probabilities lie above each and above lo.  `each` yields the probabilities to look at.
+        // thresholds of a pass, ascending, as float bits (a threshold at or beyond hi stands for "none")
+        auto uniform = [&](uint32_t (&tb)[SC_WAYS]) {
             const uint32_t stepw = (hi - lo + SC_WAYS) / (SC_WAYS + 1);
+#pragma unroll
+            for (int k = 0; k < SC_WAYS; ++k) {
+                const unsigned long long t = (unsigned long long)lo + (unsigned long long)(k + 1) * stepw;
+                tb[k] = (t < (unsigned long long)hi) ? (uint32_t)t : 0xffffffffu;
+            }
+        };
+        auto decide = [&](const double (&S)[SC_VALS], const uint32_t (&tb)[SC_WAYS], bool count) {      // S: the cluster's (or the list's) sums
+            uint32_t new_lo = lo, new_hi = hi;
+            double new_above = above;
+            double c_lo = S[SC_WAYS], c_hi = 0.0;             // counts above the new bounds
+#pragma unroll
+            for (int k = 0; k < SC_WAYS; ++k) {
+                if (tb[k] < new_hi) {
+                    const double sum = above + S[k];          // mass of p >= t: what lies above hi, plus [t, hi)
+                    if (sum >= (double)tp) { new_lo = tb[k]; c_lo = S[SC_WAYS + 1 + k]; }
+                    else { new_hi = tb[k]; new_above = sum; c_hi = S[SC_WAYS + 1 + k]; }
+                }
+            }
+            lo = new_lo; hi = new_hi; above = new_above;
+            if (count) left = (long long)(c_lo - c_hi);
+        };
+        while (hi - lo > 1u && left > SC_CAND_MAX) {          // (the same trip count in every CTA: the sums are the same)
+            uint32_t tb[SC_WAYS];
             float th[SC_WAYS];
             double sj[SC_VALS];
 #pragma unroll
             for (int k = 0; k < SC_VALS; ++k) sj[k] = 0.0;
+            // while no threshold has held yet, a pass asks at every second power of two below the upper bound (a pass that cuts
+            // the float bits evenly would spend itself on sixteen binades per step, and nearly everything lies in a few)
+            const int e_top = (int)((hi - 1u) >> 23);
+            if (lo == 0u && e_top > 2 * SC_WAYS) {
 #pragma unroll
-            for (int k = 0; k < SC_WAYS; ++k) {
-                const unsigned long long t = (unsigned long long)lo + (unsigned long long)(k + 1) * stepw;
-                th[k] = (t < (unsigned long long)hi) ? __uint_as_float((uint32_t)t) : INFINITY;
+                for (int k = 0; k < SC_WAYS; ++k) tb[k] = (uint32_t)(e_top - 2 * (SC_WAYS - k)) << 23;
+            } else {
+                uniform(tb);
             }
-            const float f_lo = __uint_as_float(lo + stepw), f_hi = __uint_as_float(hi);
+#pragma unroll
+            for (int k = 0; k < SC_WAYS; ++k) th[k] = (tb[k] < hi) ? __uint_as_float(tb[k]) : INFINITY;
+            const float f_lo = __uint_as_float(lo), f_hi = __uint_as_float(hi);
             for (int j = tid; j < n; j += SC_THREADS) {
                 const float p = prob(j);
-                if (p >= f_lo && p < f_hi) {                 // only what lies between the thresholds is summed again
+                if (p >= f_lo && p < f_hi) {
                     const double pd = (double)p;
+                    sj[SC_WAYS] += 1.0;
 #pragma unroll
-                    for (int k = 0; k < SC_WAYS; ++k) if (p >= th[k]) sj[k] += pd;
+                    for (int k = 0; k < SC_WAYS; ++k) if (p >= th[k]) { sj[k] += pd; sj[SC_WAYS + 1 + k] += 1.0; }
                 }
             }
-            sc_block_sum(sh, sj, SC_WAYS);
-            sc_all_gather(sh, parity, rank, sj, SC_WAYS);
-            uint32_t new_lo = lo, new_hi = hi;
-            double new_above = above;
+            sc_block_sum(sh, sj, 2 * SC_WAYS + 1);
+            sc_all_gather(sh, parity, rank, sj, 2 * SC_WAYS + 1);
+            double S[SC_VALS];
 #pragma unroll
-            for (int k = 0; k < SC_WAYS; ++k) {
-                const unsigned long long t = (unsigned long long)lo + (unsigned long long)(k + 1) * stepw;
-                if (t < (unsigned long long)new_hi) {
-                    double sum = above;                       // mass of p >= t: what lies above hi, plus [t, hi)
-                    for (int c = 0; c < SC_CTAS; ++c) sum += sh.gather[parity][c][k];
-                    if (sum >= (double)tp) new_lo = (uint32_t)t; else { new_hi = (uint32_t)t; new_above = sum; }
-                }
+            for (int k = 0; k < SC_VALS; ++k) {
+                S[k] = 0.0;
+                if (k < 2 * SC_WAYS + 1) for (int c = 0; c < SC_CTAS; ++c) S[k] += sh.gather[parity][c][k];
             }
             parity ^= 1;
-            lo = new_lo; hi = new_hi; above = new_above;
+            decide(S, tb, true);
+        }
+        if (hi - lo > 1u) {
+            // ---- few are left: every CTA gets all of them (each CTA's in index order, the CTAs in rank order) ...
+            const float f_lo = __uint_as_float(lo), f_hi = __uint_as_float(hi);
+            int mine_n = 0;
+            for (int j = j0; j < j1; ++j) { const float p = prob(j); mine_n += (p >= f_lo && p < f_hi) ? 1 : 0; }
+            int incl_n = mine_n;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { const int up = __shfl_up_sync(0xffffffffu, incl_n, o); if (lane >= o) incl_n += up; }
+            __syncthreads();
+            if (lane == 31) sh.scan[warp] = incl_n;
+            __syncthreads();
+            int warp_before = 0, cta_n = 0;
+            for (int k = 0; k < SC_WARPS; ++k) { const int t = sh.scan[k]; if (k < warp) warp_before += t; cta_n += t; }
+            mine[0] = (double)cta_n;
+            sc_all_gather(sh, parity, rank, mine, 1);
+            int cta_before_n = 0, total_n = 0;
+            for (int c = 0; c < SC_CTAS; ++c) { const int t = (int)sh.gather[parity][c][0]; if (c < (int)rank) cta_before_n += t; total_n += t; }
+            parity ^= 1;
+            total_n = min(total_n, SC_CAND_MAX);              // (it is at most that: the counts said so)
+            int at = cta_before_n + warp_before + incl_n - mine_n;
+            const unsigned cand_local = (unsigned)__cvta_generic_to_shared(sh.cand);
+            for (int j = j0; j < j1; ++j) {
+                const float p = prob(j);
+                if (p >= f_lo && p < f_hi) {
+                    if (at < SC_CAND_MAX) {
+#pragma unroll
+                        for (unsigned to = 0; to < (unsigned)SC_CTAS; ++to) {
+                            unsigned remote;
+                            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(cand_local + 4u * (unsigned)at), "r"(to));
+                            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(p) : "memory");
+                        }
+                    }
+                    ++at;
+                }
+            }
+            sc_cluster_sync();
+            // ---- ... and finishes the search on the list, with no further exchange
+            while (hi - lo > 1u) {
+                uint32_t tb[SC_WAYS];
+                float th[SC_WAYS];
+                double sj[SC_VALS];
+#pragma unroll
+                for (int k = 0; k < SC_VALS; ++k) sj[k] = 0.0;
+                uniform(tb);
+#pragma unroll
+                for (int k = 0; k < SC_WAYS; ++k) th[k] = (tb[k] < hi) ? __uint_as_float(tb[k]) : INFINITY;
+                const float g_lo = th[0], g_hi = __uint_as_float(hi);
+                for (int j = tid; j < total_n; j += SC_THREADS) {
+                    const float p = sh.cand[j];
+                    if (p >= g_lo && p < g_hi) {
+                        const double pd = (double)p;
+#pragma unroll
+                        for (int k = 0; k < SC_WAYS; ++k) if (p >= th[k]) sj[k] += pd;
+                    }
+                }
+                sc_block_sum(sh, sj, SC_WAYS);
+                decide(sj, tb, false);
+            }
         }
         tau = __uint_as_float(lo);
     }
 
     // ---- mass of the nucleus and the walk in index order: running sums over the threads' chunks, the CTAs in rank order
-    const int chunk = (n + SC_THREADS - 1) / SC_THREADS;
-    const int j0 = min(n, tid * chunk), j1 = min(n, j0 + chunk);
     double my_mass = 0.0;
     for (int j = j0; j < j1; ++j) { const float p = prob(j); if (p >= 0.f && p >= tau) my_mass += (double)p; }
     double incl = my_mass;
@@ -511,13 +594,10 @@ sample_cluster_kernel(const float* __restrict__ logits, long long row_stride, in
     __syncthreads();
     last_member = -1;
     for (int k = 0; k < SC_WARPS; ++k) last_member = max(last_member, sh.warp_i[k]);
-    mine[0] = (double)sh.choice; mine[1] = (double)last_member;
-    sc_all_gather(sh, parity, rank, mine, 2);
-    if (rank == 0 && tid == 0) {
-        int choice = 0x7fffffff, last = -1;
-        for (int c = 0; c < SC_CTAS; ++c) { choice = min(choice, (int)sh.gather[parity][c][0]); last = max(last, (int)sh.gather[parity][c][1]); }
-        out[row] = (choice == 0x7fffffff) ? last : choice;    // rounding left the running sum short of r: the last member
-    }
+    // the CTA in whose range of the running sum r falls writes the token (exactly one does: the ranges tile [0, mass)); should
+    // rounding have left its threads' running sums short of r, its last member
+    if (tid == 0 && cta_before <= r && (r < cta_before + cta_mass || (cta_mass > 0.0 && cta_before + cta_mass >= mass)))
+        out[row] = (sh.choice == 0x7fffffff) ? last_member : sh.choice;
 }
 
 constexpr int SAMPLE_CACHE_LIMIT = 200 * 1024;      // bytes of dynamic shared memory for a row's probabilities
