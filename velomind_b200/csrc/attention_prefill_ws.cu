@@ -206,9 +206,6 @@ attn_prefill_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     __syncthreads();
     ta_fence_after();
     const uint32_t tmem_base = __shfl_sync(0xffffffffu, tmem_slot, 0);
-    // Up to here only the step's own descriptors were read (offsets, positions: uploaded before the step's first kernel).  The
-    // queries and the cache pages are the predecessor's work.
-    vm_pdl_wait();
     volatile int* abort_p = &abort_flag;
     bool ok = !*abort_p;
 
@@ -667,12 +664,10 @@ int ws_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& m
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(units * nc), (unsigned)grid_y); cfg.blockDim = dim3(ws_threads<NT>());
     cfg.dynamicSmemBytes = ws_smem_bytes<NT>(); cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
+    cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = nc; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;      // the set-up may run under the predecessor's tail
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr; cfg.numAttrs = vm_pdl_enabled ? 2 : 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, attn_prefill_ws_kernel<NT>, mq, mk, mv, p);
     if (e != cudaSuccess) return (int)e;
     return vm_launch_status();
