@@ -346,6 +346,45 @@ def test_sampling(V, R):
     assert out.cpu().numpy()[0] == 17
 
 
+@pytest.mark.parametrize("V", [49152, 16000 + 3])
+def test_sampling_rows_that_stress_the_nucleus_search(V):
+    """Rows made for the cluster sampler's search: all logits equal (every token ties with the nucleus' last member, nothing is
+    ever left out of the candidates), two plateaus whose boundary is the threshold, a row so flat that thousands of
+    probabilities stay between the bounds (more than the candidate list holds, so the exchanges go on), a row with one
+    dominant token, a row with a few -inf and NaN logits, a threshold far below the largest probability.  Token for token
+    against the plain sampler."""
+    o = ops()
+    rng = np.random.default_rng(V)
+    rows = []
+    rows.append((np.zeros(V, dtype=np.float32), 1.0, 0.5))
+    two = np.zeros(V, dtype=np.float32); two[: V // 3] = 1.0
+    rows.append((two, 0.9, 0.35))
+    rows.append((two.copy(), 0.9, 0.8))
+    rows.append(((rng.standard_normal(V) * 0.01).astype(np.float32), 1.0, 0.9))
+    rows.append(((rng.standard_normal(V) * 0.01).astype(np.float32), 1.0, 0.999))
+    peak = (rng.standard_normal(V)).astype(np.float32); peak[123] = 30.0
+    rows.append((peak, 0.7, 0.9))
+    holes = (rng.standard_normal(V) * 3).astype(np.float32); holes[5:50] = -np.inf; holes[60:70] = np.nan
+    rows.append((holes, 1.2, 0.97))
+    rows.append(((rng.standard_normal(V) * 6).astype(np.float32), 2.5, 0.9999))
+    R = len(rows)
+    logits = np.stack([r[0] for r in rows])
+    temperature = np.array([r[1] for r in rows], dtype=np.float32)
+    top_p = np.array([r[2] for r in rows], dtype=np.float32)
+    seed = np.arange(100, 100 + R, dtype=np.int64)
+    stream = np.arange(R, dtype=np.int64)
+    dl = torch.from_numpy(logits).to(DEV)
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    for step in range(12):
+        steps = np.full(R, step, dtype=np.int64)
+        o.sample(dl, torch.from_numpy(temperature).to(DEV), torch.from_numpy(top_p).to(DEV), torch.from_numpy(seed).to(DEV),
+                 torch.from_numpy(stream).to(DEV), torch.from_numpy(steps).to(DEV), out)
+        got = out.cpu().numpy()
+        for r in range(R):
+            want = P.sample_top_p(logits[r], float(temperature[r]), float(top_p[r]), P.uniform01(int(seed[r]), int(stream[r]), step))
+            assert got[r] == want, (r, step, int(got[r]), int(want))
+
+
 def test_sampled_distribution():
     o = ops()
     probs = np.array([0.5, 0.25, 0.125, 0.0625, 0.0625], dtype=np.float32)
