@@ -28,7 +28,7 @@ namespace {
 
 enum : int { TC_STORE_BF16 = 0, TC_STORE_F32 = 1, TC_RESIDUAL = 2, TC_SWIGLU = 3, TC_ROPE_KV = 4 };
 
-constexpr int TC_BM = 128, TC_BK = 64;
+constexpr int TC_BM = 128, TC_BK = 64, TC_KPS = 2;
 constexpr int TC_THREADS = 192;
 constexpr uint32_t TC_WAIT_LIMIT = 1u << 20;
 
@@ -104,8 +104,10 @@ template <int BN>
 __global__ void __launch_bounds__(TC_THREADS)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_h, const TcParams p) {
-    constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-    constexpr int STAGES = BN <= 64 ? 4 : 3;
+    // a stage holds TC_KPS k blocks of 64 (each an A tile and a B tile): one barrier round trip of the MMA warp per stage, and
+    // a wait on an mbarrier costs it a few hundred cycles, as much as the four MMAs of one k block take on the tensor cores
+    constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2, STAGE_BYTES = TC_KPS * (A_BYTES + B_BYTES);
+    constexpr int STAGES = 3;
     constexpr uint32_t TMEM_COLS = 2 * BN;                                // two accumulators; a power of two >= 32
     // instruction descriptor: float32 accumulate (bits 4-5 = 1), A and B bf16 (bits 7-9, 10-12 = 1), both K-major,
     // N >> 3 in bits 17-22, M >> 4 in bits 24-28
@@ -119,7 +121,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int half = BN / 2;
-    const int num_kb = (p.K + TC_BK - 1) / TC_BK;
+    const int num_kb = (p.K + TC_BK * TC_KPS - 1) / (TC_BK * TC_KPS);      // stages per tile (a last half-empty one is zero-filled by TMA)
     const int num_tiles = p.tiles_m * p.tiles_n;
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
     const uint32_t accf0 = smem_u32(&bars[2 * STAGES]), acce0 = smem_u32(&bars[2 * STAGES + 2]);
@@ -156,11 +158,15 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     ok = mbar_wait(empty0 + 8 * s, (round & 1u) ^ 1u, abort_p);
                     if (!ok) break;
                     const uint32_t full = full0 + 8 * s;
-                    const uint32_t a_dst = smem_u32(tiles + (size_t)s * STAGE_BYTES), b_dst = a_dst + A_BYTES;
                     mbar_expect_tx(full, STAGE_BYTES);
-                    tma_load_2d(a_dst, &map_a, kb * TC_BK, m0, full);
-                    tma_load_2d(b_dst, &map_b, kb * TC_BK, n0, full);
-                    if (n1 >= 0) tma_load_2d(b_dst + B_BYTES / 2, &map_b, kb * TC_BK, n1, full);   // half a tile each
+#pragma unroll
+                    for (int j = 0; j < TC_KPS; ++j) {
+                        const uint32_t a_dst = smem_u32(tiles + (size_t)s * STAGE_BYTES) + j * (A_BYTES + B_BYTES), b_dst = a_dst + A_BYTES;
+                        const int k0 = (kb * TC_KPS + j) * TC_BK;
+                        tma_load_2d(a_dst, &map_a, k0, m0, full);
+                        tma_load_2d(b_dst, &map_b, k0, n0, full);
+                        if (n1 >= 0) tma_load_2d(b_dst + B_BYTES / 2, &map_b, k0, n1, full);   // half a tile each
+                    }
                 }
             }
             if (*abort_p) {
@@ -190,11 +196,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     ok = mbar_wait(full0 + 8 * s, round & 1u, abort_p);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
-                    const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(b_addr);
 #pragma unroll
-                    for (int k = 0; k < TC_BK / 16; ++k)  // +32 bytes per k step: +2 in the descriptor's 16-byte units
-                        tc_mma_bf16(tmem_d, da + 2 * k, db + 2 * k, IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+                    for (int j = 0; j < TC_KPS; ++j) {
+                        const uint32_t a_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES) + j * (A_BYTES + B_BYTES), b_addr = a_addr + A_BYTES;
+                        const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(b_addr);
+#pragma unroll
+                        for (int k = 0; k < TC_BK / 16; ++k)  // +32 bytes per k step: +2 in the descriptor's 16-byte units
+                            tc_mma_bf16(tmem_d, da + 2 * k, db + 2 * k, IDESC, (kb > 0 || j > 0 || k > 0) ? 1u : 0u);
+                    }
                     tc_commit(empty0 + 8 * s);            // the stage is free once these MMAs have read it
                 }
                 if (ok) tc_commit(accf0 + 8 * a);         // the accumulator is complete once all MMAs are done
@@ -418,8 +427,8 @@ int tc_launch(const void* A, long long lda, const void* W, TcParams p, int tiles
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
             p.tma_residual = 1;
     }
-    constexpr int STAGES = BN <= 64 ? 4 : 3;
-    const size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 4 * 4096 + 128;   // stages, epilogue staging, barriers
+    constexpr int STAGES = 3;
+    const size_t smem = (size_t)STAGES * TC_KPS * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 4 * 4096 + 128;   // stages, epilogue staging, barriers
     static bool configured = false;
     static int num_sms = 0;
     static int per_sm = 1;
