@@ -46,6 +46,7 @@ constexpr int WS_QTILE = WS_BM * 128;                      // bytes of a Q or P 
 constexpr int WS_KVTILE = WS_BN * 128;                     // bytes of a K or V page of one head
 constexpr int WS_RW = WS_D + 4;                            // floats of an exchanged row: sums, maximum, denominator, padding
 constexpr int WS_MAX_NC = 8;
+constexpr int WS_INLINE_SEQS = 16;
 
 struct WsParams {
     const __nv_bfloat16* q; int q_row_stride;
@@ -54,6 +55,8 @@ struct WsParams {
     __nv_bfloat16* out; int H, Hkv, NH;
     float scale_log2, rescale_gap;                         // rescale_gap: how far (in raw scores) the maximum may run ahead
     int window, n_pages; int* err;
+    int n_inline;                                          // > 0: the offsets of cu_tokens ride along in inline_cu (they are shape, known
+    int inline_cu[WS_INLINE_SEQS + 1];                     //      to the host at launch): the walk over the sequences loads nothing
 };
 
 struct WsSlot { int valid, head, t0, n_rows, pos0, blk_lo, blk_hi; };
@@ -142,7 +145,8 @@ attn_prefill_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int G = p.H / p.Hkv, NR = NT / p.NH;
     int unit = (int)blockIdx.x / NC, seq = 0, tok_a = 0, tok_b = 0, n_rt = 0, n_rtg = 0;
     for (; seq < p.B; ++seq) {
-        tok_a = p.cu_tokens[seq]; tok_b = p.cu_tokens[seq + 1];
+        if (p.n_inline > 0) { tok_a = p.inline_cu[seq]; tok_b = p.inline_cu[seq + 1]; }
+        else { tok_a = p.cu_tokens[seq]; tok_b = p.cu_tokens[seq + 1]; }
         n_rt = (tok_b - tok_a + WS_BM - 1) / WS_BM;
         n_rtg = (n_rt + NR - 1) / NR;
         const int units = (n_rtg + 1) / 2;
@@ -714,6 +718,11 @@ VM_API int vm_attention_prefill_ws_bf16(const void* q, int q_row_stride, const v
     p.positions = positions; p.cu_tokens = cu_tokens; p.B = B; p.out = (__nv_bfloat16*)out; p.H = H; p.Hkv = Hkv; p.NH = NH;
     p.scale_log2 = scale * 1.4426950408889634f; p.rescale_gap = 8.0f / p.scale_log2;
     p.window = window; p.n_pages = n_pages; p.err = err;
+    p.n_inline = 0;
+    if (B <= WS_INLINE_SEQS) {
+        p.n_inline = B;
+        for (int b = 0; b <= B; ++b) p.inline_cu[b] = host_cu_tokens[b];
+    }
     int est = max_blocks;                                   // key blocks a pair of tile groups walks, bounded by the table's width
     if (window > 0 && window / WS_BN + 2 < est) est = 2 * (window / WS_BN + 2);
     const int grid_y = Hkv * (G / NH);
