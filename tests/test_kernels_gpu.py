@@ -263,6 +263,15 @@ def test_attention_prefill_warp_specialised(H, Hkv, window, cluster):
     assert np.isfinite(got).all() and np.abs(got - want).max() <= 2e-2
 
 
+def test_attention_prefill_warp_specialised_with_more_sequences_than_its_launch_parameters_hold():
+    """Twenty sequences in one step: the kernel then walks the offsets in device memory instead of its launch parameters."""
+    news = [130, 1, 64, 200, 3, 128, 129, 65, 2, 300, 17, 90, 1, 256, 63, 127, 5, 400, 31, 77]
+    before = [0, 700, 0, 130, 63, 0, 0, 17, 200, 0, 0, 64, 1000, 0, 1, 0, 321, 0, 0, 50]
+    for cluster in (0, 1, 4):
+        got, want = _run_attention("prefill_ws", torch.bfloat16, 6, 2, 64, before, news, 0, groups=cluster, seed=3)
+        assert np.isfinite(got).all() and np.abs(got - want).max() <= 2e-2
+
+
 def test_attention_prefill_warp_specialised_moves_its_reference_maximum():
     """Scores that grow along the keys by far more than the gap the kernel lets its reference maximum lag behind: the rows'
     sums in tensor memory are rescaled several times."""
