@@ -311,6 +311,23 @@ void linear(const void* x, DType x_dtype, long long ldx, const DeviceTensor& W, 
     if (switches().sync) cuda_check(cudaStreamSynchronize(s), "linear");
 }
 
+void linear_residual(const void* x, long long ldx, const DeviceTensor& W, float* h, int T, cudaStream_t s) {
+    if (T <= 0) return;
+    if (W.dtype != DType::BF16) throw KernelError(format("linear_residual: weights kept in %s (bfloat16 only)", dtype_name(W.dtype)));
+    Timed t("linear", s);
+    Blas& b = blas();
+    const int N = static_cast<int>(W.rows()), K = static_cast<int>(W.cols());
+    const float one = 1.f;
+    if (cublasSetStream(b.handle, s) != CUBLAS_STATUS_SUCCESS || cublasSetWorkspace(b.handle, b.workspace->ptr, b.workspace->bytes) != CUBLAS_STATUS_SUCCESS)
+        throw KernelError("linear_residual: the matrix-product library refused the stream");
+    const cublasStatus_t st = cublasGemmEx(b.handle, CUBLAS_OP_T, CUBLAS_OP_N, N, T, K, &one, W.ptr, CUDA_R_16BF, K, x, CUDA_R_16BF, static_cast<int>(ldx), &one, h,
+                                           CUDA_R_32F, N, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT);
+    ++counters().library_calls;
+    if (st != CUBLAS_STATUS_SUCCESS) throw KernelError(format("linear_residual: the matrix-product library reported status %d", static_cast<int>(st)));
+    if (!switches().fail_op.empty() && switches().fail_op == "linear") throw KernelError("linear: injected failure (VELOMIND_B200_FAIL_OP)");
+    if (switches().sync) cuda_check(cudaStreamSynchronize(s), "linear_residual");
+}
+
 // ------------------------------------------------------------------------------------------------ attention
 namespace {
 constexpr int DECODE_COUNTERS = 1 << 16;

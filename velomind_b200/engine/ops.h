@@ -90,6 +90,9 @@ inline void rope_kv_write(void* qkv, const StepContext& ctx, const KVView& kv, c
 // out = x W^T.  x [T, K] (row stride ldx), W [N, K], out [T, N]; a library matrix product, as in the reference
 // (src/cuda/ops/matmul.cu:87-126); float32 runs without any reduced-precision mode.
 void linear(const void* x, DType x_dtype, long long ldx, const DeviceTensor& W, void* out, DType out_dtype, int T, cudaStream_t s);
+// h[T, N] += x W^T with the float32 residual stream h as the product's own accumulator (x and W bfloat16): the sum happens in
+// the library's float32 epilogue, and the kernel after it reads h alone.
+void linear_residual(const void* x, long long ldx, const DeviceTensor& W, float* h, int T, cudaStream_t s);
 
 // attention of the step's tokens over the cache; picks the kernel for the step's shape and dtype
 void attention(StepContext& ctx, const void* q, int q_row_stride, const KVView& kv, void* out, int H, int Hkv, int D, float scale, int window);

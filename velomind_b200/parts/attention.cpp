@@ -51,26 +51,46 @@ public:
     }
 
     // True if this step can run as: [norm +] qkv + rotary + cache write -> attention -> out + residual, with the
-    // weight-streaming kernels (few tokens) or the tensor-core kernels (many tokens).
+    // weight-streaming kernels (few tokens), the tensor-core kernels (many tokens, when asked for) or the library products
+    // (the out projection then adds into the residual stream as its own accumulator).
     bool can_fuse(const StepContext& ctx, const Norm& norm) const override {
         const float* nw;
         float eps;
         if (!norm.as_rms(&nw, &eps) || ctx.act_dtype != DType::BF16) return false;
         if (qkv_.weight.dtype != DType::BF16 || out_.weight.dtype != DType::BF16) return false;
-        if (!(rotary_.rotary_dim == 0 || (rotary_.rotary_dim == D_ && rotary_.pairing == VM_PAIR_HALF_SPLIT))) return false;
         if (hidden_ % 8 || (H_ * D_) % 8) return false;
+        const bool fused_rotary = rotary_.rotary_dim == 0 || (rotary_.rotary_dim == D_ && rotary_.pairing == VM_PAIR_HALF_SPLIT);
+        if (!fused_rotary) return ctx.T_cap > ops::SKINNY_MAX_ROWS;      // (the library path rotates with the kernel of its own)
         if (ctx.T_cap <= ops::SKINNY_MAX_ROWS) return hidden_ % 32 == 0 && (H_ * D_) % 32 == 0 && D_ % 16 == 0;
-        return ops::tc_fused_rows(ctx) && (D_ == 64 || D_ == 128);
+        return true;
     }
 
-    // h += attention(norm(h)): three or four launches.
+    // h += attention(norm(h)): three or four launches, five on the library path.
     void forward_fused(StepContext& ctx, float* h, Norm& norm) override {
         const float* nw = nullptr;
         float eps = 0.f;
         norm.as_rms(&nw, &eps);
-        void* q = ctx.take_tokens(static_cast<long long>(H_) * D_, DType::BF16);
         const KVView kv = ctx.kv();
         const bool skinny = ctx.T_cap <= ops::SKINNY_MAX_ROWS;
+        const bool fused_rotary = rotary_.rotary_dim == 0 || (rotary_.rotary_dim == D_ && rotary_.pairing == VM_PAIR_HALF_SPLIT);
+        const bool tc = !skinny && fused_rotary && ops::tc_fused_rows(ctx) && (D_ == 64 || D_ == 128);
+        if (!skinny && !tc) {
+            // the library's products: norm, q k v, rotary + cache write, attention, out added into h by the product itself
+            const long long width = static_cast<long long>(H_ + 2 * Hkv_) * D_;
+            void* x = ctx.take_tokens(hidden_, DType::BF16);
+            norm.forward(ctx, h, nullptr, x, nullptr, 0);
+            void* qkv = ctx.take_tokens(width, DType::BF16);
+            ops::linear(x, DType::BF16, hidden_, qkv_.weight, qkv, DType::BF16, ctx.T, ctx.stream);
+            ctx.give(x);
+            ops::rope_kv_write(qkv, ctx, kv, rotary_, H_, Hkv_, D_, DType::BF16);
+            void* att = ctx.take_tokens(static_cast<long long>(H_) * D_, DType::BF16);
+            ops::attention(ctx, qkv, static_cast<int>(width), kv, att, H_, Hkv_, D_, scale_, window_);
+            ctx.give(qkv);
+            ops::linear_residual(att, static_cast<long long>(H_) * D_, out_.weight, h, ctx.T, ctx.stream);
+            ctx.give(att);
+            return;
+        }
+        void* q = ctx.take_tokens(static_cast<long long>(H_) * D_, DType::BF16);
         if (skinny && ctx.T_cap <= ops::SKINNY_NORM_ROWS) {
             ops::skinny_qkv_rope(h, nw, eps, qkv_.weight, q, ctx, kv, rotary_, H_, Hkv_, D_);
         } else {

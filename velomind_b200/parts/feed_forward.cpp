@@ -31,7 +31,7 @@ public:
         if (!norm.as_rms(&nw, &eps) || ctx.act_dtype != DType::BF16) return false;
         if (gate_up_.weight.dtype != DType::BF16 || down_.weight.dtype != DType::BF16) return false;
         if (ctx.T_cap <= ops::SKINNY_MAX_ROWS) return hidden_ % 32 == 0 && I_ % 32 == 0;
-        return ops::tc_fused_rows(ctx) && hidden_ % 8 == 0 && I_ % 64 == 0;
+        return hidden_ % 8 == 0 && I_ % 8 == 0;
     }
 
     // h += down(silu(gate(norm(h))) * up(norm(h))): two or three launches.
@@ -39,8 +39,23 @@ public:
         const float* nw = nullptr;
         float eps = 0.f;
         norm.as_rms(&nw, &eps);
-        void* act = ctx.take_tokens(I_, DType::BF16);
         const bool skinny = ctx.T_cap <= ops::SKINNY_MAX_ROWS;
+        const bool tc = !skinny && ops::tc_fused_rows(ctx) && I_ % 64 == 0;
+        if (!skinny && !tc) {
+            // the library's products: norm, gate and up, SwiGLU, down added into h by the product itself
+            void* x = ctx.take_tokens(hidden_, DType::BF16);
+            norm.forward(ctx, h, nullptr, x, nullptr, 0);
+            void* gu = ctx.take_tokens(2ll * I_, DType::BF16);
+            ops::linear(x, DType::BF16, hidden_, gate_up_.weight, gu, DType::BF16, ctx.T, ctx.stream);
+            ctx.give(x);
+            void* a = ctx.take_tokens(I_, DType::BF16);
+            ops::swiglu(gu, a, ctx.T, I_, DType::BF16, ctx.stream);
+            ctx.give(gu);
+            ops::linear_residual(a, I_, down_.weight, h, ctx.T, ctx.stream);
+            ctx.give(a);
+            return;
+        }
+        void* act = ctx.take_tokens(I_, DType::BF16);
         if (skinny && ctx.T_cap <= ops::SKINNY_NORM_ROWS) {
             ops::skinny_swiglu(h, nw, eps, gate_up_.weight, ctx.T, I_, act, ctx.stream);
         } else {
