@@ -135,6 +135,15 @@ def test_prompts_of_thousands_of_tokens_take_the_warp_specialised_attention(tmp_
     scale = max(1.0, max(float(np.abs(v).max()) for v in want.values()))
     per_step = {k: round(float(np.abs(got[k] - want[k]).max()) / scale, 4) for k in want}
     assert max(per_step.values()) <= TOL["bfloat16"], per_step
+    # the same steps twice more: their prompt shapes come a second and a third time, so the last run replays them from graphs
+    recorded = engine.graphs_captured
+    for again in range(2):
+        got = S.run_steps_in_process(engine, steps)
+        engine.raise_if_error()
+        per_step = {k: round(float(np.abs(got[k] - want[k]).max()) / scale, 4) for k in want}
+        assert max(per_step.values()) <= TOL["bfloat16"], (again, per_step)
+    assert engine.graphs_captured >= recorded + 3          # the three prompt shapes
+    assert engine.cache.slots.held_count == 0 and engine.cache.tokens_held() == 0
 
 
 def test_the_last_places_of_the_longest_context_and_the_refusal_beyond(tmp_path):
