@@ -653,13 +653,26 @@ int ws_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& m
     }
     int nc = groups;
     if (nc <= 0) {
-        // as many CTAs per cluster as make the step shortest: waves of clusters times the blocks a CTA walks (plus what a
-        // pass costs besides its blocks, in blocks)
+        // As many CTAs per cluster as make the step shortest, in key blocks of one CTA (about 1.75 us each, measured): waves of
+        // clusters times what a CTA walks plus what it pays once.  A lone CTA walks its pair of tile groups one after the other
+        // and pays 3 (set-up, two pipeline fills); the CTAs of a cluster are dealt out to the two groups as the kernel does it
+        // (the pair with the most uneven groups decides: `est_blocks` against 2) and pay 10 (launch of a cluster, set-up,
+        // fill, the exchange of rows with its two barriers).
         double best = 0;
         for (int c = 1; c <= WS_MAX_NC; ++c) {
             const long long active = ws_active_clusters<NT>(c);
             const long long waves = (units * grid_y + active - 1) / active;
-            const double cost = (double)waves * ((est_blocks + c - 1) / c + 2.0 + 0.25 * c);
+            double blocks, fixed;
+            if (c == 1) { blocks = est_blocks + 2; fixed = 3; }
+            else {
+                int nb = (c * 2 + (est_blocks + 2) / 2) / (est_blocks + 2);
+                nb = nb < 1 ? 1 : (nb > c - 1 ? c - 1 : nb);
+                const int na = c - nb;
+                blocks = (est_blocks + na - 1) / na;
+                if ((2 + nb - 1) / nb > blocks) blocks = (2 + nb - 1) / nb;
+                fixed = 10;
+            }
+            const double cost = (double)waves * (fixed + blocks);
             if (nc <= 0 || cost < best) { best = cost; nc = c; }
         }
     }

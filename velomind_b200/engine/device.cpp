@@ -384,12 +384,11 @@ void attention(StepContext& ctx, const void* q, int q_row_stride, const KVView& 
             tiles128 += (n + 127) / 128;
             tiles64 += (n + 63) / 64;
         }
-        const int group = H / Hkv;                          // query heads per kv head: the warp-specialised kernel gives a CTA two or three of them
-        if (D == 64 && most_blocks >= WS_ATTENTION_MIN_BLOCKS && (group % 3 == 0 || group % 2 == 0) && ctx.err != nullptr) {
+        if (D == 64 && most_blocks >= WS_ATTENTION_MIN_BLOCKS && ctx.err != nullptr) {
             // the longest prompts: softmax warps, a copy warp and product warps, clusters dealt out to pairs of tile groups
             // (measured, 9 heads: 4,096 tokens 78 us against 88 us for the kernel below, 8,192: 224 / 262; 2,048: 32 / 33;
             //  2,560: 37 / 48, 3,072: 51 / 58, 1,536: 27 / 24, 1,024: 22 / 18: every CTA pays for its set-up and its cluster's exchange once, whatever its share of the keys;
-            //  with one query head per kv head a CTA takes three row tiles of the head instead, which gains nothing: 32 heads, 4,096 tokens 243 / 234 us)
+            //  with one query head per kv head a CTA takes three row tiles of the head: 32 heads, 2,048 tokens 70 / 80 us, 3,072: 88 / 148)
             ++counters().tc_attention_calls;
             Timed t("attention_prefill_ws_bf16", s);
             check(vm_attention_prefill_ws_bf16(q, q_row_stride, kv.k_pages, kv.v_pages, kv.block_table, kv.table_width, ctx.positions, ctx.cu_tokens,
