@@ -273,6 +273,16 @@ namespace {
 struct Blas {
     cublasHandle_t handle = nullptr;
     std::unique_ptr<DeviceBuffer> workspace;
+    cudaStream_t stream = nullptr;        // the stream the handle was last given (with the workspace, which a new stream resets)
+    bool bound = false;
+    // The handle's stream and scratch are set when they change, not per product: a step multiplies a hundred times and more on one stream.
+    void bind(cudaStream_t s, const char* who) {
+        if (bound && stream == s) return;
+        if (cublasSetStream(handle, s) != CUBLAS_STATUS_SUCCESS || cublasSetWorkspace(handle, workspace->ptr, workspace->bytes) != CUBLAS_STATUS_SUCCESS)
+            throw KernelError(std::string(who) + ": the matrix-product library refused the stream");
+        stream = s;
+        bound = true;
+    }
 };
 Blas& blas() {
     static Blas per_device[64];
@@ -300,8 +310,7 @@ void linear(const void* x, DType x_dtype, long long ldx, const DeviceTensor& W, 
     const cudaDataType_t in_t = x_dtype == DType::F32 ? CUDA_R_32F : CUDA_R_16BF;
     const cudaDataType_t out_t = out_dtype == DType::F32 ? CUDA_R_32F : CUDA_R_16BF;
     const float one = 1.f, zero = 0.f;
-    if (cublasSetStream(b.handle, s) != CUBLAS_STATUS_SUCCESS || cublasSetWorkspace(b.handle, b.workspace->ptr, b.workspace->bytes) != CUBLAS_STATUS_SUCCESS)
-        throw KernelError("linear: the matrix-product library refused the stream");
+    b.bind(s, "linear");
     // row-major out[T, N] = x[T, K] W[N, K]^T  is  column-major out^T[N, T] = W^T(K x N)^T x^T(K x T)
     const cublasStatus_t st = cublasGemmEx(b.handle, CUBLAS_OP_T, CUBLAS_OP_N, N, T, K, &one, W.ptr, in_t, K, x, in_t, static_cast<int>(ldx), &zero, out,
                                            out_t, N, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT);
@@ -318,8 +327,7 @@ void linear_residual(const void* x, long long ldx, const DeviceTensor& W, float*
     Blas& b = blas();
     const int N = static_cast<int>(W.rows()), K = static_cast<int>(W.cols());
     const float one = 1.f;
-    if (cublasSetStream(b.handle, s) != CUBLAS_STATUS_SUCCESS || cublasSetWorkspace(b.handle, b.workspace->ptr, b.workspace->bytes) != CUBLAS_STATUS_SUCCESS)
-        throw KernelError("linear_residual: the matrix-product library refused the stream");
+    b.bind(s, "linear_residual");
     const cublasStatus_t st = cublasGemmEx(b.handle, CUBLAS_OP_T, CUBLAS_OP_N, N, T, K, &one, W.ptr, CUDA_R_16BF, K, x, CUDA_R_16BF, static_cast<int>(ldx), &one, h,
                                            CUDA_R_32F, N, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT);
     ++counters().library_calls;
