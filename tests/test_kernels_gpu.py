@@ -272,6 +272,53 @@ def test_attention_prefill_warp_specialised_with_more_sequences_than_its_launch_
         assert np.isfinite(got).all() and np.abs(got - want).max() <= 2e-2
 
 
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_attention_prefill_warp_specialised_at_random_shapes(seed):
+    """Forty random steps per seed (heads and groups, one to five sequences of new and cached tokens of any length, windows,
+    table widths beyond the need, every cluster size) against the generic kernel in float32 on the same bfloat16 inputs; the
+    generic kernel is itself compared with the plain implementation in test_attention_generic."""
+    o = ops()
+    rng = np.random.default_rng(seed)
+    for case in range(40):
+        Hkv = int(rng.integers(1, 5)); G = int(rng.choice([1, 2, 3, 4, 6])); H = Hkv * G; D = 64
+        B = int(rng.integers(1, 6))
+        news = [int(rng.integers(1, 900)) for _ in range(B)]
+        if rng.random() < 0.3:
+            news[0] = int(rng.integers(900, 2600))
+        before = [int(rng.integers(0, 1500)) if rng.random() < 0.4 else 0 for _ in range(B)]
+        window = int(rng.choice([0, 0, 0, 64, 70, 300, 1000]))
+        cluster = int(rng.choice([0, 0, 1, 2, 3, 4, 5, 6, 7, 8]))
+        lens = [a + n for a, n in zip(before, news)]
+        n_pages = sum(-(-L // 64) for L in lens) + 2
+        width = max(-(-L // 64) for L in lens) + int(rng.integers(0, 3))
+        perm = rng.permutation(n_pages)
+        table = np.full((B, width), -1, dtype=np.int32)
+        k = 0
+        for s_, L in enumerate(lens):
+            for b in range(-(-L // 64)):
+                table[s_, b] = perm[k]; k += 1
+        g = _gen(1000 * seed + case)
+        kp = torch.randn(n_pages, Hkv, 64, D, generator=g).to(torch.bfloat16).to(DEV)
+        vp = torch.randn(n_pages, Hkv, 64, D, generator=g).to(torch.bfloat16).to(DEV)
+        T = sum(news)
+        stride = (H + 2 * Hkv) * D
+        qkv = (torch.randn(T, stride, generator=g) * (1.0 + 2.0 * rng.random())).to(torch.bfloat16).to(DEV)
+        positions = torch.cat([torch.arange(a, a + n) for a, n in zip(before, news)]).int().to(DEV)
+        seq = torch.cat([torch.full((n,), s_) for s_, n in enumerate(news)]).int().to(DEV)
+        cu = torch.tensor([0] + list(np.cumsum(news)), dtype=torch.int32)
+        tb = torch.from_numpy(table).to(DEV)
+        scale = 1.0 / math.sqrt(D)
+        err = torch.zeros(1, dtype=torch.int32, device=DEV)
+        out = torch.full((T, H * D), float("nan"), dtype=torch.bfloat16, device=DEV)
+        o.attention_prefill_ws_bf16(qkv, stride, kp, vp, tb, positions, cu.to(DEV), cu.tolist(), out, H, Hkv, D, scale, window, err, cluster)
+        ref = torch.full((T, H * D), float("nan"), dtype=torch.float32, device=DEV)
+        o.attention_generic(qkv.float(), stride, kp.float(), vp.float(), tb, positions, seq, ref, H, Hkv, D, scale, window, err)
+        what = (case, H, Hkv, news, before, window, cluster)
+        assert int(err.item()) == 0, what
+        assert torch.isfinite(out.float()).all(), what
+        assert float((out.float() - ref).abs().max()) <= 3e-2, what
+
+
 def test_attention_prefill_warp_specialised_moves_its_reference_maximum():
     """Scores that grow along the keys by far more than the gap the kernel lets its reference maximum lag behind: the rows'
     sums in tensor memory are rescaled several times."""
