@@ -259,6 +259,42 @@ def test_greedy_decode_tokens_are_near_argmax_of_plain(model_folders, name):
     assert engine.cache.slots.held_count == 0
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_first_step_of_a_shape_while_the_default_stream_is_busy(model_folders, dtype):
+    """The engine works on a stream that does not wait for the default stream.  What it prepares at the first step of a new
+    shape (the step's descriptors on the device, cleared when they are made) must be ready before the step's own copies and
+    kernels run, whatever else the process has queued on the default stream: here a few milliseconds of clearing a large
+    tensor are queued right before every first step of a shape, and each step's logits are compared with the plain model."""
+    folder = model_folders["tiny_c"]
+    requests = S.make_requests(CONFIGS["tiny_c"]["vocab_size"], (300, 57, 130), seed=71)
+    plain = S.plain_logits(folder, requests)
+    engine = _engine(folder, dtype, max_tokens=64 * 16)
+    big = torch.empty(3 << 30, dtype=torch.uint8, device="cuda:0")
+    tol = TOL[dtype]
+    scale = max(1.0, max(float(np.abs(v).max()) for v in plain.values()))
+    slots = {rid: engine.open() for rid in requests}
+    import velomind_b200 as vm
+    done = {rid: 0 for rid in requests}
+    # steps of shapes the engine has not seen: three prompts cut at different places, then single tokens
+    for cut in ((100, 57, 30), (150, 0, 60), (49, 0, 39), (1, 0, 1)):
+        entries, wants = [], []
+        for rid, n in zip(requests, cut):
+            if n == 0:
+                continue
+            a = done[rid]
+            entries.append(vm.Entry(slots[rid], requests[rid][a:a + n], [0, n - 1] if n > 1 else [0]))
+            wants += [(rid, a), (rid, a + n - 1)] if n > 1 else [(rid, a)]
+            done[rid] = a + n
+        for _ in range(6):
+            big.zero_()                              # a few milliseconds of work on the default stream, still running ...
+        got = engine.step(entries).float().cpu().numpy()      # ... while this step's descriptors are made, copied and used
+        for row, (rid, place) in zip(got, wants):
+            assert np.abs(row - plain[rid][place]).max() <= tol * scale, (cut, rid, place)
+    for s in slots.values():
+        engine.close(s)
+    engine.raise_if_error()
+
+
 def test_long_prompt_takes_the_tcgen05_attention(model_folders):
     """A prompt long enough for the tensor-memory attention kernel (head size 64, more than 1,280 keys), alone and next
     to a short one, then a few tokens one by one; logits at places spread over the prompt against the plain model."""

@@ -116,6 +116,9 @@ void* Workspace::take(size_t bytes) {
         p = static_cast<char*>(arena_->ptr) + plan.offsets[idx];
     }
     live_[p] = Live{idx, bytes};
+    // (debugging aid, with the poisoning of freed buffers: a buffer starts as NaN too, so that a kernel which leaves part of its
+    //  output unwritten shows in the step's result whatever the memory held before)
+    if (poison && bytes) ops::cuda_check(cudaMemsetAsync(p, 0xff, bytes, stream_), "poisoning a fresh buffer");
     return p;
 }
 

@@ -15,10 +15,28 @@ void cuda_check(cudaError_t e, const char* what) {
 }
 }  // namespace ops
 
+namespace {
+// The stream that clears new buffers, one per device.  A buffer must be clear BEFORE its constructor returns: the engine's
+// streams are non-blocking, so nothing orders their work after a clearing put on the default stream, and a late clearing would
+// wipe what a step has meanwhile copied into the buffer (a bucket's first descriptors, for one).
+cudaStream_t clearing_stream() {
+    static cudaStream_t per_device[64] = {};
+    int dev = 0;
+    ops::cuda_check(cudaGetDevice(&dev), "asking for the current device");
+    cudaStream_t& s = per_device[dev < 0 || dev >= 64 ? 0 : dev];
+    if (!s) ops::cuda_check(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking), "creating the stream that clears new buffers");
+    return s;
+}
+}  // namespace
+
 DeviceBuffer::DeviceBuffer(size_t n, bool zero) : bytes(n) {
     if (n == 0) return;
     ops::cuda_check(cudaMalloc(&ptr, n), "allocating device memory");
-    if (zero) ops::cuda_check(cudaMemset(ptr, 0, n), "clearing device memory");
+    if (zero) {
+        cudaStream_t s = clearing_stream();
+        ops::cuda_check(cudaMemsetAsync(ptr, 0, n, s), "clearing device memory");
+        ops::cuda_check(cudaStreamSynchronize(s), "clearing device memory");
+    }
 }
 
 DeviceBuffer::~DeviceBuffer() {
