@@ -52,6 +52,27 @@ def test_cuts_match_plain(model_folders, name, dtype, cut):
     assert engine.cache.slots.held_count == 0 and engine.cache.tokens_held() == 0
 
 
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c"])
+@pytest.mark.parametrize("cut", ["tail", "batches"])
+def test_cuts_match_plain_through_the_kernel_for_large_matrices(model_folders, name, cut):
+    """Steps of up to 32 rows multiply with one of two weight-streaming kernels, chosen by the size of the weight matrix; the
+    tiny models never reach the one for large matrices by themselves, so it is forced here (every product of such a step
+    and the head), and the logits of every step are compared with the plain model as above."""
+    from velomind_b200.kernels import ops
+    folder = model_folders[name]
+    requests = S.make_requests(CONFIGS[name]["vocab_size"], LENGTHS, seed=13)
+    plain = S.plain_logits(folder, requests)
+    steps = {"tail": S.steps_tail_one_by_one, "batches": S.steps_unequal_batches}[cut](requests)
+    ops.skinny_variant(2)
+    try:
+        engine = _engine(folder, "bfloat16", max_tokens=64 * 8, max_slots=3)
+        got = S.run_steps_in_process(engine, steps)
+        engine.raise_if_error()
+    finally:
+        ops.skinny_variant(0)
+    _compare(got, S.expected_rows(steps, requests, plain), TOL["bfloat16"])
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_poisoned_scratch_changes_nothing(model_folders, dtype):
     """`poison_freed`: every scratch buffer is filled with NaN the moment a part gives it back (in stream order, also

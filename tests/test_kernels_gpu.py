@@ -467,37 +467,58 @@ def _rms_ref(h, w, eps):
     return _bf(torch.from_numpy(P.rmsnorm(h.numpy(), w.numpy(), eps)))
 
 
-@pytest.mark.parametrize("M", [1, 8, 17, 64])
-@pytest.mark.parametrize("N,K", [(72, 64), (576, 576), (200, 160), (576, 1536), (4752, 96), (3000, 1056)])   # (the last two: CTAs take several column tiles)
-def test_skinny_linear(M, N, K):
+@pytest.fixture(params=["register-fed", "ring"])
+def skinny_kernel(request):
+    """Both weight-streaming kernels, forced: the one that fetches weights into registers (what small matrices take) and the
+    one that streams them through a ring in shared memory (large matrices, at most 32 rows)."""
     o = ops()
+    o.skinny_variant(1 if request.param == "register-fed" else 2)
+    yield request.param
+    o.skinny_variant(0)
+
+
+def _ring_takes(kernel, M):
+    if kernel == "ring" and M > 32:
+        pytest.skip("the ring kernel takes at most 32 rows")
+
+
+@pytest.mark.parametrize("M", [1, 8, 17, 64])
+@pytest.mark.parametrize("N,K", [(72, 64), (576, 576), (200, 160), (576, 1536), (4752, 96), (3000, 1056), (5200, 2080)])   # (the last three: CTAs take several column tiles)
+def test_skinny_linear(M, N, K, skinny_kernel):
+    _ring_takes(skinny_kernel, M)
+    o = ops()
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
     x = _bf(torch.randn(M, K, generator=_gen(M + N)))
     w = _bf(torch.randn(N, K, generator=_gen(K)) * 0.1)
     want = x.float() @ w.float().t()
     tol = 2e-2 * float(want.abs().max())
     out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
-    o.skinny_linear(x.to(DEV), None, w.to(DEV), out)
+    o.skinny_linear(x.to(DEV), None, w.to(DEV), out, err=err)
     assert (out.float().cpu() - want).abs().max() <= tol
     out32 = torch.full((M, N + 3), float("nan"), device=DEV)                 # a strided float32 output (logits)
-    o.skinny_linear(x.to(DEV), None, w.to(DEV), out32[:, :N])
+    o.skinny_linear(x.to(DEV), None, w.to(DEV), out32[:, :N], err=err)
     assert (out32[:, :N].cpu() - want).abs().max() <= 1e-3 * max(1.0, float(want.abs().max()))
     assert torch.isnan(out32[:, N:]).all()
     h = torch.randn(M, N, generator=_gen(5))
     hd = h.to(DEV)
-    o.skinny_linear(x.to(DEV), None, w.to(DEV), None, residual=hd)
+    o.skinny_linear(x.to(DEV), None, w.to(DEV), None, residual=hd, err=err)
     assert (hd.cpu() - (h + want)).abs().max() <= 1e-3 * max(1.0, float(want.abs().max()))
     # the norm as prologue
     hres = torch.randn(M, K, generator=_gen(6)) * 2
     nw = 1 + 0.1 * torch.randn(K, generator=_gen(7))
     xn = _rms_ref(hres, nw, 1e-5)
     want_n = xn.float() @ w.float().t()
-    o.skinny_linear(hres.to(DEV), (nw.to(DEV), 1e-5), w.to(DEV), out)
+    o.skinny_linear(hres.to(DEV), (nw.to(DEV), 1e-5), w.to(DEV), out, err=err)
     assert (out.float().cpu() - want_n).abs().max() <= 2e-2 * float(want_n.abs().max())
+    assert int(err.item()) == 0
 
 
-@pytest.mark.parametrize("M,I,K", [(3, 192, 64), (8, 1536, 576), (33, 160, 96), (64, 1000, 1536), (5, 5000, 96), (20, 2000, 1088)])
-def test_skinny_swiglu(M, I, K):
+@pytest.mark.parametrize("M,I,K", [(3, 192, 64), (8, 1536, 576), (33, 160, 96), (64, 1000, 1536), (5, 5000, 96), (20, 2000, 1088), (16, 3000, 3104),
+                                   (32, 2504, 1024)])
+def test_skinny_swiglu(M, I, K, skinny_kernel):
+    _ring_takes(skinny_kernel, M)
     o = ops()
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
     hres = torch.randn(M, K, generator=_gen(M)) * 2
     nw = 1 + 0.1 * torch.randn(K, generator=_gen(I))
     w = _bf(torch.randn(2 * I, K, generator=_gen(K)) * 0.2)
@@ -505,15 +526,16 @@ def test_skinny_swiglu(M, I, K):
     gu = xn.float() @ w.float().t()
     want = torch.from_numpy(P.swiglu(gu[:, :I].numpy(), gu[:, I:].numpy()))
     out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
-    o.skinny_swiglu(hres.to(DEV), (nw.to(DEV), 1e-6), w.to(DEV), out)
+    o.skinny_swiglu(hres.to(DEV), (nw.to(DEV), 1e-6), w.to(DEV), out, err=err)
     assert (out.float().cpu() - want).abs().max() <= 2e-2 * float(want.abs().max())
-    o.skinny_swiglu(xn.to(DEV), None, w.to(DEV), out)
+    o.skinny_swiglu(xn.to(DEV), None, w.to(DEV), out, err=err)
     assert (out.float().cpu() - want).abs().max() <= 2e-2 * float(want.abs().max())
+    assert int(err.item()) == 0
 
 
 @pytest.mark.parametrize("H,Hkv,D,K,rot", [(4, 2, 16, 64, 16), (3, 1, 32, 96, 32), (9, 3, 64, 576, 64), (5, 5, 48, 160, 0), (2, 1, 128, 256, 128),
-                                           (40, 8, 64, 96, 64)])                # (the last: CTAs take several column tiles)
-def test_skinny_qkv_rope(H, Hkv, D, K, rot):
+                                           (40, 8, 64, 96, 64), (32, 32, 64, 2048, 64)])   # (the last two: CTAs take several column tiles)
+def test_skinny_qkv_rope(H, Hkv, D, K, rot, skinny_kernel):
     o = ops()
     lens_before, new = [3, 70, 0], [5, 1, 20]
     T = sum(new)

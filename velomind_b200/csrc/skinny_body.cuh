@@ -29,6 +29,7 @@ struct SkinnyParams {
     int n_items;                 // work items of the launch (a CTA takes items blockIdx.x, + gridDim.x, ...)
     int kc;                      // k chunk staged in shared memory at a time (multiple of 32)
     int row_bytes;               // shared-memory row pitch of the A tile, == 64 mod 128
+    int stages;                  // (skinny_stream_kernel) stages of its ring of weight rows
 };
 
 // `item` is the work item (what item_index is for the stand-alone kernel); `smem` the CTA's dynamic shared memory.

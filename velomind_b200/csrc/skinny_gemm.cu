@@ -21,9 +21,13 @@
 // it waits for its predecessor; the rope_kv form lets ITS successor, the decode attention, start only after that wait
 // (common.cuh says why).
 //
+// Products that read many megabytes of weights for at most 32 rows take skinny_stream_kernel (skinny_stream.cuh): the same
+// work items and epilogues, the weights streamed through shared memory by a warp of their own.
+//
 // Sizes: K % 32 == 0, N % 8 == 0 (16 for the two-tile forms), head size % 16 == 0, I % 8 == 0; M <= 64.
 // Anything else is refused with VM_ERR_UNSUPPORTED and the caller uses the library product.
 #include "skinny_body.cuh"
+#include "skinny_stream.cuh"
 
 namespace {
 
@@ -126,30 +130,59 @@ int skinny_launch(SkinnyParams p, int grid, cudaStream_t stream) {
     return vm_launch_status();
 }
 
+// Which kernel takes a product of `items` work items: the streaming one when the weights are large enough for memory
+// bandwidth, not one chain of latencies, to set the time (measured at hidden sizes 960 and 2,048 against 576), or when
+// vm_skinny_variant() asks for it.
+int skinny_variant = 0;
+constexpr long long STREAM_MIN_WEIGHT_BYTES = 9ll << 20;
+
+int skinny_dispatch(SkinnyParams p, int items, cudaStream_t stream) {
+    const long long weight_bytes = (long long)p.N * p.K * 2;
+    if (skinny_variant >= 2 || (skinny_variant == 0 && p.M <= 32 && weight_bytes >= STREAM_MIN_WEIGHT_BYTES)) {
+        const int rc = skinny_stream_launch(p, items, stream, skinny_variant == 3);
+        if (rc != VM_ERR_UNSUPPORTED || skinny_variant >= 2) return rc;
+    }
+    return skinny_launch(p, items, stream);
+}
+
 }  // namespace
+
+// 0: the launchers choose between the two weight-streaming kernels by size; 1: always skinny_gemm_kernel; 2: always
+// skinny_stream_kernel (VM_ERR_UNSUPPORTED where it does not take the sizes).  For tests and measurements.
+VM_API void vm_skinny_variant(int variant) { skinny_variant = variant; }
 
 // out = A W^T (pro 0) or rmsnorm(h) W^T (pro 1); out bf16 (out_f32 0) or float32 (1); or h += ... (residual 1).
 VM_API int vm_skinny_linear(const void* A, int pro, const float* norm_w, float eps, const void* W, int M, int N, int K,
-                            void* out, int out_stride, int out_f32, float* residual_h, cudaStream_t stream) {
+                            void* out, int out_stride, int out_f32, float* residual_h, int* err, cudaStream_t stream) {
     if (N % 8 != 0) return VM_ERR_UNSUPPORTED;
     SkinnyParams p{};
+    p.err = err;
     p.A = A; p.pro = pro; p.norm_w = norm_w; p.eps = eps; p.W = (const __nv_bfloat16*)W; p.M = M; p.N = N; p.K = K;
     p.out = out; p.out_stride = out_stride; p.h = residual_h;
     p.epi = residual_h ? EPI_RESIDUAL : (out_f32 ? EPI_STORE_F32 : EPI_STORE_BF16);
-    if (pro == PRO_NONE && !residual_h && N >= 4096 && (size_t)((M + 15) / 16 * 16) * (K * 2 + 128) <= 200 * 1024)
-        return skinny_wide_launch(p, stream);               // many columns: warps split N, not K
     p.tiles = (N % 16 == 0 && N / 16 >= 148) ? 2 : 1;
-    return skinny_launch(p, p.tiles == 2 ? N / 16 : N / 8, stream);
+    const int items = p.tiles == 2 ? N / 16 : N / 8;
+    if (skinny_variant < 2 && pro == PRO_NONE && !residual_h && N >= 4096 && (size_t)((M + 15) / 16 * 16) * (K * 2 + 128) <= 200 * 1024) {
+        // many columns (the vocabulary head): warps split N, not K; from K = 768 on the ring kernel is faster (49,152 columns,
+        // 8 rows, K = 576 / 960 / 2,048: 13.0 / 20.7 / 48.5 us against 16.3 / 18.6 / 32.6 us)
+        if (skinny_variant == 0 && M <= 32 && K >= 768) {
+            const int rc = skinny_stream_launch(p, items, stream);
+            if (rc != VM_ERR_UNSUPPORTED) return rc;
+        }
+        return skinny_wide_launch(p, stream);
+    }
+    return skinny_dispatch(p, items, stream);
 }
 
 // out[M, I] = silu(x Wg^T) * (x Wu^T) with x = A (pro 0) or rmsnorm(h) (pro 1); W = [Wg; Wu] is [2I, K].
 VM_API int vm_skinny_swiglu(const void* A, int pro, const float* norm_w, float eps, const void* W, int M, int I, int K,
-                            void* out, cudaStream_t stream) {
+                            void* out, int* err, cudaStream_t stream) {
     if (I % 8 != 0) return VM_ERR_UNSUPPORTED;
     SkinnyParams p{};
+    p.err = err;
     p.A = A; p.pro = pro; p.norm_w = norm_w; p.eps = eps; p.W = (const __nv_bfloat16*)W; p.M = M; p.N = 2 * I; p.K = K;
     p.out = out; p.out_stride = I; p.I = I; p.epi = EPI_SWIGLU; p.tiles = 2;
-    return skinny_launch(p, I / 8, stream);
+    return skinny_dispatch(p, I / 8, stream);
 }
 
 // q_out[M, H*D] = rope(x Wq^T); rope(x Wk^T) and x Wv^T go to the cache pages; W = [Wq; Wk; Wv] is [(H+2Hkv)*D, K].
@@ -168,5 +201,5 @@ VM_API int vm_skinny_qkv_rope(const void* A, int pro, const float* norm_w, float
     p.positions = positions; p.seq_of_token = seq_of_token; p.block_table = block_table; p.max_blocks = max_blocks;
     p.inv_freq = inv_freq; p.rot_dim = rot_dim; p.kpages = (__nv_bfloat16*)kpages; p.vpages = (__nv_bfloat16*)vpages;
     p.H = H; p.Hkv = Hkv; p.D = D; p.n_pages = n_pages; p.err = err;
-    return skinny_launch(p, (H + 2 * Hkv) * (D / 16), stream);
+    return skinny_dispatch(p, (H + 2 * Hkv) * (D / 16), stream);
 }

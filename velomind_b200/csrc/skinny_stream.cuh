@@ -1,0 +1,340 @@
+// The weight-streaming products (skinny_gemm.cu) for LARGE weight matrices: the same work items, prologue and epilogues
+// as skinny_run, organised around memory bandwidth instead of around the latency of one short chain.
+//
+// skinny_run fetches its weights straight into registers; each warp alternates between requesting a group of blocks and
+// multiplying them, and the prologue is redone by every CTA while those registers are held.  That is right when a product
+// reads one to three megabytes (a launch is then one chain of memory latencies), and slow when it reads tens of megabytes:
+// two thousand dependent instructions per warp at a quarter of the memory bandwidth.  Here a ninth warp streams the
+// weight rows of the CTA's work items through a ring of shared-memory stages with bulk asynchronous copies (one copy per
+// weight row and stage, 2 KB each, completion counted on an mbarrier), which keeps 60 to 190 KB per SM in flight whatever
+// the eight multiplying warps are doing, starts before the wait on the predecessor kernel (weights are constants) and
+// costs the multiplying warps two 16-byte shared-memory loads per two mma.sync.  The prologue reads every row's value of
+// a column by the same thread, so one round of loads covers all rows.
+//
+// Work item, column permutation, accumulation order inside a warp, join of the eight warps and epilogues are those of
+// skinny_run; so are the results, up to the order in which a warp's k blocks are summed.
+#pragma once
+#include "skinny_body.cuh"
+#include "tc05.cuh"
+
+namespace vmsk {
+
+constexpr int SS_CONSUMERS = SK_WARPS;                   // warps that multiply
+constexpr int SS_THREADS = (SS_CONSUMERS + 1) * 32;      // and one that copies
+constexpr int SS_CONSUMER_THREADS = SS_CONSUMERS * 32;
+constexpr int SS_KC = 1024;                              // values of K per stage
+constexpr int SS_W_PITCH = SS_KC * 2 + 64;               // bytes between weight rows of a stage, == 64 (mod 128)
+constexpr int SS_MAX_STAGES = 8;
+
+// byte offsets of the kernel's shared memory
+struct StreamLayout { int ring, red, part, inv, bars, total; };
+__host__ __device__ inline StreamLayout stream_layout(int M, int K, int rows, int stage_rows, int stages) {
+    StreamLayout L;
+    L.ring = (M * skinny_pitch(K) + 127) / 128 * 128;                        // after the A tile: M rows of K bf16
+    L.red = L.ring + stages * stage_rows * SS_W_PITCH;                       // [warp][row][16] partial sums
+    L.part = L.red + SK_WARPS * rows * 16 * (int)sizeof(float);              // [warp][row] partial sums of squares
+    L.inv = L.part + SK_WARPS * rows * (int)sizeof(float);                   // [row] 1/rms
+    L.bars = L.inv + rows * (int)sizeof(float);                              // full[8], empty[8], two flags
+    L.total = L.bars + 2 * SS_MAX_STAGES * 8 + 16;
+    return L;
+}
+
+__device__ __forceinline__ uint64_t ss_policy_evict_first() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+// `bytes` (a multiple of 16) from global to this CTA's shared memory, both 16-byte aligned; completion is counted on `bar`
+__device__ __forceinline__ void ss_bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar, uint64_t policy) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy) : "memory");
+}
+__device__ __forceinline__ void ss_consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(SS_CONSUMER_THREADS) : "memory"); }
+
+template <int MT>
+__global__ void __launch_bounds__(SS_THREADS, MT == 1 ? 2 : 1)
+skinny_stream_kernel(const SkinnyParams p) {
+    extern __shared__ __align__(128) unsigned char ss_smem[];
+    unsigned char* const smem = ss_smem;
+    constexpr int ROWS = 16 * MT;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    const bool two = (p.tiles == 2);
+    const int stage_rows = two ? 16 : 8;
+    const int stage_bytes = stage_rows * SS_W_PITCH;
+    const int S = p.stages;
+    const StreamLayout L = stream_layout(p.M, p.K, ROWS, stage_rows, S);
+    unsigned char* sA = smem;
+    float* red = reinterpret_cast<float*>(smem + L.red);
+    float* part = reinterpret_cast<float*>(smem + L.part);
+    float* inv = reinterpret_cast<float*>(smem + L.inv);
+    const uint32_t bars = ta_u32(smem + L.bars);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L.bars + 2 * SS_MAX_STAGES * 8);
+    volatile int* never_set = abort_flag + 1;
+#define SS_FULL(s) (bars + 8u * (uint32_t)(s))
+#define SS_EMPTY(s) (bars + 8u * (uint32_t)(SS_MAX_STAGES + (s)))
+    if (tid == 0) {
+        for (int s = 0; s < S; ++s) { ta_bar_init(SS_FULL(s), 1); ta_bar_init(SS_EMPTY(s), SS_CONSUMERS); }
+        *abort_flag = 0; *never_set = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    // (the kernel that writes the cache lets its successor, the attention, start only after its own wait: see common.cuh)
+    if (p.epi != EPI_ROPE_KV) vm_pdl_launch_dependents();
+    const int my_items = (int)blockIdx.x < p.n_items ? (p.n_items - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+    const int chunks = (p.K + SS_KC - 1) / SS_KC;
+    int n_issued = 0;
+
+    if (warp == SS_CONSUMERS) {
+        // ---- the copying warp: lane l fetches weight row l of each stage.  Weights are constants of the model, so it does
+        //      not wait for the predecessor kernel: the ring is full when the multiplying warps get there.
+        const uint64_t policy = ss_policy_evict_first();           // every weight byte is used once per step
+        const uint32_t ring = ta_u32(smem + L.ring);
+        int n = 0;
+        bool ok = true;
+        for (int it = 0; it < my_items && ok; ++it) {
+            const SkinnyCols c = skinny_cols(p, (int)blockIdx.x + it * (int)gridDim.x);
+            const __nv_bfloat16* src = p.W + (size_t)(lane < 8 ? c.nA + lane : c.nB + lane - 8) * p.K;   // (lanes past stage_rows copy nothing)
+            for (int ch = 0; ch < chunks; ++ch) {
+                const int s = n % S;
+                if (n >= S) ok = ta_wait(SS_EMPTY(s), (uint32_t)((n / S) - 1) & 1u, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                const int kc0 = ch * SS_KC, kc = min(SS_KC, p.K - kc0);
+                if (lane == 0) ta_bar_expect_tx(SS_FULL(s), (uint32_t)(stage_rows * kc * 2));
+                if (lane < stage_rows)
+                    ss_bulk_load(ring + (uint32_t)(s * stage_bytes + lane * SS_W_PITCH), src + kc0, (uint32_t)(kc * 2), SS_FULL(s), policy);
+                ++n;
+            }
+        }
+        n_issued = n;
+    } else {
+        // ---- the multiplying warps
+        vm_pdl_wait();                                          // from here on: data written by earlier kernels
+        if (p.epi == EPI_ROPE_KV) vm_pdl_launch_dependents();
+        const int a_pitch = p.row_bytes;
+        // this thread's place in the epilogue: one (row, column-in-tile) of the work item
+        const int e_row = tid >> 3, e_c = tid & 7;
+        const bool e_live = tid < ROWS * 8 && e_row < p.M;
+        int row_pos = 0, row_page = -1;
+        if (p.epi == EPI_ROPE_KV && e_live) {
+            row_pos = p.positions[e_row];
+            if (p.kpages != nullptr) {
+                const int blk = row_pos / VM_PAGE_TOKENS;
+                row_page = (blk < p.max_blocks) ? p.block_table[(size_t)p.seq_of_token[e_row] * p.max_blocks + blk] : -1;
+            }
+        }
+        // ---- stage A once for all work items of the CTA
+        if (p.pro == PRO_NONE) {
+            const __nv_bfloat16* A = static_cast<const __nv_bfloat16*>(p.A);
+            const int per_row = p.K / 8;
+            for (int r = 0; r < p.M; ++r)
+                for (int ch = tid; ch < per_row; ch += SS_CONSUMER_THREADS)
+                    vm_cp_async16(sA + (size_t)r * a_pitch + ch * 16, A + (size_t)r * p.K + ch * 8);
+            vm_cp_async_commit();
+            vm_cp_async_wait_all();
+        } else {
+            // x * w as bf16; the row's 1/rms multiplies the float32 sums in the epilogue (a row scale commutes with the
+            // product).  A thread owns columns: it reads the norm weight once and the values of all rows in one round.
+            const float* h = static_cast<const float*>(p.A);
+            const int quads = p.K / 4;
+            float ss[ROWS];
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) ss[r] = 0.f;
+#pragma unroll 2
+            for (int q = tid; q < quads; q += SS_CONSUMER_THREADS) {
+                const float4 w = reinterpret_cast<const float4*>(p.norm_w)[q];
+#pragma unroll
+                for (int r0 = 0; r0 < ROWS; r0 += 8) {
+                    if (r0 >= p.M) break;
+                    float4 x[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+                        if (r0 + u < p.M) x[u] = __ldcg(reinterpret_cast<const float4*>(h + (size_t)(r0 + u) * p.K) + q);   // from L2: another SM wrote it
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+                        if (r0 + u < p.M) {
+                            ss[r0 + u] += x[u].x * x[u].x + x[u].y * x[u].y + x[u].z * x[u].z + x[u].w * x[u].w;
+                            uint2 v;
+                            v.x = vm_pack_bf16(x[u].x * w.x, x[u].y * w.y);
+                            v.y = vm_pack_bf16(x[u].z * w.z, x[u].w * w.w);
+                            *reinterpret_cast<uint2*>(sA + (size_t)(r0 + u) * a_pitch + q * 8) = v;
+                        }
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r)
+                if (r < p.M) {
+                    const float v = vm_warp_sum(ss[r]);
+                    if (lane == 0) part[warp * ROWS + r] = v;
+                }
+        }
+        ss_consumer_sync();
+        if (p.pro == PRO_RMSNORM && tid < p.M) {                 // (read by the epilogue after the join's barrier)
+            float sum = 0.f;
+#pragma unroll
+            for (int w = 0; w < SS_CONSUMERS; ++w) sum += part[w * ROWS + tid];
+            inv[tid] = 1.0f / sqrtf(sum / (float)p.K + p.eps);
+        }
+
+        int n = 0;
+        bool ok = true;
+        for (int it = 0; it < my_items; ++it) {
+            const SkinnyCols cols = skinny_cols(p, (int)blockIdx.x + it * (int)gridDim.x);
+            const int nA = cols.nA, nB = cols.nB, head = cols.head;
+            const bool rotate = p.epi == EPI_ROPE_KV && head < p.H + p.Hkv && p.rot_dim > 0;
+            // what the epilogue adds to or multiplies with is requested now: its latency passes under the product
+            float freq = 0.f, res_a = 0.f, res_b = 0.f;
+            if (rotate) freq = p.inv_freq[(nA - head * p.D) + e_c];
+            if (p.epi == EPI_RESIDUAL && e_live) {
+                const float* o = p.h + (size_t)e_row * p.N;
+                res_a = __ldcg(o + nA + e_c);
+                if (two) res_b = __ldcg(o + nB + e_c);
+            }
+            float acc[MT][2][4];
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int t = 0; t < 2; ++t) acc[mt][t][0] = acc[mt][t][1] = acc[mt][t][2] = acc[mt][t][3] = 0.f;
+
+            for (int ch = 0; ch < chunks; ++ch, ++n) {
+                const int s = n % S;
+                if (ok) ok = ta_wait(SS_FULL(s), (uint32_t)(n / S) & 1u, abort_flag);
+                const int kc0 = ch * SS_KC, blocks = min(SS_KC, p.K - kc0) >> 5;
+                const unsigned char* wbase = smem + L.ring + s * stage_bytes + g * SS_W_PITCH + t4 * 16;
+                const unsigned char* abase = sA + kc0 * 2 + t4 * 16;
+#pragma unroll 2
+                for (int b = warp; b < blocks; b += SS_CONSUMERS) {
+                    const uint4 wa = *reinterpret_cast<const uint4*>(wbase + b * 64);
+                    uint4 wb = make_uint4(0u, 0u, 0u, 0u);
+                    if (two) wb = *reinterpret_cast<const uint4*>(wbase + 8 * SS_W_PITCH + b * 64);
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        uint4 a_lo = make_uint4(0u, 0u, 0u, 0u), a_hi = a_lo;          // rows past M: zeros, never read
+                        if (mt * 16 + g < p.M) a_lo = *reinterpret_cast<const uint4*>(abase + (size_t)(mt * 16 + g) * a_pitch + b * 64);
+                        if (mt * 16 + g + 8 < p.M) a_hi = *reinterpret_cast<const uint4*>(abase + (size_t)(mt * 16 + g + 8) * a_pitch + b * 64);
+                        vm_mma_bf16_16816(acc[mt][0], a_lo.x, a_hi.x, a_lo.y, a_hi.y, wa.x, wa.y);
+                        vm_mma_bf16_16816(acc[mt][0], a_lo.z, a_hi.z, a_lo.w, a_hi.w, wa.z, wa.w);
+                        if (two) {
+                            vm_mma_bf16_16816(acc[mt][1], a_lo.x, a_hi.x, a_lo.y, a_hi.y, wb.x, wb.y);
+                            vm_mma_bf16_16816(acc[mt][1], a_lo.z, a_hi.z, a_lo.w, a_hi.w, wb.z, wb.w);
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) ta_bar_arrive(SS_EMPTY(s));       // this warp has read the stage
+            }
+            // ---- join the warps' partial sums: red[warp][row][col], col 0..7 = tile A, 8..15 = tile B
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int t = 0; t < 2; ++t)
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        const int row = mt * 16 + g + 8 * half;
+                        if (row < p.M && (t == 0 || two))
+                            *reinterpret_cast<float2*>(&red[((size_t)warp * ROWS + row) * 16 + t * 8 + 2 * t4]) =
+                                make_float2(acc[mt][t][2 * half], acc[mt][t][2 * half + 1]);
+                    }
+            ss_consumer_sync();
+            if (e_live && !*abort_flag) {
+                const int row = e_row, c = e_c;
+                float vA = 0.f, vB = 0.f;
+#pragma unroll
+                for (int w = 0; w < SS_CONSUMERS; ++w) {
+                    vA += red[((size_t)w * ROWS + row) * 16 + c];
+                    if (two) vB += red[((size_t)w * ROWS + row) * 16 + 8 + c];
+                }
+                if (p.pro == PRO_RMSNORM) { const float rs = inv[row]; vA *= rs; vB *= rs; }
+                switch (p.epi) {
+                    case EPI_STORE_BF16: {
+                        __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + (size_t)row * p.out_stride;
+                        o[nA + c] = __float2bfloat16_rn(vA);
+                        if (two) o[nB + c] = __float2bfloat16_rn(vB);
+                    } break;
+                    case EPI_STORE_F32: {
+                        float* o = static_cast<float*>(p.out) + (size_t)row * p.out_stride;
+                        o[nA + c] = vA;
+                        if (two) o[nB + c] = vB;
+                    } break;
+                    case EPI_RESIDUAL: {
+                        float* o = p.h + (size_t)row * p.N;
+                        o[nA + c] = res_a + vA;
+                        if (two) o[nB + c] = res_b + vB;
+                    } break;
+                    case EPI_SWIGLU: {
+                        const float sig = 1.0f / (1.0f + expf(-vA));
+                        static_cast<__nv_bfloat16*>(p.out)[(size_t)row * p.out_stride + nA + c] = __float2bfloat16_rn((sig * vA) * vB);
+                    } break;
+                    case EPI_ROPE_KV: {
+                        float ya = vA, yb = vB;
+                        int da, db;                                 // the two columns' places inside the head
+                        if (rotate) {
+                            da = (nA - head * p.D) + c; db = da + p.D / 2;
+                            float sn, co;
+                            sincosf((float)row_pos * freq, &sn, &co);
+                            ya = vA * co - vB * sn;
+                            yb = vB * co + vA * sn;
+                        } else { da = (nA - head * p.D) + c; db = da + 8; }
+                        if (head < p.H) {
+                            __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + (size_t)row * p.out_stride + (size_t)head * p.D;
+                            o[da] = __float2bfloat16_rn(ya); o[db] = __float2bfloat16_rn(yb);
+                        } else if (p.kpages != nullptr) {
+                            if (row_page < 0 || row_page >= p.n_pages) { if (p.err) atomicExch(p.err, VM_ERRWORD_CACHE_WRITE); break; }
+                            const bool is_k = head < p.H + p.Hkv;
+                            const int hk = is_k ? head - p.H : head - p.H - p.Hkv;
+                            __nv_bfloat16* dst = (is_k ? p.kpages : p.vpages) + (size_t)row_page * ((size_t)p.Hkv * VM_PAGE_TOKENS * p.D)
+                                                 + ((size_t)hk * VM_PAGE_TOKENS + row_pos % VM_PAGE_TOKENS) * p.D;
+                            dst[da] = __float2bfloat16_rn(ya); dst[db] = __float2bfloat16_rn(yb);
+                        }
+                    } break;
+                }
+            }
+            ss_consumer_sync();                                  // the sums' buffer is reused by the next item
+        }
+    }
+    // ---- a wait that ran out: nothing more was stored; copies still in flight into this CTA's shared memory are waited
+    //      for (again with a limit) before the CTA ends, and the step's error word says what happened
+    __syncthreads();
+    if (*abort_flag && warp == SS_CONSUMERS) {
+        if (lane == 0) {
+            for (int k = max(0, n_issued - S); k < n_issued; ++k) ta_wait(SS_FULL(k % S), (uint32_t)(k / S) & 1u, never_set);
+            if (p.err) atomicExch(p.err, VM_ERRWORD_BARRIER_WAIT);
+        }
+    }
+#undef SS_FULL
+#undef SS_EMPTY
+}
+
+// Launch for `items` work items (p.tiles, p.epi and the epilogue's fields set by the caller).  VM_ERR_UNSUPPORTED when the
+// A tile and two stages do not fit into shared memory or M is over 32: the caller then takes skinny_launch.
+inline int skinny_stream_launch(SkinnyParams p, int items, cudaStream_t stream, bool one_per_sm = false) {
+    if (p.M <= 0 || items <= 0) return 0;
+    if (p.M > 32 || p.K % 32 != 0 || p.K <= 0) return VM_ERR_UNSUPPORTED;
+    const int MT = p.M <= 16 ? 1 : 2;
+    const int rows = 16 * MT, stage_rows = p.tiles == 2 ? 16 : 8, stage_bytes = stage_rows * SS_W_PITCH;
+    const int fixed = stream_layout(p.M, p.K, rows, stage_rows, 0).total;
+    constexpr int SM_BYTES = 227 * 1024, CTA_RESERVED = 1024;
+    int per_sm = 1, S = (SM_BYTES - CTA_RESERVED - fixed) / stage_bytes;
+    if (!one_per_sm && MT == 1 && fixed + 2 * stage_bytes <= SM_BYTES / 2 - CTA_RESERVED) { per_sm = 2; S = (SM_BYTES / 2 - CTA_RESERVED - fixed) / stage_bytes; }
+    if (S > SS_MAX_STAGES) S = SS_MAX_STAGES;
+    if (S < 2) return VM_ERR_UNSUPPORTED;
+    const int sms = vm_sm_count() > 0 ? vm_sm_count() : 1;
+    const int grid = items < sms * per_sm ? items : sms * per_sm;
+    p.n_items = items; p.stages = S; p.row_bytes = skinny_pitch(p.K);
+    const size_t smem = (size_t)stream_layout(p.M, p.K, rows, stage_rows, S).total;
+#define VM_SS_CASE(X)                                                                                                 \
+    {                                                                                                                 \
+        static bool configured = false;                                                                               \
+        if (!configured) {                                                                                            \
+            cudaError_t e = cudaFuncSetAttribute(skinny_stream_kernel<X>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_BYTES - CTA_RESERVED); \
+            if (e != cudaSuccess) return (int)e;                                                                      \
+            configured = true;                                                                                        \
+        }                                                                                                             \
+        vm_launch_pdl(skinny_stream_kernel<X>, dim3(grid), dim3(SS_THREADS), smem, stream, p);                        \
+    }
+    if (MT == 1) VM_SS_CASE(1) else VM_SS_CASE(2)
+#undef VM_SS_CASE
+    return vm_launch_status();
+}
+
+}  // namespace vmsk

@@ -103,16 +103,16 @@ extern int SKINNY_NORM_ROWS;       // up to this many rows the norm is fused int
 inline bool skinny_ok(int M, long long K, const DeviceTensor& W) { return M > 0 && M <= SKINNY_MAX_ROWS && K % 32 == 0 && W.dtype == DType::BF16; }
 
 inline void skinny_linear(const void* x, const float* norm_w, float eps, const DeviceTensor& W, int M, void* out, int out_stride, bool out_f32,
-                          float* residual, cudaStream_t s) {
+                          float* residual, int* err, cudaStream_t s) {
     Timed t("skinny_linear", s);
     check(vm_skinny_linear(x, norm_w ? 1 : 0, norm_w, eps, W.ptr, M, static_cast<int>(W.rows()), static_cast<int>(W.cols()), out, out_stride,
-                           out_f32 ? 1 : 0, residual, s),
+                           out_f32 ? 1 : 0, residual, err, s),
           "skinny_linear", s);
 }
 
-inline void skinny_swiglu(const void* x, const float* norm_w, float eps, const DeviceTensor& W, int M, int I, void* out, cudaStream_t s) {
+inline void skinny_swiglu(const void* x, const float* norm_w, float eps, const DeviceTensor& W, int M, int I, void* out, int* err, cudaStream_t s) {
     Timed t("skinny_swiglu", s);
-    check(vm_skinny_swiglu(x, norm_w ? 1 : 0, norm_w, eps, W.ptr, M, I, static_cast<int>(W.cols()), out, s), "skinny_swiglu", s);
+    check(vm_skinny_swiglu(x, norm_w ? 1 : 0, norm_w, eps, W.ptr, M, I, static_cast<int>(W.cols()), out, err, s), "skinny_swiglu", s);
 }
 
 inline void skinny_qkv_rope(const void* x, const float* norm_w, float eps, const DeviceTensor& W, void* q_out, const StepContext& ctx, const KVView& kv,

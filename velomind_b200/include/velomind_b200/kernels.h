@@ -61,10 +61,12 @@ int vm_attention_decode_bf16(const void* q, int q_row_stride, const void* kpages
                              int Hkv, int D, int n_splits, float scale, int window, int n_pages, int* err, cudaStream_t stream);
 
 // ---- skinny_gemm.cu: weight-streaming products for few rows (bfloat16 weights [N, K])
+// (err: the step's error word, may be null; the kernel for large weight matrices reports a wait that ran out there)
 int vm_skinny_linear(const void* A, int pro, const float* norm_w, float eps, const void* W, int M, int N, int K, void* out,
-                     int out_stride, int out_f32, float* residual_h, cudaStream_t stream);
+                     int out_stride, int out_f32, float* residual_h, int* err, cudaStream_t stream);
 int vm_skinny_swiglu(const void* A, int pro, const float* norm_w, float eps, const void* W, int M, int I, int K, void* out,
-                     cudaStream_t stream);
+                     int* err, cudaStream_t stream);
+void vm_skinny_variant(int variant);       // 0 choose by size, 1 / 2 force one of the two kernels (tests, measurements)
 int vm_skinny_qkv_rope(const void* A, int pro, const float* norm_w, float eps, const void* W, int M, int K, void* q_out,
                        const int* positions, const int* seq_of_token, const int* block_table, int max_blocks,
                        const float* inv_freq, int rot_dim, int pairing, void* kpages, void* vpages, int H, int Hkv, int D,

@@ -285,8 +285,14 @@ def _norm_args(norm):
     return 1, weight, float(eps)
 
 
+def skinny_variant(variant: int) -> None:
+    """Which weight-streaming kernel the three launchers below take: 0 by size, 1 the register-fed one, 2 the one that streams
+    the weights through shared memory (refuses what it does not take)."""
+    library().vm_skinny_variant(_c_int(variant))
+
+
 def skinny_linear(x: torch.Tensor, norm, weight: torch.Tensor, out: Optional[torch.Tensor],
-                  residual: Optional[torch.Tensor] = None) -> None:
+                  residual: Optional[torch.Tensor] = None, err: Optional[torch.Tensor] = None) -> None:
     """out = x' W^T (bf16 or float32 out), or residual += x' W^T (float32), for M <= 64 rows.
     x' = x (bf16 [M, K]) when `norm` is None, else rmsnorm(x) * norm[0] with eps norm[1] from x float32 [M, K]."""
     M, K = x.shape
@@ -295,15 +301,15 @@ def skinny_linear(x: torch.Tensor, norm, weight: torch.Tensor, out: Optional[tor
     _check(library().vm_skinny_linear(_ptr(_contig(x, "x")), _c_int(pro), _ptr(nw), _c_f(eps), _ptr(weight), _c_int(M), _c_int(N),
                                       _c_int(K), _ptr(out), _c_int(out.stride(0) if out is not None else N),
                                       _c_int(1 if (out is not None and out.dtype == torch.float32) else 0), _ptr(residual),
-                                      _stream()), "skinny_linear")
+                                      _ptr(err), _stream()), "skinny_linear")
 
 
-def skinny_swiglu(x: torch.Tensor, norm, weight: torch.Tensor, out: torch.Tensor) -> None:
+def skinny_swiglu(x: torch.Tensor, norm, weight: torch.Tensor, out: torch.Tensor, err: Optional[torch.Tensor] = None) -> None:
     """out[M, I] = silu(x' Wg^T) * (x' Wu^T), weight = [Wg; Wu] stacked [2I, K]; x' as in skinny_linear."""
     M, K = x.shape
     pro, nw, eps = _norm_args(norm)
     _check(library().vm_skinny_swiglu(_ptr(_contig(x, "x")), _c_int(pro), _ptr(nw), _c_f(eps), _ptr(weight), _c_int(M),
-                                      _c_int(out.shape[1]), _c_int(K), _ptr(_contig(out, "out")), _stream()), "skinny_swiglu")
+                                      _c_int(out.shape[1]), _c_int(K), _ptr(_contig(out, "out")), _ptr(err), _stream()), "skinny_swiglu")
 
 
 def skinny_qkv_rope(x: torch.Tensor, norm, weight: torch.Tensor, q_out: torch.Tensor, positions: torch.Tensor,

@@ -103,7 +103,7 @@ public:
         void* att = ctx.take_tokens(static_cast<long long>(H_) * D_, DType::BF16);
         ops::attention(ctx, q, H_ * D_, kv, att, H_, Hkv_, D_, scale_, window_);
         ctx.give(q);
-        if (skinny) ops::skinny_linear(att, nullptr, 0.f, out_.weight, ctx.T, nullptr, hidden_, false, h, ctx.stream);
+        if (skinny) ops::skinny_linear(att, nullptr, 0.f, out_.weight, ctx.T, nullptr, hidden_, false, h, ctx.err, ctx.stream);
         else ops::tc_linear(att, static_cast<long long>(H_) * D_, out_.weight, ctx.T, nullptr, hidden_, false, h, ctx.err, ctx.stream);
         ctx.give(att);
     }

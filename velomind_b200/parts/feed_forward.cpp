@@ -57,15 +57,15 @@ public:
         }
         void* act = ctx.take_tokens(I_, DType::BF16);
         if (skinny && ctx.T_cap <= ops::SKINNY_NORM_ROWS) {
-            ops::skinny_swiglu(h, nw, eps, gate_up_.weight, ctx.T, I_, act, ctx.stream);
+            ops::skinny_swiglu(h, nw, eps, gate_up_.weight, ctx.T, I_, act, ctx.err, ctx.stream);
         } else {
             void* x = ctx.take_tokens(hidden_, DType::BF16);           // many rows: norm once, not once per CTA
             norm.forward(ctx, h, nullptr, x, nullptr, 0);
-            if (skinny) ops::skinny_swiglu(x, nullptr, 0.f, gate_up_.weight, ctx.T, I_, act, ctx.stream);
+            if (skinny) ops::skinny_swiglu(x, nullptr, 0.f, gate_up_.weight, ctx.T, I_, act, ctx.err, ctx.stream);
             else ops::tc_swiglu(x, hidden_, gate_up_.weight, ctx.T, I_, act, ctx.err, ctx.stream);
             ctx.give(x);
         }
-        if (skinny) ops::skinny_linear(act, nullptr, 0.f, down_.weight, ctx.T, nullptr, hidden_, false, h, ctx.stream);
+        if (skinny) ops::skinny_linear(act, nullptr, 0.f, down_.weight, ctx.T, nullptr, hidden_, false, h, ctx.err, ctx.stream);
         else ops::tc_linear(act, I_, down_.weight, ctx.T, nullptr, hidden_, false, h, ctx.err, ctx.stream);
         ctx.give(act);
     }
