@@ -467,18 +467,19 @@ def _rms_ref(h, w, eps):
     return _bf(torch.from_numpy(P.rmsnorm(h.numpy(), w.numpy(), eps)))
 
 
-@pytest.fixture(params=["register-fed", "ring"])
+@pytest.fixture(params=["register-fed", "ring", "ring-one-cta"])
 def skinny_kernel(request):
     """Both weight-streaming kernels, forced: the one that fetches weights into registers (what small matrices take) and the
-    one that streams them through a ring in shared memory (large matrices, at most 32 rows)."""
+    one that streams them through a ring in shared memory (large matrices, at most 32 rows), the latter also in the form it
+    takes when only one CTA fits an SM (sixteen multiplying warps for up to 16 rows)."""
     o = ops()
-    o.skinny_variant(1 if request.param == "register-fed" else 2)
+    o.skinny_variant({"register-fed": 1, "ring": 2, "ring-one-cta": 3}[request.param])
     yield request.param
     o.skinny_variant(0)
 
 
 def _ring_takes(kernel, M):
-    if kernel == "ring" and M > 32:
+    if kernel.startswith("ring") and M > 32:
         pytest.skip("the ring kernel takes at most 32 rows")
 
 

@@ -148,7 +148,8 @@ int skinny_dispatch(SkinnyParams p, int items, cudaStream_t stream) {
 }  // namespace
 
 // 0: the launchers choose between the two weight-streaming kernels by size; 1: always skinny_gemm_kernel; 2: always
-// skinny_stream_kernel (VM_ERR_UNSUPPORTED where it does not take the sizes).  For tests and measurements.
+// skinny_stream_kernel (VM_ERR_UNSUPPORTED where it does not take the sizes); 3: the same with one CTA per SM.  For tests
+// and measurements.
 VM_API void vm_skinny_variant(int variant) { skinny_variant = variant; }
 
 // out = A W^T (pro 0) or rmsnorm(h) W^T (pro 1); out bf16 (out_f32 0) or float32 (1); or h += ... (residual 1).

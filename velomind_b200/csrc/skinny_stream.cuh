@@ -4,7 +4,7 @@
 // skinny_run fetches its weights straight into registers; each warp alternates between requesting a group of blocks and
 // multiplying them, and the prologue is redone by every CTA while those registers are held.  That is right when a product
 // reads one to three megabytes (a launch is then one chain of memory latencies), and slow when it reads tens of megabytes:
-// two thousand dependent instructions per warp at a quarter of the memory bandwidth.  Here a ninth warp streams the
+// two thousand dependent instructions per warp at a quarter of the memory bandwidth.  Here warps of their own stream the
 // weight rows of the CTA's work items through a ring of shared-memory stages with bulk asynchronous copies (one copy per
 // weight row and stage, 2 KB each, completion counted on an mbarrier), which keeps 60 to 190 KB per SM in flight whatever
 // the eight multiplying warps are doing, starts before the wait on the predecessor kernel (weights are constants) and
@@ -19,21 +19,19 @@
 
 namespace vmsk {
 
-constexpr int SS_CONSUMERS = SK_WARPS;                   // warps that multiply
-constexpr int SS_THREADS = (SS_CONSUMERS + 1) * 32;      // and one that copies
-constexpr int SS_CONSUMER_THREADS = SS_CONSUMERS * 32;
+// (CW: warps that multiply, 8 or 16; PW: warps that copy, 2 or 4)
 constexpr int SS_KC = 1024;                              // values of K per stage
 constexpr int SS_W_PITCH = SS_KC * 2 + 64;               // bytes between weight rows of a stage, == 64 (mod 128)
 constexpr int SS_MAX_STAGES = 8;
 
 // byte offsets of the kernel's shared memory
 struct StreamLayout { int ring, red, part, inv, bars, total; };
-__host__ __device__ inline StreamLayout stream_layout(int M, int K, int rows, int stage_rows, int stages) {
+__host__ __device__ inline StreamLayout stream_layout(int M, int K, int rows, int stage_rows, int stages, int cw) {
     StreamLayout L;
     L.ring = (M * skinny_pitch(K) + 127) / 128 * 128;                        // after the A tile: M rows of K bf16
     L.red = L.ring + stages * stage_rows * SS_W_PITCH;                       // [warp][row][16] partial sums
-    L.part = L.red + SK_WARPS * rows * 16 * (int)sizeof(float);              // [warp][row] partial sums of squares
-    L.inv = L.part + SK_WARPS * rows * (int)sizeof(float);                   // [row] 1/rms
+    L.part = L.red + cw * rows * 16 * (int)sizeof(float);              // [warp][row] partial sums of squares
+    L.inv = L.part + cw * rows * (int)sizeof(float);                   // [row] 1/rms
     L.bars = L.inv + rows * (int)sizeof(float);                              // full[8], empty[8], two flags
     L.total = L.bars + 2 * SS_MAX_STAGES * 8 + 16;
     return L;
@@ -49,11 +47,12 @@ __device__ __forceinline__ void ss_bulk_load(uint32_t dst, const void* src, uint
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy) : "memory");
 }
-__device__ __forceinline__ void ss_consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(SS_CONSUMER_THREADS) : "memory"); }
+template <int THREADS> __device__ __forceinline__ void ss_consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(THREADS) : "memory"); }
 
-template <int MT>
-__global__ void __launch_bounds__(SS_THREADS, MT == 1 ? 2 : 1)
+template <int MT, int CW, int PW>
+__global__ void __launch_bounds__((CW + PW) * 32, (MT == 1 && CW == 8) ? 2 : 1)
 skinny_stream_kernel(const SkinnyParams p) {
+    constexpr int SS_CONSUMERS = CW, SS_CONSUMER_THREADS = CW * 32;
     extern __shared__ __align__(128) unsigned char ss_smem[];
     unsigned char* const smem = ss_smem;
     constexpr int ROWS = 16 * MT;
@@ -62,7 +61,7 @@ skinny_stream_kernel(const SkinnyParams p) {
     const int stage_rows = two ? 16 : 8;
     const int stage_bytes = stage_rows * SS_W_PITCH;
     const int S = p.stages;
-    const StreamLayout L = stream_layout(p.M, p.K, ROWS, stage_rows, S);
+    const StreamLayout L = stream_layout(p.M, p.K, ROWS, stage_rows, S, CW);
     unsigned char* sA = smem;
     float* red = reinterpret_cast<float*>(smem + L.red);
     float* part = reinterpret_cast<float*>(smem + L.part);
@@ -73,7 +72,7 @@ skinny_stream_kernel(const SkinnyParams p) {
 #define SS_FULL(s) (bars + 8u * (uint32_t)(s))
 #define SS_EMPTY(s) (bars + 8u * (uint32_t)(SS_MAX_STAGES + (s)))
     if (tid == 0) {
-        for (int s = 0; s < S; ++s) { ta_bar_init(SS_FULL(s), 1); ta_bar_init(SS_EMPTY(s), SS_CONSUMERS); }
+        for (int s = 0; s < S; ++s) { ta_bar_init(SS_FULL(s), PW); ta_bar_init(SS_EMPTY(s), SS_CONSUMERS); }
         *abort_flag = 0; *never_set = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -84,25 +83,29 @@ skinny_stream_kernel(const SkinnyParams p) {
     const int chunks = (p.K + SS_KC - 1) / SS_KC;
     int n_issued = 0;
 
-    if (warp == SS_CONSUMERS) {
-        // ---- the copying warp: lane l fetches weight row l of each stage.  Weights are constants of the model, so it does
-        //      not wait for the predecessor kernel: the ring is full when the multiplying warps get there.
+    if (warp >= SS_CONSUMERS) {
+        // ---- the copying warps: each fetches its share of a stage's weight rows, a lane a row (a bulk copy takes the issuing
+        //      warp about a hundred cycles whatever its size; with two CTAs per SM two warps are enough, a CTA that has
+        //      an SM to itself has four).  Weights are constants of the model, so these warps do not wait for the
+        //      predecessor kernel: the ring is full when the multiplying warps get there.
         const uint64_t policy = ss_policy_evict_first();           // every weight byte is used once per step
         const uint32_t ring = ta_u32(smem + L.ring);
+        const int rows_pw = stage_rows / PW;
+        const int my_row = (warp - SS_CONSUMERS) * rows_pw + lane;             // (lanes past rows_pw copy nothing)
         int n = 0;
         bool ok = true;
         for (int it = 0; it < my_items && ok; ++it) {
             const SkinnyCols c = skinny_cols(p, (int)blockIdx.x + it * (int)gridDim.x);
-            const __nv_bfloat16* src = p.W + (size_t)(lane < 8 ? c.nA + lane : c.nB + lane - 8) * p.K;   // (lanes past stage_rows copy nothing)
+            const __nv_bfloat16* src = p.W + (size_t)(my_row < 8 ? c.nA + my_row : c.nB + my_row - 8) * p.K;
             for (int ch = 0; ch < chunks; ++ch) {
                 const int s = n % S;
                 if (n >= S) ok = ta_wait(SS_EMPTY(s), (uint32_t)((n / S) - 1) & 1u, abort_flag);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 const int kc0 = ch * SS_KC, kc = min(SS_KC, p.K - kc0);
-                if (lane == 0) ta_bar_expect_tx(SS_FULL(s), (uint32_t)(stage_rows * kc * 2));
-                if (lane < stage_rows)
-                    ss_bulk_load(ring + (uint32_t)(s * stage_bytes + lane * SS_W_PITCH), src + kc0, (uint32_t)(kc * 2), SS_FULL(s), policy);
+                if (lane == 0) ta_bar_expect_tx(SS_FULL(s), (uint32_t)(rows_pw * kc * 2));
+                if (lane < rows_pw)
+                    ss_bulk_load(ring + (uint32_t)(s * stage_bytes + my_row * SS_W_PITCH), src + kc0, (uint32_t)(kc * 2), SS_FULL(s), policy);
                 ++n;
             }
         }
@@ -168,7 +171,7 @@ skinny_stream_kernel(const SkinnyParams p) {
                     if (lane == 0) part[warp * ROWS + r] = v;
                 }
         }
-        ss_consumer_sync();
+        ss_consumer_sync<SS_CONSUMER_THREADS>();
         if (p.pro == PRO_RMSNORM && tid < p.M) {                 // (read by the epilogue after the join's barrier)
             float sum = 0.f;
 #pragma unroll
@@ -235,7 +238,7 @@ skinny_stream_kernel(const SkinnyParams p) {
                             *reinterpret_cast<float2*>(&red[((size_t)warp * ROWS + row) * 16 + t * 8 + 2 * t4]) =
                                 make_float2(acc[mt][t][2 * half], acc[mt][t][2 * half + 1]);
                     }
-            ss_consumer_sync();
+            ss_consumer_sync<SS_CONSUMER_THREADS>();
             if (e_live && !*abort_flag) {
                 const int row = e_row, c = e_c;
                 float vA = 0.f, vB = 0.f;
@@ -289,13 +292,13 @@ skinny_stream_kernel(const SkinnyParams p) {
                     } break;
                 }
             }
-            ss_consumer_sync();                                  // the sums' buffer is reused by the next item
+            ss_consumer_sync<SS_CONSUMER_THREADS>();                                  // the sums' buffer is reused by the next item
         }
     }
     // ---- a wait that ran out: nothing more was stored; copies still in flight into this CTA's shared memory are waited
     //      for (again with a limit) before the CTA ends, and the step's error word says what happened
     __syncthreads();
-    if (*abort_flag && warp == SS_CONSUMERS) {
+    if (*abort_flag && warp >= SS_CONSUMERS) {
         if (lane == 0) {
             for (int k = max(0, n_issued - S); k < n_issued; ++k) ta_wait(SS_FULL(k % S), (uint32_t)(k / S) & 1u, never_set);
             if (p.err) atomicExch(p.err, VM_ERRWORD_BARRIER_WAIT);
@@ -312,27 +315,35 @@ inline int skinny_stream_launch(SkinnyParams p, int items, cudaStream_t stream, 
     if (p.M > 32 || p.K % 32 != 0 || p.K <= 0) return VM_ERR_UNSUPPORTED;
     const int MT = p.M <= 16 ? 1 : 2;
     const int rows = 16 * MT, stage_rows = p.tiles == 2 ? 16 : 8, stage_bytes = stage_rows * SS_W_PITCH;
-    const int fixed = stream_layout(p.M, p.K, rows, stage_rows, 0).total;
     constexpr int SM_BYTES = 227 * 1024, CTA_RESERVED = 1024;
-    int per_sm = 1, S = (SM_BYTES - CTA_RESERVED - fixed) / stage_bytes;
-    if (!one_per_sm && MT == 1 && fixed + 2 * stage_bytes <= SM_BYTES / 2 - CTA_RESERVED) { per_sm = 2; S = (SM_BYTES / 2 - CTA_RESERVED - fixed) / stage_bytes; }
+    // two CTAs of eight multiplying warps per SM when the A tile leaves room for two stages each; else one CTA, with sixteen
+    // multiplying warps where the registers allow (up to 16 rows): eight do not keep up with the ring of a whole SM
+    int cw = 8, per_sm = 2;
+    int fixed = stream_layout(p.M, p.K, rows, stage_rows, 0, cw).total;
+    int S = (SM_BYTES / 2 - CTA_RESERVED - fixed) / stage_bytes;
+    if (one_per_sm || MT != 1 || S < 2) {
+        per_sm = 1;
+        cw = MT == 1 ? 16 : 8;
+        fixed = stream_layout(p.M, p.K, rows, stage_rows, 0, cw).total;
+        S = (SM_BYTES - CTA_RESERVED - fixed) / stage_bytes;
+    }
     if (S > SS_MAX_STAGES) S = SS_MAX_STAGES;
     if (S < 2) return VM_ERR_UNSUPPORTED;
     const int sms = vm_sm_count() > 0 ? vm_sm_count() : 1;
     const int grid = items < sms * per_sm ? items : sms * per_sm;
     p.n_items = items; p.stages = S; p.row_bytes = skinny_pitch(p.K);
-    const size_t smem = (size_t)stream_layout(p.M, p.K, rows, stage_rows, S).total;
-#define VM_SS_CASE(X)                                                                                                 \
+    const size_t smem = (size_t)stream_layout(p.M, p.K, rows, stage_rows, S, cw).total;
+#define VM_SS_CASE(X, W, P)                                                                                             \
     {                                                                                                                 \
         static bool configured = false;                                                                               \
         if (!configured) {                                                                                            \
-            cudaError_t e = cudaFuncSetAttribute(skinny_stream_kernel<X>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_BYTES - CTA_RESERVED); \
+            cudaError_t e = cudaFuncSetAttribute(skinny_stream_kernel<X, W, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_BYTES - CTA_RESERVED); \
             if (e != cudaSuccess) return (int)e;                                                                      \
             configured = true;                                                                                        \
         }                                                                                                             \
-        vm_launch_pdl(skinny_stream_kernel<X>, dim3(grid), dim3(SS_THREADS), smem, stream, p);                        \
+        vm_launch_pdl(skinny_stream_kernel<X, W, P>, dim3(grid), dim3((W + P) * 32), smem, stream, p);               \
     }
-    if (MT == 1) VM_SS_CASE(1) else VM_SS_CASE(2)
+    if (MT == 2) VM_SS_CASE(2, 8, 4) else if (cw == 16) VM_SS_CASE(1, 16, 4) else VM_SS_CASE(1, 8, 2)
 #undef VM_SS_CASE
     return vm_launch_status();
 }
