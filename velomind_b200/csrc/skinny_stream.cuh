@@ -29,8 +29,9 @@ struct StreamLayout { int ring, red, part, inv, bars, total; };
 __host__ __device__ inline StreamLayout stream_layout(int M, int K, int rows, int stage_rows, int stages, int cw) {
     StreamLayout L;
     L.ring = (M * skinny_pitch(K) + 127) / 128 * 128;                        // after the A tile: M rows of K bf16
-    L.red = L.ring + stages * stage_rows * SS_W_PITCH;                       // [warp][row][16] partial sums
-    L.part = L.red + cw * rows * 16 * (int)sizeof(float);              // [warp][row] partial sums of squares
+    L.red = L.ring + stages * stage_rows * SS_W_PITCH;                       // [buffer][warp][row][16] partial sums
+    // (up to 16 rows: two buffers of the live rows, rounded up to 8, used by alternate work items; else one of all rows)
+    L.part = L.red + (rows == 16 ? 2 * ((M + 7) / 8 * 8) : rows) * cw * 16 * (int)sizeof(float);   // [warp][row] partial sums of squares
     L.inv = L.part + cw * rows * (int)sizeof(float);                   // [row] 1/rms
     L.bars = L.inv + rows * (int)sizeof(float);                              // full[8], empty[8], two flags
     L.total = L.bars + 2 * SS_MAX_STAGES * 8 + 16;
@@ -116,10 +117,13 @@ skinny_stream_kernel(const SkinnyParams p) {
         if (p.epi == EPI_ROPE_KV) vm_pdl_launch_dependents();
         const int a_pitch = p.row_bytes;
         // this thread's place in the epilogue: one (row, column-in-tile) of the work item
-        const int e_row = tid >> 3, e_c = tid & 7;
-        const bool e_live = tid < ROWS * 8 && e_row < p.M;
+        // (an epilogue has ROWS x 8 such places; with more threads than that, groups of threads take the work items' epilogues
+        // in turn, so that the others are already multiplying the next item, and the partial sums have two buffers)
+        constexpr int EG = ROWS * 8, NG = SS_CONSUMER_THREADS / EG;
+        const int e_row = (tid % EG) >> 3, e_c = tid & 7, e_grp = tid / EG;
+        const int red_rows = NG > 1 ? (p.M + 7) / 8 * 8 : ROWS;
         int row_pos = 0, row_page = -1;
-        if (p.epi == EPI_ROPE_KV && e_live) {
+        if (p.epi == EPI_ROPE_KV && e_row < p.M) {
             row_pos = p.positions[e_row];
             if (p.kpages != nullptr) {
                 const int blk = row_pos / VM_PAGE_TOKENS;
@@ -185,6 +189,8 @@ skinny_stream_kernel(const SkinnyParams p) {
             const SkinnyCols cols = skinny_cols(p, (int)blockIdx.x + it * (int)gridDim.x);
             const int nA = cols.nA, nB = cols.nB, head = cols.head;
             const bool rotate = p.epi == EPI_ROPE_KV && head < p.H + p.Hkv && p.rot_dim > 0;
+            const bool e_live = e_row < p.M && e_grp == it % NG;
+            float* const red_it = red + (NG > 1 ? (size_t)(it & 1) * SS_CONSUMERS * red_rows * 16 : 0);
             // what the epilogue adds to or multiplies with is requested now: its latency passes under the product
             float freq = 0.f, res_a = 0.f, res_b = 0.f;
             if (rotate) freq = p.inv_freq[(nA - head * p.D) + e_c];
@@ -235,7 +241,7 @@ skinny_stream_kernel(const SkinnyParams p) {
                     for (int half = 0; half < 2; ++half) {
                         const int row = mt * 16 + g + 8 * half;
                         if (row < p.M && (t == 0 || two))
-                            *reinterpret_cast<float2*>(&red[((size_t)warp * ROWS + row) * 16 + t * 8 + 2 * t4]) =
+                            *reinterpret_cast<float2*>(&red_it[((size_t)warp * red_rows + row) * 16 + t * 8 + 2 * t4]) =
                                 make_float2(acc[mt][t][2 * half], acc[mt][t][2 * half + 1]);
                     }
             ss_consumer_sync<SS_CONSUMER_THREADS>();
@@ -244,8 +250,8 @@ skinny_stream_kernel(const SkinnyParams p) {
                 float vA = 0.f, vB = 0.f;
 #pragma unroll
                 for (int w = 0; w < SS_CONSUMERS; ++w) {
-                    vA += red[((size_t)w * ROWS + row) * 16 + c];
-                    if (two) vB += red[((size_t)w * ROWS + row) * 16 + 8 + c];
+                    vA += red_it[((size_t)w * red_rows + row) * 16 + c];
+                    if (two) vB += red_it[((size_t)w * red_rows + row) * 16 + 8 + c];
                 }
                 if (p.pro == PRO_RMSNORM) { const float rs = inv[row]; vA *= rs; vB *= rs; }
                 switch (p.epi) {
@@ -292,7 +298,7 @@ skinny_stream_kernel(const SkinnyParams p) {
                     } break;
                 }
             }
-            ss_consumer_sync<SS_CONSUMER_THREADS>();                                  // the sums' buffer is reused by the next item
+            if (NG == 1) ss_consumer_sync<SS_CONSUMER_THREADS>();                    // the sums' one buffer is reused by the next item
         }
     }
     // ---- a wait that ran out: nothing more was stored; copies still in flight into this CTA's shared memory are waited
