@@ -514,6 +514,24 @@ def test_skinny_linear(M, N, K, skinny_kernel):
     assert int(err.item()) == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(8, 2304, 2048), (16, 640, 8192), (40, 2304, 2048)])
+def test_skinny_linear_chooses_its_kernel_by_size(M, N, K):
+    """Left to themselves the launchers take the ring kernel from 9 MB of weights and up to 32 rows; where it does not take the
+    sizes (16 rows of K = 8,192 do not fit its shared memory beside two stages; 40 rows are too many) they fall back to the
+    register-fed kernel.  Same result either way."""
+    o = ops()
+    o.skinny_variant(0)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    x = _bf(torch.randn(M, K, generator=_gen(M)))
+    w = _bf(torch.randn(N, K, generator=_gen(N)) * 0.05)
+    h = torch.randn(M, N, generator=_gen(K))
+    want = h + x.float() @ w.float().t()
+    hd = h.to(DEV)
+    o.skinny_linear(x.to(DEV), None, w.to(DEV), None, residual=hd, err=err)
+    assert (hd.cpu() - want).abs().max() <= 1e-3 * max(1.0, float(want.abs().max()))
+    assert int(err.item()) == 0
+
+
 @pytest.mark.parametrize("M,I,K", [(3, 192, 64), (8, 1536, 576), (33, 160, 96), (64, 1000, 1536), (5, 5000, 96), (20, 2000, 1088), (16, 3000, 3104),
                                    (32, 2504, 1024)])
 def test_skinny_swiglu(M, I, K, skinny_kernel):
