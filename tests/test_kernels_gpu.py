@@ -467,13 +467,13 @@ def _rms_ref(h, w, eps):
     return _bf(torch.from_numpy(P.rmsnorm(h.numpy(), w.numpy(), eps)))
 
 
-@pytest.fixture(params=["register-fed", "ring", "ring-one-cta"])
+@pytest.fixture(params=["register-fed", "ring-two-ctas", "ring-two-pipelines"])
 def skinny_kernel(request):
     """Both weight-streaming kernels, forced: the one that fetches weights into registers (what small matrices take) and the
-    one that streams them through a ring in shared memory (large matrices, at most 32 rows), the latter also in the form it
-    takes when only one CTA fits an SM (sixteen multiplying warps for up to 16 rows)."""
+    one that streams them through a ring in shared memory (large matrices, at most 32 rows), the latter in both its forms for
+    up to 16 rows: two CTAs per SM, or one CTA whose two pipelines share the staged rows."""
     o = ops()
-    o.skinny_variant({"register-fed": 1, "ring": 2, "ring-one-cta": 3}[request.param])
+    o.skinny_variant({"register-fed": 1, "ring-two-ctas": 4, "ring-two-pipelines": 3}[request.param])
     yield request.param
     o.skinny_variant(0)
 

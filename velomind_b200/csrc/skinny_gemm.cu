@@ -139,7 +139,7 @@ constexpr long long STREAM_MIN_WEIGHT_BYTES = 9ll << 20;
 int skinny_dispatch(SkinnyParams p, int items, cudaStream_t stream) {
     const long long weight_bytes = (long long)p.N * p.K * 2;
     if (skinny_variant >= 2 || (skinny_variant == 0 && p.M <= 32 && weight_bytes >= STREAM_MIN_WEIGHT_BYTES)) {
-        const int rc = skinny_stream_launch(p, items, stream, skinny_variant == 3);
+        const int rc = skinny_stream_launch(p, items, stream, skinny_variant == 3 ? 2 : (skinny_variant == 4 ? 1 : 0));
         if (rc != VM_ERR_UNSUPPORTED || skinny_variant >= 2) return rc;
     }
     return skinny_launch(p, items, stream);
@@ -148,8 +148,8 @@ int skinny_dispatch(SkinnyParams p, int items, cudaStream_t stream) {
 }  // namespace
 
 // 0: the launchers choose between the two weight-streaming kernels by size; 1: always skinny_gemm_kernel; 2: always
-// skinny_stream_kernel (VM_ERR_UNSUPPORTED where it does not take the sizes); 3: the same with one CTA per SM.  For tests
-// and measurements.
+// skinny_stream_kernel (VM_ERR_UNSUPPORTED where it does not take the sizes); 3 / 4: the same in its form of one CTA with two
+// pipelines per SM / of two CTAs per SM.  For tests and measurements.
 VM_API void vm_skinny_variant(int variant) { skinny_variant = variant; }
 
 // out = A W^T (pro 0) or rmsnorm(h) W^T (pro 1); out bf16 (out_f32 0) or float32 (1); or h += ... (residual 1).

@@ -99,7 +99,7 @@ def main(argv=None) -> int:
     ap.add_argument("--layers", type=int, default=6, help="prefill_step: layers of the random model")
     ap.add_argument("--temp", type=float, default=0.0, help="sample: temperature (0: greedy)")
     ap.add_argument("--top-p", type=float, default=0.9, help="sample: nucleus mass, with --temp")
-    ap.add_argument("--variant", type=int, default=0, help="weight-streaming products: 0 the launcher's choice, 1 the register-fed kernel, 2 the one with a ring in shared memory")
+    ap.add_argument("--variant", type=int, default=0, help="weight-streaming products: 0 the launcher's choice, 1 the register-fed kernel, 2 the one with a ring in shared memory (3 / 4: its form with two pipelines in one CTA / two CTAs per SM)")
     ap.add_argument("--repeat", type=int, default=50)
     ap.add_argument("--no-graph", action="store_true")
     a = ap.parse_args(argv)

@@ -287,7 +287,8 @@ def _norm_args(norm):
 
 def skinny_variant(variant: int) -> None:
     """Which weight-streaming kernel the three launchers below take: 0 by size, 1 the register-fed one, 2 the one that streams
-    the weights through shared memory (refuses what it does not take)."""
+    the weights through shared memory (refuses what it does not take), 3 / 4 that one as one CTA with two pipelines / as two CTAs
+    per SM."""
     library().vm_skinny_variant(_c_int(variant))
 
 
