@@ -9,7 +9,8 @@
 // weight row and stage, 2 KB each, completion counted on an mbarrier), which keeps 60 to 190 KB per SM in flight whatever
 // the eight multiplying warps are doing, starts before the wait on the predecessor kernel (weights are constants) and
 // costs the multiplying warps two 16-byte shared-memory loads per two mma.sync.  The prologue reads every row's value of
-// a column by the same thread, so one round of loads covers all rows.
+// a column by the same thread, so one round of loads covers all rows.  Copying warps, multiplying warps, their work items,
+// ring, sums and barriers are a pipeline; a CTA is one pipeline (two CTAs per SM) or two that share the staged rows.
 //
 // Work item, column permutation, accumulation order inside a warp, join of the eight warps and epilogues are those of
 // skinny_run; so are the results, up to the order in which a warp's k blocks are summed.
