@@ -514,9 +514,10 @@ def test_skinny_linear(M, N, K, skinny_kernel):
     assert int(err.item()) == 0
 
 
-@pytest.mark.parametrize("M,N,K", [(8, 2304, 2048), (16, 640, 8192), (40, 2304, 2048)])
+@pytest.mark.parametrize("M,N,K", [(8, 2304, 2048), (16, 640, 8192), (40, 2304, 2048), (2, 1200, 2048), (3, 1200, 2048)])
 def test_skinny_linear_chooses_its_kernel_by_size(M, N, K):
-    """Left to themselves the launchers take the ring kernel from 9 MB of weights and up to 32 rows; where it does not take the
+    """Left to themselves the launchers take the ring kernel from 9 MB of weights and up to 32 rows (from 4.5 MB for one or two
+    rows: the last two cases lie on either side); where it does not take the
     sizes (16 rows of K = 8,192 do not fit its shared memory beside two stages; 40 rows are too many) they fall back to the
     register-fed kernel.  Same result either way."""
     o = ops()

@@ -131,14 +131,17 @@ int skinny_launch(SkinnyParams p, int grid, cudaStream_t stream) {
 }
 
 // Which kernel takes a product of `items` work items: the streaming one when the weights are large enough for memory
-// bandwidth, not one chain of latencies, to set the time (measured at hidden sizes 960 and 2,048 against 576), or when
+// bandwidth, not one chain of latencies, to set the time (measured at hidden sizes 960 and 2,048 against 576: from 9 MB, and
+// from 4.5 MB for one or two rows: the down projection at hidden 960, 4.9 MB, takes 4.9 / 5.0 / 5.1 us at 1 / 2 / 4 rows in the
+// register-fed kernel and 3.9 / 4.5 / 4.9 us in this one), or when
 // vm_skinny_variant() asks for it.
 int skinny_variant = 0;
 constexpr long long STREAM_MIN_WEIGHT_BYTES = 9ll << 20;
+constexpr long long STREAM_MIN_WEIGHT_BYTES_TWO_ROWS = 9ll << 19;      // 4.5 MB: with one or two rows there is next to no prologue
 
 int skinny_dispatch(SkinnyParams p, int items, cudaStream_t stream) {
     const long long weight_bytes = (long long)p.N * p.K * 2;
-    if (skinny_variant >= 2 || (skinny_variant == 0 && p.M <= 32 && weight_bytes >= STREAM_MIN_WEIGHT_BYTES)) {
+    if (skinny_variant >= 2 || (skinny_variant == 0 && p.M <= 32 && weight_bytes >= (p.M <= 2 ? STREAM_MIN_WEIGHT_BYTES_TWO_ROWS : STREAM_MIN_WEIGHT_BYTES))) {
         const int rc = skinny_stream_launch(p, items, stream, skinny_variant == 3 ? 2 : (skinny_variant == 4 ? 1 : 0));
         if (rc != VM_ERR_UNSUPPORTED || skinny_variant >= 2) return rc;
     }
