@@ -174,6 +174,13 @@ namespace ops {
 
 int SKINNY_MAX_ROWS = 32;      // beyond this the library product wins (the A tile is staged once per CTA; measured per decode step at
                                // 33 / 48 / 64 rows: 1.07 / 1.20 / 1.25 ms fused against 1.02 / 1.07 / 1.05 ms with the library product)
+// Large weight matrices: the library product streams them at 3.5 to 5.5 TB/s from 16 rows on, whatever the row count (hidden
+// 2,048, 32 rows: 7.2 / 12.1 / 12.5 us for qkv / gate-up / down), the weight-streaming kernels slow down with every row they
+// stage.  Decode steps of the 1.7B shape (24 layers), fused against library path: 8 rows 1.32 / 1.63 ms, 12 rows 1.81 / 1.87,
+// 16 rows 1.96 / 1.85, 24 rows 2.83 / 2.12, 32 rows 3.22 / 2.30; the 360M shape (largest matrix 9.8 MB) stays fused up to 32
+// rows (0.79 / 1.29 ms at 8 rows, 1.45 / 1.43 at 32).
+int SKINNY_MAX_ROWS_LARGE = 8;
+long long SKINNY_LARGE_WEIGHT_BYTES = 16ll << 20;
 int SKINNY_NORM_ROWS = 32;     // up to this many rows the norm is fused into the product that follows it (measured per decode step at
                                // 17 / 24 / 32 rows: 0.70 / 0.72 / 0.86 ms against 0.82 / 0.84 / 0.92 ms with a norm kernel of its own)
 

@@ -100,6 +100,12 @@ void attention(StepContext& ctx, const void* q, int q_row_stride, const KVView& 
 // the weight-streaming products for few rows (bfloat16 weights)
 extern int SKINNY_MAX_ROWS;        // beyond this many rows the library product takes over
 extern int SKINNY_NORM_ROWS;       // up to this many rows the norm is fused into the product that follows it
+extern int SKINNY_MAX_ROWS_LARGE;  // the same limit for a part whose largest weight matrix has SKINNY_LARGE_WEIGHT_BYTES and more
+extern long long SKINNY_LARGE_WEIGHT_BYTES;
+// rows (of a step's capacity) up to which the weight-streaming kernels take a part whose largest weight matrix has `weight_bytes`
+inline int skinny_max_rows(long long weight_bytes) {
+    return weight_bytes >= SKINNY_LARGE_WEIGHT_BYTES && SKINNY_MAX_ROWS_LARGE < SKINNY_MAX_ROWS ? SKINNY_MAX_ROWS_LARGE : SKINNY_MAX_ROWS;
+}
 inline bool skinny_ok(int M, long long K, const DeviceTensor& W) { return M > 0 && M <= SKINNY_MAX_ROWS && K % 32 == 0 && W.dtype == DType::BF16; }
 
 inline void skinny_linear(const void* x, const float* norm_w, float eps, const DeviceTensor& W, int M, void* out, int out_stride, bool out_f32,

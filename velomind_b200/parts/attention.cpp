@@ -53,6 +53,11 @@ public:
     // True if this step can run as: [norm +] qkv + rotary + cache write -> attention -> out + residual, with the
     // weight-streaming kernels (few tokens), the tensor-core kernels (many tokens, when asked for) or the library products
     // (the out projection then adds into the residual stream as its own accumulator).
+    // rows up to which the weight-streaming kernels take this part (fewer when its matrices are large)
+    int max_rows() const {
+        return ops::skinny_max_rows(2 * std::max(qkv_.weight.rows() * qkv_.weight.cols(), out_.weight.rows() * out_.weight.cols()));
+    }
+
     bool can_fuse(const StepContext& ctx, const Norm& norm) const override {
         const float* nw;
         float eps;
@@ -60,8 +65,8 @@ public:
         if (qkv_.weight.dtype != DType::BF16 || out_.weight.dtype != DType::BF16) return false;
         if (hidden_ % 8 || (H_ * D_) % 8) return false;
         const bool fused_rotary = rotary_.rotary_dim == 0 || (rotary_.rotary_dim == D_ && rotary_.pairing == VM_PAIR_HALF_SPLIT);
-        if (!fused_rotary) return ctx.T_cap > ops::SKINNY_MAX_ROWS;      // (the library path rotates with the kernel of its own)
-        if (ctx.T_cap <= ops::SKINNY_MAX_ROWS) return hidden_ % 32 == 0 && (H_ * D_) % 32 == 0 && D_ % 16 == 0;
+        if (!fused_rotary) return ctx.T_cap > max_rows();      // (the library path rotates with the kernel of its own)
+        if (ctx.T_cap <= max_rows()) return hidden_ % 32 == 0 && (H_ * D_) % 32 == 0 && D_ % 16 == 0;
         return true;
     }
 
@@ -71,7 +76,7 @@ public:
         float eps = 0.f;
         norm.as_rms(&nw, &eps);
         const KVView kv = ctx.kv();
-        const bool skinny = ctx.T_cap <= ops::SKINNY_MAX_ROWS;
+        const bool skinny = ctx.T_cap <= max_rows();
         const bool fused_rotary = rotary_.rotary_dim == 0 || (rotary_.rotary_dim == D_ && rotary_.pairing == VM_PAIR_HALF_SPLIT);
         const bool tc = !skinny && fused_rotary && ops::tc_fused_rows(ctx) && (D_ == 64 || D_ == 128);
         if (!skinny && !tc) {

@@ -25,12 +25,17 @@ public:
 
     bool graph_safe() const override { return true; }
 
+    // rows up to which the weight-streaming kernels take this part (fewer when its matrices are large)
+    int max_rows() const {
+        return ops::skinny_max_rows(2 * std::max(gate_up_.weight.rows() * gate_up_.weight.cols(), down_.weight.rows() * down_.weight.cols()));
+    }
+
     bool can_fuse(const StepContext& ctx, const Norm& norm) const override {
         const float* nw;
         float eps;
         if (!norm.as_rms(&nw, &eps) || ctx.act_dtype != DType::BF16) return false;
         if (gate_up_.weight.dtype != DType::BF16 || down_.weight.dtype != DType::BF16) return false;
-        if (ctx.T_cap <= ops::SKINNY_MAX_ROWS) return hidden_ % 32 == 0 && I_ % 32 == 0;
+        if (ctx.T_cap <= max_rows()) return hidden_ % 32 == 0 && I_ % 32 == 0;
         return hidden_ % 8 == 0 && I_ % 8 == 0;
     }
 
@@ -39,7 +44,7 @@ public:
         const float* nw = nullptr;
         float eps = 0.f;
         norm.as_rms(&nw, &eps);
-        const bool skinny = ctx.T_cap <= ops::SKINNY_MAX_ROWS;
+        const bool skinny = ctx.T_cap <= max_rows();
         const bool tc = !skinny && ops::tc_fused_rows(ctx) && I_ % 64 == 0;
         if (!skinny && !tc) {
             // the library's products: norm, gate and up, SwiGLU, down added into h by the product itself
