@@ -180,6 +180,9 @@ int SKINNY_MAX_ROWS = 32;      // beyond this the library product wins (the A ti
 // 16 rows 1.96 / 1.85, 24 rows 2.83 / 2.12, 32 rows 3.22 / 2.30; the 360M shape (largest matrix 9.8 MB) stays fused up to 32
 // rows (0.79 / 1.29 ms at 8 rows, 1.45 / 1.43 at 32).
 int SKINNY_MAX_ROWS_LARGE = 8;
+// The head (49,152 rows of K = 576 / 960 / 2,048): own kernels 13.0 / 18.1 / 31.8 us at 8 rows, 24.0 / 35.8 / 55.8 us at 32; the
+// library product 11 to 35 us whatever the row count (17.6 / 34.6 us at 8 rows of K = 960 / 2,048, 11.2 / 18.2 / 35.5 us at 32).
+int SKINNY_HEAD_MAX_ROWS = 8;
 long long SKINNY_LARGE_WEIGHT_BYTES = 16ll << 20;
 int SKINNY_NORM_ROWS = 32;     // up to this many rows the norm is fused into the product that follows it (measured per decode step at
                                // 17 / 24 / 32 rows: 0.70 / 0.72 / 0.86 ms against 0.82 / 0.84 / 0.92 ms with a norm kernel of its own)

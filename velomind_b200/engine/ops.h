@@ -100,6 +100,7 @@ void attention(StepContext& ctx, const void* q, int q_row_stride, const KVView& 
 // the weight-streaming products for few rows (bfloat16 weights)
 extern int SKINNY_MAX_ROWS;        // beyond this many rows the library product takes over
 extern int SKINNY_NORM_ROWS;       // up to this many rows the norm is fused into the product that follows it
+extern int SKINNY_HEAD_MAX_ROWS;   // up to this many rows the head streams its table with the weight-streaming kernels
 extern int SKINNY_MAX_ROWS_LARGE;  // the same limit for a part whose largest weight matrix has SKINNY_LARGE_WEIGHT_BYTES and more
 extern long long SKINNY_LARGE_WEIGHT_BYTES;
 // rows (of a step's capacity) up to which the weight-streaming kernels take a part whose largest weight matrix has `weight_bytes`

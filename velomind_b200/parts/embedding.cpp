@@ -37,7 +37,7 @@ public:
     void bind(const Weights& w, BindContext& bc) override { proj_.bind({&w.at("weight")}, bc); }
     bool graph_safe() const override { return true; }
     void forward(StepContext& ctx, const void* x, float* logits) override {
-        if (ctx.act_dtype == DType::BF16 && ops::skinny_ok(ctx.R, hidden_, proj_.weight) && vocab_ % 8 == 0 && ctx.R_cap <= ops::SKINNY_MAX_ROWS)
+        if (ctx.act_dtype == DType::BF16 && ops::skinny_ok(ctx.R, hidden_, proj_.weight) && vocab_ % 8 == 0 && ctx.R_cap <= ops::SKINNY_HEAD_MAX_ROWS)
             ops::skinny_linear(x, nullptr, 0.f, proj_.weight, ctx.R, logits, vocab_, true, nullptr, ctx.err, ctx.stream);   // few rows: stream the table once
         else
             proj_.apply(ctx, x, ctx.act_dtype, logits, DType::F32, ctx.R, ctx.R_cap);
